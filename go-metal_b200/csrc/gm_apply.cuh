@@ -1,0 +1,156 @@
+// gm_apply.cuh -- the multi-tensor-apply skeleton shared by the fp32 rules.
+//
+// One launch walks a whole tensor list.  Work is cut into fixed-size chunks of
+// one tensor each; persistent CTAs take chunks in a grid-stride loop.  Inside a
+// chunk every stream is read and written with 128-bit accesses; the few
+// elements before the first and after the last 16-byte boundary of a tensor
+// are handled one at a time by the first threads of the CTA.
+//
+// Arithmetic uses the round-to-nearest intrinsics (__fmul_rn, __fadd_rn,
+// __fdiv_rn, __fsqrt_rn): the compiler never contracts them into fused
+// multiply-adds, so each operation rounds exactly like the scalar statement
+// order of cgo_bridge/bridge_optimizer.m.
+#pragma once
+
+#include "gm_internal.h"
+
+namespace gm {
+
+__device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float dvd(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float root(float a) { return __fsqrt_rn(a); }
+
+// Streaming accesses: every byte is touched once per step, so lines are marked
+// evict-first on the way in and on the way out.
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }
+
+// Finds the tensor that owns chunk c: the largest t with prefix[t] <= c.
+__device__ __forceinline__ int find_tensor(const int* __restrict__ prefix, int num_tensors, int c) {
+    int lo = 0, hi = num_tensors;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (__ldg(prefix + mid) <= c) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// Rule concept:
+//   static constexpr int NS;            number of streams (w, g, state...)
+//   static constexpr unsigned WMASK;    bit s set => stream s is written back
+//   struct P;                           scalars, passed by value
+//   static __device__ void elem(float (&x)[NS], const P&);   in-place on x
+template <class Rule, int UNROLL>
+__global__ void __launch_bounds__(kApplyThreads)
+mta_apply_kernel(const DevList L, const typename Rule::P prm) {
+    constexpr int NS = Rule::NS;
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+
+    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+        const int t = find_tensor(L.chunk_prefix, T, c);
+        const int k = c - __ldg(L.chunk_prefix + t);
+        const long long n = __ldg(L.numel + t);
+        const int h = __ldg(L.head + t);
+        float* p[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) p[s] = reinterpret_cast<float*>(__ldg(L.ptrs + (size_t)s * T + t));
+
+        if (h < 0) {
+            // streams disagree on alignment: element-wise walk of this chunk
+            const long long b = (long long)k * chunk;
+            const long long e = (b + chunk < n) ? b + chunk : n;
+            for (long long i = b + tid; i < e; i += NT) {
+                float x[NS];
+#pragma unroll
+                for (int s = 0; s < NS; ++s) x[s] = ld_stream(p[s] + i);
+                Rule::elem(x, prm);
+#pragma unroll
+                for (int s = 0; s < NS; ++s) if (Rule::WMASK & (1u << s)) st_stream(p[s] + i, x[s]);
+            }
+            continue;
+        }
+
+        const long long b = (long long)h + (long long)k * chunk;     // 16-byte aligned in every stream
+        const long long e = (b + chunk < n) ? b + chunk : n;
+
+        if (k == 0 && tid < h) {                                      // head of the tensor
+            float x[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) x[s] = ld_stream(p[s] + tid);
+            Rule::elem(x, prm);
+#pragma unroll
+            for (int s = 0; s < NS; ++s) if (Rule::WMASK & (1u << s)) st_stream(p[s] + tid, x[s]);
+        }
+
+        const long long nvec = (e - b) >> 2;
+        float4* q[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) q[s] = reinterpret_cast<float4*>(p[s] + b);
+
+        for (long long i0 = tid; i0 < nvec; i0 += (long long)NT * UNROLL) {
+            float4 v[UNROLL][NS];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const long long i = i0 + (long long)u * NT;
+                if (i < nvec) {
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) v[u][s] = ld_stream(q[s] + i);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const long long i = i0 + (long long)u * NT;
+                if (i < nvec) {
+                    float x0[NS], x1[NS], x2[NS], x3[NS];
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) { x0[s] = v[u][s].x; x1[s] = v[u][s].y; x2[s] = v[u][s].z; x3[s] = v[u][s].w; }
+                    Rule::elem(x0, prm);
+                    Rule::elem(x1, prm);
+                    Rule::elem(x2, prm);
+                    Rule::elem(x3, prm);
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) {
+                        if (Rule::WMASK & (1u << s)) st_stream(q[s] + i, make_float4(x0[s], x1[s], x2[s], x3[s]));
+                    }
+                }
+            }
+        }
+
+        const long long tb = b + (nvec << 2);                         // tail of the tensor (< 4 elements)
+        if (tb + tid < e) {
+            const long long i = tb + tid;
+            float x[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) x[s] = ld_stream(p[s] + i);
+            Rule::elem(x, prm);
+#pragma unroll
+            for (int s = 0; s < NS; ++s) if (Rule::WMASK & (1u << s)) st_stream(p[s] + i, x[s]);
+        }
+    }
+}
+
+template <class Rule, int UNROLL>
+int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm) {
+    if (l->dl.num_streams != Rule::NS) {
+        set_error("tensor list has %d streams, rule needs %d", l->dl.num_streams, Rule::NS);
+        return GM_ERR_BAD_ARG;
+    }
+    for (int s = 0; s < Rule::NS; ++s) {
+        if (l->elem_bytes[s] != 4) { set_error("stream %d is not fp32", s); return GM_ERR_BAD_ARG; }
+    }
+    auto kernel = mta_apply_kernel<Rule, UNROLL>;
+    int grid = persistent_grid(d, (const void*)kernel, kApplyThreads, l->dl.num_chunks);
+    kernel<<<grid, kApplyThreads, 0, d->stream>>>(l->dl, prm);
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    return GM_OK;
+}
+
+}  // namespace gm

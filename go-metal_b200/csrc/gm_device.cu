@@ -1,0 +1,621 @@
+// gm_device.cu -- device handles, the buffer registry, cudaMalloc-backed
+// buffers and arenas, host<->device copies and the fp32<->fp16 conversion.
+//
+// Replaces cgo_bridge/bridge_memory.m (allocate/zero/copy/convert, :4-55,
+// :163-188, :221-423) and the device/queue calls of cgo_bridge/bridge_device.m
+// for the optimizer-step path.
+#include <cuda_fp16.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <set>
+
+#include "gm_internal.h"
+
+namespace gm {
+
+// ------------------------------------------------------------------
+// errors
+// ------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return GM_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------
+// live-handle and buffer registries
+// ------------------------------------------------------------------
+struct BufInfo { int64_t bytes; int ordinal; bool owned; };
+struct Arena {
+    uintptr_t base = 0; int64_t cap = 0; int64_t used = 0; int ordinal = 0;
+};
+
+static std::mutex g_mu;
+static std::set<Device*> g_devices;
+static std::set<TensorList*> g_lists;
+static std::set<Arena*> g_arenas;
+static std::unordered_map<uintptr_t, BufInfo> g_bufs;
+
+Device* as_device(uintptr_t h) {
+    if (h == 0) { set_error("device handle is nil"); return nullptr; }
+    std::lock_guard<std::mutex> lk(g_mu);
+    Device* d = reinterpret_cast<Device*>(h);
+    if (!g_devices.count(d)) { set_error("handle %p is not a live device", (void*)h); return nullptr; }
+    return d;
+}
+
+TensorList* as_list(uintptr_t h) {
+    if (h == 0) { set_error("tensor list handle is nil"); return nullptr; }
+    std::lock_guard<std::mutex> lk(g_mu);
+    TensorList* l = reinterpret_cast<TensorList*>(h);
+    if (!g_lists.count(l)) { set_error("handle %p is not a live tensor list", (void*)h); return nullptr; }
+    return l;
+}
+
+static Arena* as_arena(uintptr_t h) {
+    if (h == 0) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    Arena* a = reinterpret_cast<Arena*>(h);
+    return g_arenas.count(a) ? a : nullptr;
+}
+
+int64_t registered_size(uintptr_t p) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_bufs.find(p);
+    return it == g_bufs.end() ? -1 : it->second.bytes;
+}
+
+int registered_ordinal(uintptr_t p) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_bufs.find(p);
+    return it == g_bufs.end() ? -1 : it->second.ordinal;
+}
+
+static int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+static uintptr_t alloc_registered(Device* d, int64_t bytes) {
+    if (bytes <= 0) { set_error("allocation size %lld is not positive", (long long)bytes); return 0; }
+    DeviceGuard g(d);
+    void* p = nullptr;
+    // cudaMalloc returns 256-byte aligned addresses; the reservation is rounded
+    // up to the same granule so vector tails never touch a neighbour.
+    cudaError_t e = cudaMalloc(&p, (size_t)round_up(bytes, 256));
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc"); cudaGetLastError(); return 0; }
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_bufs[(uintptr_t)p] = BufInfo{bytes, d->ordinal, true};
+    return (uintptr_t)p;
+}
+
+static void free_registered(uintptr_t p) {
+    if (!p) return;
+    BufInfo info{};
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_bufs.find(p);
+        if (it == g_bufs.end() || !it->second.owned) return;   // not ours: leave it alone
+        info = it->second;
+        g_bufs.erase(it);
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != info.ordinal) cudaSetDevice(info.ordinal);
+    cudaFree((void*)p);
+    if (prev != info.ordinal && prev >= 0) cudaSetDevice(prev);
+}
+
+// ------------------------------------------------------------------
+// devices
+// ------------------------------------------------------------------
+static Device* make_device(int ordinal) {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        set_error("no CUDA device is visible (%s); this library has no CPU path",
+                  e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (ordinal < 0 || ordinal >= count) { set_error("device ordinal %d out of range [0,%d)", ordinal, count); return nullptr; }
+    e = cudaSetDevice(ordinal);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaSetDevice"); return nullptr; }
+    Device* d = new Device();
+    d->ordinal = ordinal;
+    cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
+    e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaStreamCreate"); delete d; return nullptr; }
+    cudaEventCreate(&d->ev_start);
+    cudaEventCreate(&d->ev_stop);
+    e = cudaMalloc((void**)&d->ticket, 256);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&d->scalars, 4096);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(scratch)"); delete d; return nullptr; }
+    cudaMemset(d->ticket, 0, 256);
+    cudaMemset(d->scalars, 0, 4096);
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_devices.insert(d);
+    return d;
+}
+
+int ensure_partials(Device* d, int64_t count) {
+    if (count <= d->partials_cap) return GM_OK;
+    DeviceGuard g(d);
+    int64_t cap = round_up(count, 4096);
+    if (d->partials) { cudaStreamSynchronize(d->stream); cudaFree(d->partials); d->partials = nullptr; d->partials_cap = 0; }
+    GM_CUDA_CHECK(cudaMalloc((void**)&d->partials, (size_t)cap * sizeof(float)));
+    d->partials_cap = cap;
+    return GM_OK;
+}
+
+int persistent_grid(Device* d, const void* kernel, int threads, int64_t work_items) {
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+    if (e != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+    int64_t grid = (int64_t)per_sm * d->sm_count;
+    if (grid > work_items) grid = work_items;
+    if (grid < 1) grid = 1;
+    return (int)grid;
+}
+
+// ------------------------------------------------------------------
+// tensor lists
+// ------------------------------------------------------------------
+static uint64_t fnv1a(uint64_t h, const void* data, size_t n) {
+    const unsigned char* p = (const unsigned char*)data;
+    for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 0x100000001b3ull; }
+    return h;
+}
+
+void free_list(TensorList* l) {
+    if (!l) return;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_lists.erase(l);
+    }
+    if (l->blob && l->dev) {
+        DeviceGuard g(l->dev);
+        cudaFree(l->blob);
+    }
+    delete l;
+}
+
+TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, const int64_t* numel,
+                       const int* elem_bytes, bool cache, int* err) {
+    *err = GM_OK;
+    if (ns < 1 || ns > kMaxStreams) { set_error("stream count %d outside [1,%d]", ns, kMaxStreams); *err = GM_ERR_BAD_ARG; return nullptr; }
+    if (nt < 1) { set_error("tensor count %d is not positive", nt); *err = GM_ERR_BAD_ARG; return nullptr; }
+    for (int t = 0; t < nt; ++t) {
+        if (numel[t] <= 0) { set_error("tensor %d has %lld elements", t, (long long)numel[t]); *err = GM_ERR_BAD_SIZE; return nullptr; }
+        for (int s = 0; s < ns; ++s) {
+            uintptr_t p = sp[s][t];
+            if (p == 0) { set_error("stream %d tensor %d is a nil buffer", s, t); *err = GM_ERR_NIL_BUFFER; return nullptr; }
+            int eb = elem_bytes ? elem_bytes[s] : 4;
+            if (p % (uintptr_t)eb) { set_error("stream %d tensor %d address is not %d-byte aligned", s, t, eb); *err = GM_ERR_BAD_ARG; return nullptr; }
+            int64_t have = registered_size(p);
+            if (have >= 0 && have < numel[t] * eb) {
+                set_error("stream %d tensor %d: buffer holds %lld bytes, step needs %lld", s, t,
+                          (long long)have, (long long)(numel[t] * eb));
+                *err = GM_ERR_BAD_SIZE;
+                return nullptr;
+            }
+        }
+    }
+    uint64_t key = 0xcbf29ce484222325ull;
+    key = fnv1a(key, &ns, sizeof(ns));
+    key = fnv1a(key, &nt, sizeof(nt));
+    for (int s = 0; s < ns; ++s) {
+        key = fnv1a(key, sp[s], sizeof(uintptr_t) * nt);
+        int eb = elem_bytes ? elem_bytes[s] : 4;
+        key = fnv1a(key, &eb, sizeof(eb));
+    }
+    key = fnv1a(key, numel, sizeof(int64_t) * nt);
+    if (key == 0) key = 1;
+    if (cache) {
+        std::lock_guard<std::mutex> lk(d->mu);
+        auto it = d->list_cache.find(key);
+        if (it != d->list_cache.end()) {
+            TensorList* l = it->second;
+            bool same = (int)l->ptrs.size() == ns && (int)l->numel.size() == nt;
+            for (int s = 0; same && s < ns; ++s)
+                same = memcmp(l->ptrs[s].data(), sp[s], sizeof(uintptr_t) * nt) == 0
+                       && l->elem_bytes[s] == (elem_bytes ? elem_bytes[s] : 4);
+            if (same) same = memcmp(l->numel.data(), numel, sizeof(int64_t) * nt) == 0;
+            if (same) return l;
+            d->list_cache.erase(it);   // hash collision: rebuild below
+            free_list(l);
+        }
+    }
+
+    TensorList* l = new TensorList();
+    l->dev = d;
+    l->numel.assign(numel, numel + nt);
+    l->ptrs.resize(ns);
+    for (int s = 0; s < ns; ++s) {
+        l->ptrs[s].assign(sp[s], sp[s] + nt);
+        l->elem_bytes[s] = elem_bytes ? elem_bytes[s] : 4;
+    }
+    int64_t total = 0;
+    for (int t = 0; t < nt; ++t) total += numel[t];
+    l->total = total;
+
+    // Chunk size: large chunks amortise the per-chunk lookup on big lists;
+    // small lists get small chunks so every SM has work.
+    const int tile = kApplyThreads * 8;                 // elements one CTA pass covers
+    int chunk = tile * 8;                               // 16384
+    int64_t want = (int64_t)d->sm_count * 8;
+    while (chunk > tile && total / chunk < want) chunk /= 2;
+
+    // head[t]: number of leading elements to peel so that every stream of the
+    // tensor sits on a 16-byte boundary; the vector tile is 8 elements for
+    // lists with 2-byte streams so one 16-byte access covers it.
+    std::vector<int> head(nt), prefix(nt + 1);
+    int lanes = 4;
+    for (int s = 0; s < ns; ++s) if (l->elem_bytes[s] == 2) lanes = 8;
+    prefix[0] = 0;
+    for (int t = 0; t < nt; ++t) {
+        int h = -1;
+        for (int cand = 0; cand < lanes && h < 0; ++cand) {
+            bool ok = true;
+            for (int s = 0; s < ns && ok; ++s)
+                ok = ((sp[s][t] + (uintptr_t)cand * l->elem_bytes[s]) % kVecBytes) == 0;
+            if (ok) h = cand;
+        }
+        if (h >= 0 && h > numel[t]) h = (int)numel[t];
+        head[t] = h;
+        int64_t body = numel[t] - (h > 0 ? h : 0);
+        int64_t nchunks = body > 0 ? (body + chunk - 1) / chunk : 1;
+        if ((int64_t)prefix[t] + nchunks > 0x7fffffff) { set_error("tensor list too large"); *err = GM_ERR_BAD_SIZE; delete l; return nullptr; }
+        prefix[t + 1] = prefix[t] + (int)nchunks;
+    }
+
+    size_t off_ptrs = 0;
+    size_t off_numel = off_ptrs + sizeof(unsigned long long) * ns * nt;
+    size_t off_head = off_numel + sizeof(long long) * nt;
+    size_t off_prefix = off_head + sizeof(int) * nt;
+    size_t bytes = off_prefix + sizeof(int) * (nt + 1);
+    std::vector<unsigned char> host(bytes);
+    for (int s = 0; s < ns; ++s)
+        for (int t = 0; t < nt; ++t)
+            ((unsigned long long*)(host.data() + off_ptrs))[(size_t)s * nt + t] = (unsigned long long)sp[s][t];
+    for (int t = 0; t < nt; ++t) ((long long*)(host.data() + off_numel))[t] = numel[t];
+    memcpy(host.data() + off_head, head.data(), sizeof(int) * nt);
+    memcpy(host.data() + off_prefix, prefix.data(), sizeof(int) * (nt + 1));
+
+    {
+        DeviceGuard g(d);
+        cudaError_t e = cudaMalloc(&l->blob, round_up((int64_t)bytes, 256));
+        if (e == cudaSuccess) e = cudaMemcpy(l->blob, host.data(), bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { *err = cuda_fail(e, "tensor list upload"); cudaGetLastError(); if (l->blob) cudaFree(l->blob); delete l; return nullptr; }
+    }
+    unsigned char* b = (unsigned char*)l->blob;
+    l->dl.ptrs = (const unsigned long long*)(b + off_ptrs);
+    l->dl.numel = (const long long*)(b + off_numel);
+    l->dl.head = (const int*)(b + off_head);
+    l->dl.chunk_prefix = (const int*)(b + off_prefix);
+    l->dl.num_tensors = nt;
+    l->dl.num_chunks = prefix[nt];
+    l->dl.chunk_elems = chunk;
+    l->dl.num_streams = ns;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_lists.insert(l);
+    }
+    if (cache) {
+        std::lock_guard<std::mutex> lk(d->mu);
+        if (d->list_cache.size() >= 64) {       // bounded: drop everything, rebuild on demand
+            std::vector<TensorList*> old;
+            for (auto& kv : d->list_cache) old.push_back(kv.second);
+            d->list_cache.clear();
+            cudaStreamSynchronize(d->stream);
+            for (TensorList* o : old) free_list(o);
+        }
+        l->key = key;
+        d->list_cache[key] = l;
+    }
+    return l;
+}
+
+// ------------------------------------------------------------------
+// fp32 <-> fp16 conversion (bridge_memory.m:362-376)
+// ------------------------------------------------------------------
+__global__ void convert_f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __float2half_rn(src[i]);
+}
+
+__global__ void convert_f16_to_f32_kernel(const __half* __restrict__ src, float* __restrict__ dst, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __half2float(src[i]);
+}
+
+}  // namespace gm
+
+using namespace gm;
+
+// ======================================================================
+// C ABI
+// ======================================================================
+extern "C" {
+
+const char* gm_last_error(void) { return g_err; }
+const char* gm_version(void) { return "gometal_cuda 0.1 (sm_100a)"; }
+
+uintptr_t gm_device_create(int ordinal) { return (uintptr_t)make_device(ordinal); }
+
+uintptr_t create_cuda_device(void) {
+    int ordinal = 0;
+    const char* e = getenv("GOMETAL_CUDA_DEVICE");
+    if (!e || !*e) e = getenv("LOCAL_RANK");
+    if (e && *e) ordinal = atoi(e);
+    return (uintptr_t)make_device(ordinal);
+}
+
+void destroy_cuda_device(uintptr_t h) {
+    Device* d = as_device(h);
+    if (!d) return;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_devices.erase(d);
+    }
+    DeviceGuard g(d);
+    cudaStreamSynchronize(d->stream);
+    std::vector<TensorList*> lists;
+    for (auto& kv : d->list_cache) lists.push_back(kv.second);
+    d->list_cache.clear();
+    for (TensorList* l : lists) free_list(l);
+    if (d->partials) cudaFree(d->partials);
+    if (d->ticket) cudaFree(d->ticket);
+    if (d->scalars) cudaFree(d->scalars);
+    cudaEventDestroy(d->ev_start);
+    cudaEventDestroy(d->ev_stop);
+    cudaStreamDestroy(d->stream);
+    delete d;
+}
+
+uintptr_t create_command_queue(uintptr_t h) {
+    Device* d = as_device(h);
+    return d ? (uintptr_t)d->stream : 0;
+}
+
+void release_command_queue(uintptr_t) {}   // the stream belongs to the device handle
+
+int gm_device_ordinal(uintptr_t h) { Device* d = as_device(h); return d ? d->ordinal : GM_ERR_NIL_DEVICE; }
+int gm_device_sm_count(uintptr_t h) { Device* d = as_device(h); return d ? d->sm_count : GM_ERR_NIL_DEVICE; }
+uintptr_t gm_device_stream(uintptr_t h) { Device* d = as_device(h); return d ? (uintptr_t)d->stream : 0; }
+int64_t gm_device_launch_count(uintptr_t h) { Device* d = as_device(h); return d ? d->launches : -1; }
+
+int gm_device_synchronize(uintptr_t h) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    return GM_OK;
+}
+
+// ---- buffers ----
+uintptr_t gm_buffer_alloc(uintptr_t h, int64_t bytes) {
+    Device* d = as_device(h);
+    return d ? alloc_registered(d, bytes) : 0;
+}
+
+void gm_buffer_free(uintptr_t p) { free_registered(p); }
+int64_t gm_buffer_size(uintptr_t p) { return registered_size(p); }
+
+// bridge_memory.m:4-42: nil device or size<=0 gives 0; every storage mode maps
+// to device memory here.
+uintptr_t allocate_cuda_buffer(uintptr_t h, int size, int device_type) {
+    (void)device_type;
+    if (size <= 0) { set_error("allocation size %d is not positive", size); return 0; }
+    return gm_buffer_alloc(h, (int64_t)size);
+}
+
+void deallocate_cuda_buffer(uintptr_t p) { free_registered(p); }
+
+int gm_buffer_zero(uintptr_t h, uintptr_t p, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!p) { set_error("buffer is nil"); return GM_ERR_NIL_BUFFER; }
+    if (bytes <= 0) { set_error("size %lld is not positive", (long long)bytes); return GM_ERR_BAD_SIZE; }
+    int64_t have = registered_size(p);
+    if (have >= 0 && bytes > have) { set_error("zero of %lld bytes exceeds the %lld-byte buffer", (long long)bytes, (long long)have); return GM_ERR_BAD_SIZE; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaMemsetAsync((void*)p, 0, (size_t)bytes, d->stream));
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    return GM_OK;
+}
+
+int zero_cuda_buffer(uintptr_t h, uintptr_t p, int size) { return gm_buffer_zero(h, p, (int64_t)size); }
+
+static int copy_sync(uintptr_t p, void* host, int64_t bytes, bool to_device) {
+    if (!p) { set_error("buffer is nil"); return GM_ERR_NIL_BUFFER; }
+    if (!host) { set_error("host pointer is nil"); return GM_ERR_BAD_ARG; }
+    if (bytes <= 0) { set_error("size %lld is not positive", (long long)bytes); return GM_ERR_BAD_SIZE; }
+    int64_t have = registered_size(p);
+    if (have >= 0 && bytes > have) { set_error("copy of %lld bytes exceeds the %lld-byte buffer", (long long)bytes, (long long)have); return GM_ERR_BAD_SIZE; }
+    int ord = registered_ordinal(p);
+    int prev = -1;
+    if (ord >= 0) { cudaGetDevice(&prev); if (prev != ord) cudaSetDevice(ord); }
+    cudaError_t e = to_device ? cudaMemcpy((void*)p, host, (size_t)bytes, cudaMemcpyHostToDevice)
+                              : cudaMemcpy(host, (void*)p, (size_t)bytes, cudaMemcpyDeviceToHost);
+    if (ord >= 0 && prev != ord && prev >= 0) cudaSetDevice(prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy");
+    return GM_OK;
+}
+
+int copy_data_to_cuda_buffer(uintptr_t p, void* data, int size) { return copy_sync(p, data, size, true); }
+int copy_float32_array_to_cuda_buffer(uintptr_t p, float* data, int n) { return copy_sync(p, data, (int64_t)n * 4, true); }
+int copy_int32_array_to_cuda_buffer(uintptr_t p, int* data, int n) { return copy_sync(p, data, (int64_t)n * 4, true); }
+int copy_cuda_buffer_to_float32_array(uintptr_t p, float* data, int n) { return copy_sync(p, data, (int64_t)n * 4, false); }
+int copy_cuda_buffer_to_int32_array(uintptr_t p, int* data, int n) { return copy_sync(p, data, (int64_t)n * 4, false); }
+
+int gm_buffer_upload(uintptr_t h, uintptr_t p, const void* host, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    DeviceGuard g(d);
+    return copy_sync(p, const_cast<void*>(host), bytes, true);
+}
+
+int gm_buffer_download(uintptr_t h, uintptr_t p, void* host, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    return copy_sync(p, host, bytes, false);
+}
+
+int gm_buffer_upload_async(uintptr_t h, uintptr_t p, const void* host, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!p || !host || bytes <= 0) { set_error("bad async upload arguments"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaMemcpyAsync((void*)p, host, (size_t)bytes, cudaMemcpyHostToDevice, d->stream));
+    return GM_OK;
+}
+
+int gm_buffer_download_async(uintptr_t h, uintptr_t p, void* host, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!p || !host || bytes <= 0) { set_error("bad async download arguments"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaMemcpyAsync(host, (void*)p, (size_t)bytes, cudaMemcpyDeviceToHost, d->stream));
+    return GM_OK;
+}
+
+void* gm_host_alloc_pinned(int64_t bytes) {
+    void* p = nullptr;
+    if (bytes <= 0) return nullptr;
+    cudaError_t e = cudaMallocHost(&p, (size_t)bytes);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMallocHost"); cudaGetLastError(); return nullptr; }
+    return p;
+}
+
+void gm_host_free_pinned(void* p) { if (p) cudaFreeHost(p); }
+
+// ---- arenas ----
+// The arena's own allocation stays out of the buffer registry; only the
+// sub-buffers handed out are registered (as not separately freeable).
+uintptr_t gm_arena_create(uintptr_t h, int64_t bytes) {
+    Device* d = as_device(h);
+    if (!d) return 0;
+    if (bytes <= 0) { set_error("arena size %lld is not positive", (long long)bytes); return 0; }
+    DeviceGuard g(d);
+    void* p = nullptr;
+    int64_t cap = round_up(bytes, 256);
+    cudaError_t e = cudaMalloc(&p, (size_t)cap);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(arena)"); cudaGetLastError(); return 0; }
+    Arena* a = new Arena();
+    a->base = (uintptr_t)p; a->cap = cap; a->used = 0; a->ordinal = d->ordinal;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_arenas.insert(a);
+    return (uintptr_t)a;
+}
+
+uintptr_t gm_arena_alloc(uintptr_t h, int64_t bytes) {
+    Arena* a = as_arena(h);
+    if (!a) { set_error("not a live arena"); return 0; }
+    if (bytes <= 0) { set_error("allocation size %lld is not positive", (long long)bytes); return 0; }
+    int64_t need = round_up(bytes, 256);
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (a->used + need > a->cap) { set_error("arena full: %lld of %lld bytes used, %lld requested", (long long)a->used, (long long)a->cap, (long long)bytes); return 0; }
+    uintptr_t p = a->base + (uintptr_t)a->used;
+    a->used += need;
+    g_bufs[p] = BufInfo{bytes, a->ordinal, false};
+    return p;
+}
+
+uintptr_t gm_arena_base(uintptr_t h) { Arena* a = as_arena(h); return a ? a->base : 0; }
+int64_t gm_arena_capacity(uintptr_t h) { Arena* a = as_arena(h); return a ? a->cap : -1; }
+int64_t gm_arena_used(uintptr_t h) { Arena* a = as_arena(h); return a ? a->used : -1; }
+
+static void arena_forget_subbuffers(Arena* a) {     // g_mu held
+    for (auto it = g_bufs.begin(); it != g_bufs.end();) {
+        bool inside = !it->second.owned && it->first >= a->base && it->first < a->base + (uintptr_t)a->cap;
+        if (inside) it = g_bufs.erase(it); else ++it;
+    }
+}
+
+void gm_arena_reset(uintptr_t h) {
+    Arena* a = as_arena(h);
+    if (!a) return;
+    std::lock_guard<std::mutex> lk(g_mu);
+    arena_forget_subbuffers(a);
+    a->used = 0;
+}
+
+void gm_arena_destroy(uintptr_t h) {
+    Arena* a = as_arena(h);
+    if (!a) return;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_arenas.erase(a);
+        arena_forget_subbuffers(a);
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != a->ordinal) cudaSetDevice(a->ordinal);
+    cudaFree((void*)a->base);
+    if (prev != a->ordinal && prev >= 0) cudaSetDevice(prev);
+    delete a;
+}
+
+// ---- conversion ----
+int convert_tensor_type_cuda(uintptr_t src, uintptr_t dst, int* shape, int nd, int src_t, int dst_t, uintptr_t h) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!src || !dst) { set_error("source or destination buffer is nil"); return GM_ERR_NIL_BUFFER; }
+    if (!shape || nd <= 0) { set_error("shape is empty"); return GM_ERR_BAD_ARG; }
+    long long n = 1;
+    for (int i = 0; i < nd; ++i) {
+        if (shape[i] <= 0) { set_error("shape[%d]=%d is not positive", i, shape[i]); return GM_ERR_BAD_SIZE; }
+        n *= shape[i];
+    }
+    const int F32 = 0, F16 = 2;
+    DeviceGuard g(d);
+    int blocks = (int)((n + 255) / 256);
+    int cap = d->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (src_t == F32 && dst_t == F16) {
+        convert_f32_to_f16_kernel<<<blocks, 256, 0, d->stream>>>((const float*)src, (__half*)dst, n);
+    } else if (src_t == F16 && dst_t == F32) {
+        convert_f16_to_f32_kernel<<<blocks, 256, 0, d->stream>>>((const __half*)src, (float*)dst, n);
+    } else {
+        set_error("conversion %d -> %d is not supported (only Float32<->Float16)", src_t, dst_t);
+        return GM_ERR_UNSUPPORTED;
+    }
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    return GM_OK;
+}
+
+// ---- tensor lists ----
+uintptr_t gm_tensor_list_create(uintptr_t h, int ns, int nt, const uintptr_t* const* sp,
+                                const int64_t* numel, const int* elem_bytes) {
+    Device* d = as_device(h);
+    if (!d) return 0;
+    if (!sp || !numel) { set_error("pointer or size array is nil"); return 0; }
+    int err = 0;
+    return (uintptr_t)build_list(d, ns, nt, sp, numel, elem_bytes, false, &err);
+}
+
+void gm_tensor_list_destroy(uintptr_t h) {
+    TensorList* l = as_list(h);
+    if (!l || l->key != 0) return;      // cached lists belong to the device
+    free_list(l);
+}
+
+int64_t gm_tensor_list_total(uintptr_t h) { TensorList* l = as_list(h); return l ? l->total : -1; }
+int gm_tensor_list_num_chunks(uintptr_t h) { TensorList* l = as_list(h); return l ? l->dl.num_chunks : -1; }
+
+}  // extern "C"

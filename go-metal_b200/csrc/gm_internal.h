@@ -1,0 +1,110 @@
+// gm_internal.h -- shared host-side structures of libgometal_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "gometal_cuda.h"
+
+namespace gm {
+
+constexpr int kMaxStreams = 5;          // pointer arrays one rule can walk
+constexpr int kApplyThreads = 256;      // CTA width of the apply kernels
+constexpr int kVecBytes = 16;           // 128-bit accesses
+constexpr int kMagicDevice = 0x474d4456;   // "GMDV"
+constexpr int kMagicList = 0x474d544c;     // "GMTL"
+
+// Descriptor a multi-tensor kernel receives by value.  All arrays live in one
+// device allocation owned by the TensorList.
+struct DevList {
+    const unsigned long long* ptrs;   // [num_streams][num_tensors] device addresses
+    const long long* numel;           // [num_tensors]
+    const int* head;                  // [num_tensors] scalar elements before the 16-B aligned body; -1 = no aligned body
+    const int* chunk_prefix;          // [num_tensors+1] first chunk of each tensor
+    int num_tensors;
+    int num_chunks;
+    int chunk_elems;                  // elements per chunk (multiple of the vector tile)
+    int num_streams;
+};
+
+struct Device;
+
+struct TensorList {
+    int magic = kMagicList;
+    Device* dev = nullptr;
+    DevList dl{};
+    void* blob = nullptr;             // device allocation behind dl
+    int64_t total = 0;
+    int elem_bytes[kMaxStreams] = {4, 4, 4, 4, 4};
+    std::vector<int64_t> numel;       // host copy
+    std::vector<std::vector<uintptr_t>> ptrs;   // host copy [stream][tensor]
+    uint64_t key = 0;                 // cache key (0 = not cached)
+};
+
+struct Device {
+    int magic = kMagicDevice;
+    int ordinal = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    std::mutex mu;
+    std::unordered_map<uint64_t, TensorList*> list_cache;
+    int64_t launches = 0;
+    int lbfgs_mode = 1;
+    // scratch for reductions (dot partials, tickets); grown on demand
+    float* partials = nullptr;
+    int64_t partials_cap = 0;
+    unsigned int* ticket = nullptr;     // one counter for last-CTA-done finishes
+    float* scalars = nullptr;           // small device scratch for L-BFGS scalars
+};
+
+// ---- error reporting ----
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);   // records and returns GM_ERR_CUDA
+
+#define GM_CUDA_CHECK(call)                                              \
+    do {                                                                  \
+        cudaError_t e__ = (call);                                         \
+        if (e__ != cudaSuccess) return ::gm::cuda_fail(e__, #call);       \
+    } while (0)
+
+Device* as_device(uintptr_t h);        // nullptr (and error text) if not a live device
+TensorList* as_list(uintptr_t h);
+
+// RAII: make the device's ordinal current for the scope.
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(const Device* d) {
+        cudaGetDevice(&prev);
+        if (prev != d->ordinal) cudaSetDevice(d->ordinal);
+        else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// ---- tensor lists ----
+// Builds (or fetches from the device's cache when `cache` is set) the
+// descriptor for the given pointer arrays.  Returns nullptr on failure.
+TensorList* build_list(Device* d, int num_streams, int num_tensors,
+                       const uintptr_t* const* stream_ptrs, const int64_t* numel,
+                       const int* elem_bytes, bool cache, int* err);
+void free_list(TensorList* l);
+
+// Grid size for a persistent kernel: resident CTAs x SMs, capped by the work.
+int persistent_grid(Device* d, const void* kernel, int threads, int64_t work_items);
+
+int ensure_partials(Device* d, int64_t count);
+
+// ---- rule launchers (gm_rules.cu) ----
+int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h);
+
+// ---- buffer registry (gm_device.cu) ----
+int64_t registered_size(uintptr_t p);   // -1 if unknown
+int registered_ordinal(uintptr_t p);    // -1 if unknown
+
+}  // namespace gm

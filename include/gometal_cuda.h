@@ -1,0 +1,267 @@
+/*
+ * gometal_cuda.h -- C ABI of libgometal_cuda.so, the CUDA (sm_100a) replacement
+ * for go-metal's optimizer-step bridge.
+ *
+ * Part 1 mirrors, entry for entry, what the reference's cgo layer binds for
+ * this path (cgo_bridge/bridge_optimizer.h, cgo_bridge/bridge_memory.h and the
+ * device/queue calls of cgo_bridge/bridge.go).  Argument order, C types and the
+ * int return convention (0 = ok, negative = failure class) are unchanged; only
+ * the `_mpsgraph` / `metal` part of each name became `_cuda` / `cuda`, so a Go
+ * wrapper changes its symbol and nothing else.  Every pointer is borrowed for
+ * the duration of the call; host arrays are copied, never retained.  These
+ * entries are synchronous: results are in the buffers when they return.
+ *
+ * Part 2 holds entries that have no counterpart in the reference (64-bit
+ * sizes, persistent tensor lists, asynchronous steps, mixed precision with a
+ * device-resident loss scale, grad-norm, ZeRO-1 sharding, timing).
+ *
+ * All buffers are device pointers (cudaMalloc or any CUDA allocation on the
+ * device's ordinal).  No entry falls back to the CPU.
+ */
+#ifndef GOMETAL_CUDA_H
+#define GOMETAL_CUDA_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes.  -1..-8 keep the reference's meaning where one exists
+ * (cgo_bridge/bridge_optimizer.m:174-193, 377-394, 413, 630, 638). */
+#define GM_OK                 0
+#define GM_ERR_NIL_DEVICE    -1   /* device handle is 0 */
+#define GM_ERR_NIL_BUFFER    -4   /* a required buffer pointer is 0 */
+#define GM_ERR_AUX_BUFFER    -5   /* momentum>0 / centered without its buffer */
+#define GM_ERR_CUDA          -8   /* a CUDA call failed; see gm_last_error() */
+#define GM_ERR_BAD_SIZE      -9   /* size <= 0, not a multiple of the element, or too small */
+#define GM_ERR_BAD_ARG      -10   /* any other invalid argument */
+#define GM_ERR_UNSUPPORTED  -11   /* valid call that this build cannot serve (e.g. NCCL missing) */
+#define GM_ERR_TIMEOUT      -12   /* a bounded device-side wait ran out */
+
+/* ===================================================================== */
+/* Part 1 -- drop-in entries                                              */
+/* ===================================================================== */
+
+/* ---- device and queue: cgo_bridge/bridge.go:632-645 (CreateMetalDevice,
+ * DestroyMetalDevice), :1676-1695 (CreateCommandQueue, ReleaseCommandQueue) */
+uintptr_t create_cuda_device(void);              /* ordinal from GOMETAL_CUDA_DEVICE or LOCAL_RANK, else 0 */
+void destroy_cuda_device(uintptr_t device_ptr);
+uintptr_t create_command_queue(uintptr_t device_ptr);   /* returns the device's stream handle */
+void release_command_queue(uintptr_t command_queue);
+
+/* ---- buffers: cgo_bridge/bridge_memory.h:6-26 ---- */
+uintptr_t allocate_cuda_buffer(uintptr_t device_ptr, int size, int device_type);
+void deallocate_cuda_buffer(uintptr_t buffer_ptr);
+int zero_cuda_buffer(uintptr_t device_ptr, uintptr_t buffer_ptr, int size);
+int copy_data_to_cuda_buffer(uintptr_t buffer_ptr, void* data, int size);
+int copy_float32_array_to_cuda_buffer(uintptr_t buffer_ptr, float* data, int num_elements);
+int copy_int32_array_to_cuda_buffer(uintptr_t buffer_ptr, int* data, int num_elements);
+int copy_cuda_buffer_to_float32_array(uintptr_t buffer_ptr, float* data, int num_elements);
+int copy_cuda_buffer_to_int32_array(uintptr_t buffer_ptr, int* data, int num_elements);
+/* dtype codes follow memory/tensor.go:12-17: 0 Float32, 1 Int32, 2 Float16, 3 Int8.
+ * Only Float32<->Float16 is implemented, as in bridge_memory.m:323-423. */
+int convert_tensor_type_cuda(uintptr_t src_buffer_ptr, uintptr_t dst_buffer_ptr,
+                             int* shape, int num_dims, int src_type, int dst_type,
+                             uintptr_t device_ptr);
+
+/* ---- SGD: cgo_bridge/bridge_optimizer.h:11-23 ---- */
+int execute_sgd_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                          uintptr_t* gradient_buffers, uintptr_t* momentum_buffers,
+                          int num_weights, int* buffer_sizes, float learning_rate,
+                          float momentum, float weight_decay, int nesterov, int step_count);
+
+/* ---- Adam: cgo_bridge/bridge_optimizer.h:26-40 and :58-73 (pooled) ---- */
+int execute_adam_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                           uintptr_t* gradient_buffers, uintptr_t* momentum_buffers,
+                           uintptr_t* variance_buffers, int num_weights, int* buffer_sizes,
+                           float learning_rate, float beta1, float beta2, float epsilon,
+                           float weight_decay, int step_count);
+int execute_adam_step_cuda_pooled(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                                  uintptr_t* gradient_buffers, uintptr_t* momentum_buffers,
+                                  uintptr_t* variance_buffers, int num_weights, int* buffer_sizes,
+                                  float learning_rate, float beta1, float beta2, float epsilon,
+                                  float weight_decay, int step_count, uintptr_t command_pool);
+
+/* ---- RMSProp: cgo_bridge/bridge_optimizer.h:76-92 ----
+ * Unlike the reference (bridge_optimizer.m:915-937) the new momentum and
+ * gradient-average values are stored, so momentum>0 and centered work. */
+int execute_rmsprop_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                              uintptr_t* gradient_buffers, uintptr_t* squared_grad_avg_buffers,
+                              uintptr_t* momentum_buffers, uintptr_t* gradient_avg_buffers,
+                              int num_weights, int* buffer_sizes, float learning_rate,
+                              float alpha, float epsilon, float weight_decay, float momentum,
+                              bool centered, int step_count);
+
+/* ---- AdaGrad: cgo_bridge/bridge_optimizer.h:97-120 ---- */
+int execute_adagrad_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                              uintptr_t* gradient_buffers, uintptr_t* squared_grad_avg_buffers,
+                              int num_weights, int* buffer_sizes, float learning_rate,
+                              float epsilon, float weight_decay);
+int execute_adagrad_step_cuda_pooled(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                                     uintptr_t* gradient_buffers,
+                                     uintptr_t* squared_grad_avg_buffers, int num_weights,
+                                     int* buffer_sizes, float learning_rate, float epsilon,
+                                     float weight_decay, uintptr_t command_pool);
+
+/* ---- AdaDelta: cgo_bridge/bridge_optimizer.h:125-150 ---- */
+int execute_adadelta_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                               uintptr_t* gradient_buffers, uintptr_t* squared_grad_avg_buffers,
+                               uintptr_t* squared_update_avg_buffers, int num_weights,
+                               int* buffer_sizes, float rho, float epsilon, float weight_decay);
+int execute_adadelta_step_cuda_pooled(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                                      uintptr_t* gradient_buffers,
+                                      uintptr_t* squared_grad_avg_buffers,
+                                      uintptr_t* squared_update_avg_buffers, int num_weights,
+                                      int* buffer_sizes, float rho, float epsilon,
+                                      float weight_decay, uintptr_t command_pool);
+
+/* ---- NAdam: cgo_bridge/bridge_optimizer.h:207-221 ---- */
+int execute_nadam_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                            uintptr_t* gradient_buffers, uintptr_t* momentum_buffers,
+                            uintptr_t* variance_buffers, int num_weights, int* buffer_sizes,
+                            float learning_rate, float beta1, float beta2, float epsilon,
+                            float weight_decay, int step_count);
+
+/* ---- L-BFGS: cgo_bridge/bridge_optimizer.h:155-202 ----
+ * s_vectors_flat / y_vectors_flat are history_size*num_weights pointers laid
+ * out [slot*num_weights + tensor] (cgo_bridge/bridge.go:1987-1998);
+ * rho_buffers are history_size device buffers of one float; alpha_buffer holds
+ * history_size floats.  Uses the corrected curvature pair by default; see
+ * gm_lbfgs_set_mode(). */
+int execute_lbfgs_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                            uintptr_t* gradient_buffers, uintptr_t* old_gradient_buffers,
+                            uintptr_t* search_dir_buffers, uintptr_t* s_vectors_flat,
+                            uintptr_t* y_vectors_flat, uintptr_t* rho_buffers,
+                            uintptr_t alpha_buffer, int num_weights, int* buffer_sizes,
+                            int history_size, int history_count, int history_index,
+                            float initial_step, float c1, float c2, int max_line_search,
+                            float current_loss, float prev_loss, float* step_size);
+int execute_lbfgs_step_cuda_pooled(uintptr_t device_ptr, uintptr_t* weight_buffers,
+                                   uintptr_t* gradient_buffers, uintptr_t* old_gradient_buffers,
+                                   uintptr_t* search_dir_buffers, uintptr_t* s_vectors_flat,
+                                   uintptr_t* y_vectors_flat, uintptr_t* rho_buffers,
+                                   uintptr_t alpha_buffer, int num_weights, int* buffer_sizes,
+                                   int history_size, int history_count, int history_index,
+                                   float initial_step, float c1, float c2, int max_line_search,
+                                   float current_loss, float prev_loss, uintptr_t command_pool,
+                                   float* step_size);
+
+/* ===================================================================== */
+/* Part 2 -- entries with no counterpart in the reference                 */
+/* ===================================================================== */
+
+/* ---- diagnostics ---- */
+const char* gm_last_error(void);                 /* thread-local text of the last failure */
+const char* gm_version(void);
+uintptr_t gm_device_create(int ordinal);         /* explicit ordinal */
+int gm_device_ordinal(uintptr_t device_ptr);
+int gm_device_sm_count(uintptr_t device_ptr);
+uintptr_t gm_device_stream(uintptr_t device_ptr);/* cudaStream_t the device launches on */
+int gm_device_synchronize(uintptr_t device_ptr);
+/* Number of kernels this library has launched on the device so far. */
+int64_t gm_device_launch_count(uintptr_t device_ptr);
+
+/* ---- 64-bit buffers and arenas (the reference's `int` sizes stop at 2 GiB) ----
+ * An arena is one cudaMalloc carved into 256-byte-aligned sub-buffers. */
+uintptr_t gm_buffer_alloc(uintptr_t device_ptr, int64_t bytes);
+void gm_buffer_free(uintptr_t buffer_ptr);
+int64_t gm_buffer_size(uintptr_t buffer_ptr);    /* bytes reserved, -1 if unknown to the library */
+int gm_buffer_zero(uintptr_t device_ptr, uintptr_t buffer_ptr, int64_t bytes);
+int gm_buffer_upload(uintptr_t device_ptr, uintptr_t buffer_ptr, const void* host, int64_t bytes);
+int gm_buffer_download(uintptr_t device_ptr, uintptr_t buffer_ptr, void* host, int64_t bytes);
+uintptr_t gm_arena_create(uintptr_t device_ptr, int64_t bytes);
+uintptr_t gm_arena_alloc(uintptr_t arena, int64_t bytes);   /* 0 when the arena is full */
+uintptr_t gm_arena_base(uintptr_t arena);
+int64_t gm_arena_capacity(uintptr_t arena);
+int64_t gm_arena_used(uintptr_t arena);
+void gm_arena_reset(uintptr_t arena);
+void gm_arena_destroy(uintptr_t arena);
+/* Pinned host staging memory for callers that overlap copies with steps. */
+void* gm_host_alloc_pinned(int64_t bytes);
+void gm_host_free_pinned(void* p);
+int gm_buffer_upload_async(uintptr_t device_ptr, uintptr_t buffer_ptr, const void* host, int64_t bytes);
+int gm_buffer_download_async(uintptr_t device_ptr, uintptr_t buffer_ptr, void* host, int64_t bytes);
+
+/* ---- persistent tensor lists ----
+ * A tensor list is the device-resident descriptor one multi-tensor launch
+ * walks: `num_streams` pointer arrays of `num_tensors` entries plus element
+ * counts.  The drop-in entries build and cache one implicitly. */
+uintptr_t gm_tensor_list_create(uintptr_t device_ptr, int num_streams, int num_tensors,
+                                const uintptr_t* const* stream_ptrs, const int64_t* numel,
+                                const int* elem_bytes /* per stream: 4 or 2 */);
+void gm_tensor_list_destroy(uintptr_t list);
+int64_t gm_tensor_list_total(uintptr_t list);
+int gm_tensor_list_num_chunks(uintptr_t list);
+
+/* Optimizer rule selector for gm_step_async(). */
+enum {
+    GM_RULE_SGD = 0,        /* streams: w,g[,mom]            scalars: lr, momentum, wd, nesterov */
+    GM_RULE_ADAM = 1,       /* streams: w,g,m,v              scalars: lr, beta1, beta2, eps, wd */
+    GM_RULE_RMSPROP = 2,    /* streams: w,g,sq[,mom][,gavg]  scalars: lr, alpha, eps, wd, momentum, centered */
+    GM_RULE_ADAGRAD = 3,    /* streams: w,g,sq               scalars: lr, eps, wd */
+    GM_RULE_ADADELTA = 4,   /* streams: w,g,sq,upd           scalars: rho, eps, wd */
+    GM_RULE_NADAM = 5       /* streams: w,g,m,v              scalars: lr, beta1, beta2, eps, wd */
+};
+
+typedef struct {
+    float lr, beta1, beta2, eps, weight_decay;   /* beta1 doubles as momentum / alpha / rho */
+    float momentum;                              /* RMSProp momentum */
+    int nesterov, centered;
+    int step;                                    /* 1-based, already incremented by the caller */
+} gm_hyper_t;
+
+/* Enqueue one step on the device's stream and return without waiting. */
+int gm_step_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper);
+/* Same, timed with CUDA events on the launching stream; waits for completion. */
+int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
+                  float* elapsed_ms);
+
+/* ---- mixed-precision Adam with a device-resident dynamic loss scale ---- */
+typedef struct {
+    float scale, growth, backoff, max_scale;
+    int32_t interval, good_steps, adam_t, skipped, last_overflow;
+} gm_loss_scale_t;
+
+/* list streams: g16 (2 B), master, m, v (4 B), p16 (2 B). */
+uintptr_t gm_mixed_create(uintptr_t device_ptr, const gm_loss_scale_t* initial,
+                          float beta1, float beta2, int table_steps);
+void gm_mixed_destroy(uintptr_t mixed);
+int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list,
+                        float lr, float eps, float weight_decay);
+int gm_mixed_get_state(uintptr_t device_ptr, uintptr_t mixed, gm_loss_scale_t* out);   /* waits */
+int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scale_t* in);
+uintptr_t gm_mixed_state_device_ptr(uintptr_t mixed);   /* device address of the gm_loss_scale_t */
+
+/* ---- gradient norm (sum of squares; one float atomic per CTA) ---- */
+/* list stream 0 is the gradient (4 B or 2 B elements).  *out_sumsq is a
+ * device float the kernel accumulates into after zeroing it. */
+int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, float inv_scale,
+                        uintptr_t out_sumsq_device);
+
+/* ---- L-BFGS controls ---- */
+/* mode 0: statement order of the reference (curvature pairs are always
+ * rejected because y is formed after old_g is overwritten);
+ * mode 1 (default): y is formed from the previous gradient first. */
+int gm_lbfgs_set_mode(uintptr_t device_ptr, int mode);
+int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, float* out);
+
+/* ---- ZeRO-1: sharded state + all-gather of updated parameters ---- */
+#define GM_NCCL_UNIQUE_ID_BYTES 128
+int gm_zero1_unique_id(void* out_id /* 128 bytes */);
+uintptr_t gm_zero1_create(uintptr_t device_ptr, const void* unique_id, int rank, int world);
+void gm_zero1_destroy(uintptr_t zero1);
+/* In-place all-gather: every rank holds the whole arena; rank r has just
+ * updated elements [r*count, (r+1)*count). */
+int gm_zero1_allgather_async(uintptr_t zero1, uintptr_t arena_base, int64_t count_per_rank,
+                             int elem_bytes);
+/* Update of this rank's shard, then the all-gather, on one stream. */
+int gm_zero1_adam_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper,
+                             uintptr_t arena_base, int64_t count_per_rank);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GOMETAL_CUDA_H */

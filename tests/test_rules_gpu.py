@@ -1,0 +1,288 @@
+"""GPU parity of the six elementwise rules against the CPU oracle, called
+through the drop-in C entries (execute_*_step_cuda).
+
+Tolerance: the north-star bound is 2 ulp per step and 1e-5 relative after 100
+steps.  The kernels use the same IEEE operations in the same order as the
+oracle, so the tests first demand bit equality and report the ulp distance if
+that ever fails.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+MAX_ULP = 2
+REL_TOL = 1e-5
+
+
+class DeviceSet:
+    """One device buffer per tensor, allocated through allocate_cuda_buffer."""
+
+    def __init__(self, gm, dev, arrays):
+        self.gm, self.dev = gm, dev
+        self.n = [a.size for a in arrays]
+        self.ptrs = []
+        for a in arrays:
+            p = gm.lib.allocate_cuda_buffer(dev.h, a.size * 4, 1)
+            assert p, gm.last_error()
+            gm.check(gm.lib.copy_float32_array_to_cuda_buffer(p, a.ctypes.data, a.size), "upload")
+            self.ptrs.append(p)
+
+    def upload(self, arrays):
+        for p, a in zip(self.ptrs, arrays):
+            self.gm.check(self.gm.lib.copy_float32_array_to_cuda_buffer(p, a.ctypes.data, a.size), "upload")
+
+    def download(self):
+        out = []
+        for p, n in zip(self.ptrs, self.n):
+            a = np.empty(n, dtype=np.float32)
+            self.gm.check(self.gm.lib.copy_cuda_buffer_to_float32_array(p, a.ctypes.data, n), "download")
+            out.append(a)
+        return out
+
+    def array(self):
+        return self.gm.uarray(self.ptrs)
+
+    def free(self):
+        for p in self.ptrs:
+            self.gm.lib.deallocate_cuda_buffer(p)
+
+
+def zeros_like(ws):
+    return [np.zeros_like(w) for w in ws]
+
+
+def assert_close(name, step, got, want):
+    for t, (a, b) in enumerate(zip(got, want)):
+        if np.array_equal(a.view(np.uint32), b.view(np.uint32)):
+            continue
+        finite = np.isfinite(a) & np.isfinite(b)
+        assert np.array_equal(np.isfinite(a), np.isfinite(b)), f"{name} step {step} tensor {t}: finiteness differs"
+        ulp = W.ulp_distance(a[finite], b[finite])
+        assert ulp.max() <= MAX_ULP, f"{name} step {step} tensor {t}: {ulp.max()} ulp apart (limit {MAX_ULP})"
+
+
+def assert_rel(name, got, want):
+    for t, (a, b) in enumerate(zip(got, want)):
+        denom = np.maximum(np.abs(b), np.float32(1e-30))
+        rel = np.abs(a.astype(np.float64) - b.astype(np.float64)) / denom
+        # entries at zero are compared absolutely
+        rel = np.where(np.abs(b) < 1e-30, np.abs(a), rel)
+        assert rel.max() <= REL_TOL, f"{name} tensor {t}: relative error {rel.max():.3e} > {REL_TOL}"
+
+
+def run_rule(gm, dev, O, name, shapes, fan_in, steps, heavy_tail, state_count, gpu_step, cpu_step):
+    w_cpu = W.he_uniform_weights(O, shapes, fan_in)
+    states_cpu = [zeros_like(w_cpu) for _ in range(state_count)]
+    w_gpu = DeviceSet(gm, dev, w_cpu)
+    g_gpu = DeviceSet(gm, dev, zeros_like(w_cpu))
+    states_gpu = [DeviceSet(gm, dev, s) for s in states_cpu]
+    sizes = gm.iarray([a.size * 4 for a in w_cpu])
+    exact = True
+    try:
+        for step in range(1, steps + 1):
+            grads = W.normal_grads(O, shapes, step, 0.01, heavy_tail)
+            g_gpu.upload(grads)
+            rc = gpu_step(w_gpu.array(), g_gpu.array(), [s.array() for s in states_gpu], len(shapes), sizes, step)
+            assert rc == 0, f"{name} step {step}: code {rc}: {gm.last_error()}"
+            for t in range(len(shapes)):
+                cpu_step(w_cpu[t], grads[t], [s[t] for s in states_cpu], step)
+            if step <= 3 or step % 10 == 0 or step == steps:
+                got_w = w_gpu.download()
+                assert_close(name + ".w", step, got_w, w_cpu)
+                for k, s in enumerate(states_gpu):
+                    assert_close(f"{name}.state{k}", step, s.download(), states_cpu[k])
+                exact = exact and all(np.array_equal(a.view(np.uint32), b.view(np.uint32)) for a, b in zip(got_w, w_cpu))
+        assert_rel(name + ".w", w_gpu.download(), w_cpu)
+        for k, s in enumerate(states_gpu):
+            assert_rel(f"{name}.state{k}", s.download(), states_cpu[k])
+    finally:
+        for s in [w_gpu, g_gpu] + states_gpu:
+            s.free()
+    return exact
+
+
+def test_adam_mlp_100_steps(gm, dev, oracle):
+    """fp32 Adam, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, no decay, MLP 784-128-10, 100 steps."""
+    O = oracle
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.999, 1e-8, 0.0
+
+    def gpu(w, g, st, n, sizes, step):
+        return gm.lib.execute_adam_step_cuda(dev.h, w, g, st[0], st[1], n, sizes, lr, b1, b2, eps, wd, step)
+
+    def cpu(w, g, st, step):
+        O.adam_step(w, g, st[0], st[1], lr, b1, b2, eps, wd, step)
+
+    exact = run_rule(gm, dev, O, "adam", W.MLP_SHAPES, W.MLP_FAN_IN, 100, False, 2, gpu, cpu)
+    assert exact, "Adam is expected to be bit-identical to the oracle"
+
+
+CNN_CASES = {
+    "sgd_momentum": 1, "sgd_nesterov": 1, "rmsprop": 1, "adagrad": 1, "adadelta": 2, "nadam": 2,
+    "adam_decay": 2,
+}
+
+
+@pytest.mark.parametrize("case", list(CNN_CASES))
+def test_cnn_rules_100_steps(gm, dev, oracle, case):
+    """SGD-momentum, RMSProp, AdaGrad, AdaDelta, NAdam on the 8 CNN tensors with
+    heavy-tailed gradients (1 % of entries x100), 100 steps.  Learning rates the
+    configuration leaves open use the reference defaults (sgd.go:48-55 0.01,
+    rmsprop.go:54-63 0.01, adagrad.go:42-48 0.01, nadam.go:47-55 0.002)."""
+    O = oracle
+    L = gm.lib
+
+    if case in ("sgd_momentum", "sgd_nesterov"):
+        nest = 1 if case == "sgd_nesterov" else 0
+        wd = 1e-4 if nest else 0.0
+        gpu = lambda w, g, st, n, sz, step: L.execute_sgd_step_cuda(dev.h, w, g, st[0], n, sz, 0.01, 0.9, wd, nest, step)
+        cpu = lambda w, g, st, step: O.sgd_step(w, g, st[0], 0.01, 0.9, wd, nest)
+    elif case == "rmsprop":
+        gpu = lambda w, g, st, n, sz, step: L.execute_rmsprop_step_cuda(dev.h, w, g, st[0], None, None, n, sz, 0.01, 0.99, 1e-8, 0.0, 0.0, False, step)
+        cpu = lambda w, g, st, step: O.rmsprop_step(w, g, st[0], None, None, 0.01, 0.99, 1e-8, 0.0, 0.0, False)
+    elif case == "adagrad":
+        gpu = lambda w, g, st, n, sz, step: L.execute_adagrad_step_cuda(dev.h, w, g, st[0], n, sz, 0.01, 1e-10, 0.0)
+        cpu = lambda w, g, st, step: O.adagrad_step(w, g, st[0], 0.01, 1e-10, 0.0)
+    elif case == "adadelta":
+        gpu = lambda w, g, st, n, sz, step: L.execute_adadelta_step_cuda(dev.h, w, g, st[0], st[1], n, sz, 0.9, 1e-6, 0.0)
+        cpu = lambda w, g, st, step: O.adadelta_step(w, g, st[0], st[1], 0.9, 1e-6, 0.0)
+    elif case == "nadam":
+        gpu = lambda w, g, st, n, sz, step: L.execute_nadam_step_cuda(dev.h, w, g, st[0], st[1], n, sz, 0.002, 0.9, 0.999, 1e-8, 0.0, step)
+        cpu = lambda w, g, st, step: O.nadam_step(w, g, st[0], st[1], 0.002, 0.9, 0.999, 1e-8, 0.0, step)
+    else:   # Adam with weight decay: exercises the decay branch
+        gpu = lambda w, g, st, n, sz, step: L.execute_adam_step_cuda_pooled(dev.h, w, g, st[0], st[1], n, sz, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0)
+        cpu = lambda w, g, st, step: O.adam_step(w, g, st[0], st[1], 1e-3, 0.9, 0.999, 1e-8, 0.01, step)
+
+    exact = run_rule(gm, dev, O, case, W.CNN_SHAPES, W.CNN_FAN_IN, 100, True, CNN_CASES[case], gpu, cpu)
+    assert exact, f"{case} is expected to be bit-identical to the oracle"
+
+
+@pytest.mark.parametrize("mode", ["plain", "momentum", "centered", "both"])
+def test_rmsprop_modes(gm, dev, oracle, mode):
+    """RMSProp with momentum and/or centering keeps its extra state between steps."""
+    O = oracle
+    mom = 0.9 if mode in ("momentum", "both") else 0.0
+    cen = mode in ("centered", "both")
+    shapes, fan = [(1000,), (37,), (4099,)], [10, 10, 10]
+    nstate = 1 + (1 if mom > 0 else 0) + (1 if cen else 0)
+
+    def gpu(w, g, st, n, sz, step):
+        k = 1
+        mb = gb = None
+        if mom > 0:
+            mb = st[k]; k += 1
+        if cen:
+            gb = st[k]
+        return gm.lib.execute_rmsprop_step_cuda(dev.h, w, g, st[0], mb, gb, n, sz, 0.01, 0.99, 1e-8, 1e-3, mom, cen, step)
+
+    def cpu(w, g, st, step):
+        k = 1
+        mb = gb = None
+        if mom > 0:
+            mb = st[k]; k += 1
+        if cen:
+            gb = st[k]
+        O.rmsprop_step(w, g, st[0], mb, gb, 0.01, 0.99, 1e-8, 1e-3, mom, cen, True)
+
+    assert run_rule(gm, dev, O, "rmsprop-" + mode, shapes, fan, 20, True, nstate, gpu, cpu)
+
+
+def test_plain_sgd_and_small_sizes(gm, dev, oracle):
+    """Vanilla SGD (no momentum buffers) on every size from 1 to 130 elements."""
+    O = oracle
+    shapes = [(n,) for n in range(1, 131)]
+    fan = [4] * len(shapes)
+
+    def gpu(w, g, st, n, sz, step):
+        return gm.lib.execute_sgd_step_cuda(dev.h, w, g, None, n, sz, 0.05, 0.0, 0.0, 0, step)
+
+    def cpu(w, g, st, step):
+        O.sgd_step(w, g, None, 0.05, 0.0, 0.0, 0)
+
+    assert run_rule(gm, dev, O, "sgd-plain", shapes, fan, 5, False, 0, gpu, cpu)
+
+
+def test_misaligned_views_inside_an_arena(gm, dev, oracle):
+    """Tensors packed back to back in flat arenas, so most start off a 16-byte
+    boundary; one tensor's streams disagree on alignment and takes the scalar path."""
+    O = oracle
+    L = gm.lib
+    sizes = [5, 1, 3, 4097, 8191, 2, 70001, 33, 16385]
+    total = sum(sizes) + 16
+    rng_w = O.fill_uniform(total, -1.0, 1.0, 7, 1)
+    host = {k: np.zeros(total, dtype=np.float32) for k in "wgmv"}
+    host["w"][:] = rng_w
+    arena = L.gm_arena_create(dev.h, 4 * total * 4 + 4096)
+    assert arena
+    base = {k: L.gm_arena_alloc(arena, total * 4) for k in "wgmv"}
+    assert all(base.values())
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64) + 1      # +1: nothing starts aligned
+    # the last tensor's v stream is shifted by one more element: inconsistent alignment
+    shift = {k: [0] * len(sizes) for k in "wgmv"}
+    shift["v"][-1] = 1
+    ptrs = {k: [base[k] + 4 * (int(o) + shift[k][i]) for i, o in enumerate(offs)] for k in "wgmv"}
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.999, 1e-8, 0.0
+    try:
+        for step in range(1, 4):
+            host["g"][:] = O.fill_normal(total, 0.0, 0.01, 7, 10 + step)
+            for k in "wgmv":
+                dev.upload(base[k], host[k])
+            rc = L.execute_adam_step_cuda(dev.h, gm.uarray(ptrs["w"]), gm.uarray(ptrs["g"]), gm.uarray(ptrs["m"]),
+                                          gm.uarray(ptrs["v"]), len(sizes), gm.iarray([4 * s for s in sizes]),
+                                          lr, b1, b2, eps, wd, step)
+            assert rc == 0, gm.last_error()
+            want = {k: host[k].copy() for k in "wmv"}
+            for i, (o, n) in enumerate(zip(offs, sizes)):
+                sl = {k: slice(int(o) + shift[k][i], int(o) + shift[k][i] + n) for k in "wgmv"}
+                w, m, v = (np.ascontiguousarray(want[k][sl[k]]) for k in "wmv")
+                O.adam_step(w, np.ascontiguousarray(host["g"][sl["g"]]), m, v, lr, b1, b2, eps, wd, step)
+                want["w"][sl["w"]], want["m"][sl["m"]], want["v"][sl["v"]] = w, m, v
+            for k in "wmv":
+                got = dev.to_host(base[k], total)
+                # bytes between and around the tensors must be untouched
+                assert np.array_equal(got.view(np.uint32), want[k].view(np.uint32)), f"stream {k} step {step}"
+                host[k] = got
+    finally:
+        L.gm_arena_destroy(arena)
+
+
+def test_error_codes(gm, dev):
+    L = gm.lib
+    p = L.allocate_cuda_buffer(dev.h, 64, 1)
+    one = gm.uarray([p])
+    sizes = gm.iarray([64])
+    assert L.execute_adam_step_cuda(0, one, one, one, one, 1, sizes, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -1
+    nil = gm.uarray([0])
+    assert L.execute_adam_step_cuda(dev.h, one, nil, one, one, 1, sizes, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -4
+    assert L.execute_adam_step_cuda(dev.h, one, one, one, one, 1, gm.iarray([128]), 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -9
+    assert L.execute_adam_step_cuda(dev.h, one, one, one, one, 1, gm.iarray([6]), 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -9
+    assert L.execute_rmsprop_step_cuda(dev.h, one, one, one, None, None, 1, sizes, 0.01, 0.99, 1e-8, 0.0, 0.9, False, 1) == -5
+    assert L.execute_rmsprop_step_cuda(dev.h, one, one, one, None, None, 1, sizes, 0.01, 0.99, 1e-8, 0.0, 0.0, True, 1) == -6
+    assert L.allocate_cuda_buffer(dev.h, 0, 1) == 0
+    assert L.allocate_cuda_buffer(0, 64, 1) == 0
+    L.deallocate_cuda_buffer(p)
+
+
+def test_convert_roundtrip(gm, dev, oracle):
+    """fp32 -> fp16 is round-to-nearest-even, fp16 -> fp32 is exact (bridge_memory.m:362-376)."""
+    O = oracle
+    n = 100003
+    exps = (np.arange(n) % 12 - 6).astype(np.float32)
+    x = (O.fill_normal(n, 0.0, 1.0, 3, 3) * np.float32(10.0) ** exps).astype(np.float32)
+    x[:8] = [0.0, -0.0, 65504.0, 65520.0, 1e-8, 6e-8, np.inf, -np.inf]
+    src = dev.to_device(x)
+    dst = dev.alloc(n * 2)
+    back = dev.alloc(n * 4)
+    shape = gm.iarray([n])
+    gm.check(gm.lib.convert_tensor_type_cuda(src, dst, shape, 1, 0, 2, dev.h), "f32->f16")
+    h = dev.to_host(dst, n, np.uint16)
+    assert np.array_equal(h, O.f32_to_f16(x))
+    gm.check(gm.lib.convert_tensor_type_cuda(dst, back, shape, 1, 2, 0, dev.h), "f16->f32")
+    assert np.array_equal(dev.to_host(back, n).view(np.uint32), O.f16_to_f32(h).view(np.uint32))
+    assert gm.lib.convert_tensor_type_cuda(src, dst, shape, 1, 0, 1, dev.h) == -11
+    for p in (src, dst, back):
+        dev.free(p)
