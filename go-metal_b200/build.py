@@ -68,7 +68,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(LIB, objects):
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objects + ["-cudart", "static", "-Xcompiler", "-fPIC", "-ldl", "-lpthread"]
+        cmd = [_nvcc(), "-Wno-deprecated-gpu-targets", "-shared", "-o", LIB] + objects + ["-cudart", "static", "-Xcompiler", "-fPIC", "-ldl", "-lpthread"]
         subprocess.run(cmd, check=True)
     return LIB
 

@@ -39,6 +39,25 @@ __device__ __forceinline__ int find_tensor(const int* __restrict__ prefix, int n
     return lo;
 }
 
+// ---- Adam (shared by the fp32 and the mixed-precision kernels): bridge_optimizer.m:398-399 (host), :484-550 (graph) ----
+struct AdamRule {
+    static constexpr int NS = 4;                 // w, g, m, v
+    static constexpr unsigned WMASK = 0b1101;
+    struct P { float lr, beta1, beta2, omb1, omb2, bc1, bc2, eps, wd; int use_wd; };
+    static __device__ __forceinline__ void elem(float (&x)[NS], const P& p) {
+        const float w = x[0], g = x[1];
+        const float m_new = add(mul(x[2], p.beta1), mul(g, p.omb1));
+        const float v_new = add(mul(x[3], p.beta2), mul(mul(g, g), p.omb2));
+        const float m_hat = dvd(m_new, p.bc1);
+        const float v_hat = dvd(v_new, p.bc2);
+        float upd = dvd(m_hat, add(root(v_hat), p.eps));
+        if (p.use_wd) upd = add(upd, mul(w, p.wd));
+        x[0] = sub(w, mul(upd, p.lr));
+        x[2] = m_new;
+        x[3] = v_new;
+    }
+};
+
 // Rule concept:
 //   static constexpr int NS;            number of streams (w, g, state...)
 //   static constexpr unsigned WMASK;    bit s set => stream s is written back

@@ -403,6 +403,25 @@ int gm_device_synchronize(uintptr_t h) {
     return GM_OK;
 }
 
+int gm_timer_start(uintptr_t h) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaEventRecord(d->ev_start, d->stream));
+    return GM_OK;
+}
+
+int gm_timer_stop(uintptr_t h, float* elapsed_ms) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!elapsed_ms) { set_error("output is nil"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaEventRecord(d->ev_stop, d->stream));
+    GM_CUDA_CHECK(cudaEventSynchronize(d->ev_stop));
+    GM_CUDA_CHECK(cudaEventElapsedTime(elapsed_ms, d->ev_start, d->ev_stop));
+    return GM_OK;
+}
+
 // ---- buffers ----
 uintptr_t gm_buffer_alloc(uintptr_t h, int64_t bytes) {
     Device* d = as_device(h);
@@ -463,6 +482,7 @@ int gm_buffer_upload(uintptr_t h, uintptr_t p, const void* host, int64_t bytes) 
     Device* d = as_device(h);
     if (!d) return GM_ERR_NIL_DEVICE;
     DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));     // never overwrite inputs of a step still in flight
     return copy_sync(p, const_cast<void*>(host), bytes, true);
 }
 

@@ -55,7 +55,7 @@ struct Device {
     std::mutex mu;
     std::unordered_map<uint64_t, TensorList*> list_cache;
     int64_t launches = 0;
-    int lbfgs_mode = 1;
+    int lbfgs_mode = 3;                 // bit 0: corrected curvature pair, bit 1: descent direction
     // scratch for reductions (dot partials, tickets); grown on demand
     float* partials = nullptr;
     int64_t partials_cap = 0;

@@ -1,0 +1,525 @@
+// gm_lbfgs.cu -- L-BFGS two-loop recursion with fixed-order dot products.
+//
+// Replaces execute_lbfgs_step_mpsgraph (cgo_bridge/bridge_optimizer.m:980-1321),
+// whose body is scalar CPU loops over buffer contents.  The statement order of
+// that function is kept (q=-g, first loop newest->oldest, identity initial
+// Hessian, second loop oldest->newest, p=-r, fixed step, x+=step*p, old_g<-g,
+// s[hi]=step*p, y[prev]=g-old_g, rho[prev]=1/(s.y) if |s.y|>1e-10 else 0;
+// pairs with |rho|<1e-10 are skipped).  What changes is how it runs:
+//
+//  * every pass over the vectors is one multi-tensor launch; the axpy of one
+//    history pair is fused with the dot product the next pair needs, so a
+//    pair costs 16 B/element instead of 20;
+//  * all scalars (rho, alpha, beta, the skip decisions) stay on the device;
+//  * dot products use one fixed summation order, independent of the grid:
+//    4096-element chunks, inside a chunk lane t of 256 adds the products of
+//    elements (i*256+t)*4+k (i=0..3, k=0..3) in that order, the 32 lanes of a
+//    warp combine with an xor tree (16,8,4,2,1), the 8 warp sums are added in
+//    ascending order; the CTA that finishes last adds the chunk sums (lane t
+//    takes chunks t, t+256, ... then the same tree).  Products are rounded to
+//    fp32 before every add (no fused multiply-add, no float atomics).
+//
+// The mode is a bit set.  Bit 0: y[prev] is formed from the previous gradient
+// before old_g is overwritten (the reference overwrites first, :1232-1239, so
+// its y is always zero and every curvature pair is rejected).  Bit 1: the
+// recursion starts from q = +g, so p = -H*g descends (the reference starts
+// from q = -g, :1026-1038, and negates again at :1204-1213, which moves along
+// +H*g).  Mode 0 is the reference's statement order; mode 3, the default, is a
+// working L-BFGS.
+#include <math.h>
+#include <string.h>
+
+#include <map>
+
+#include "gm_apply.cuh"
+
+namespace gm {
+
+constexpr int kDotChunk = 4096;
+constexpr int kDotThreads = 256;
+
+struct LbfgsTable {
+    const unsigned long long* ptrs;   // [ncols][T]
+    const long long* numel;           // [T]
+    const int* chunk_prefix;          // [T+1]
+    const int* aligned;               // [T] every column of the tensor is 16-byte aligned
+    int T, num_chunks, ncols;
+};
+
+// column layout of the pointer table
+constexpr int COL_W = 0, COL_G = 1, COL_OLDG = 2, COL_DIR = 3, COL_HIST = 4;   // then s[0..m), y[0..m)
+
+struct LbfgsOp {
+    int kind;                 // 0 init (dir=-g), 1 dir-=c*vec, 2 dir+=c*vec, 3 final update, 4 plain dot(colA,colB)
+    int col_axpy;             // kinds 1,2: vector column; kind 4: first operand
+    int col_dot;              // column dotted with the new direction (-1 none); kind 4: second operand
+    const float* rho_axpy;    // kinds 1,2: the pair is skipped when |rho| < 1e-10
+    const float* rho_dot;     // the dot is skipped when |rho| < 1e-10 (nullptr: never skipped)
+    const float* coef;        // kinds 1,2: coefficient, read on the device
+    int epilogue;             // 0 none, 1 out=dot*rho_dot, 2 out=alpha_in-dot*rho_dot, 3 out=1/dot if |dot|>1e-10 else 0, 4 out=dot
+    float* out;
+    const float* alpha_in;
+    // kind 3
+    int col_s_new, col_y_prev, col_s_prev, have_pair, corrected;
+    int descent;              // kind 0: dir = +g instead of -g
+    float step;
+};
+
+__device__ __forceinline__ bool rho_skips(const float* rho) {
+    // bridge_optimizer.m:1066: fabs(rho_j) < 1e-10, evaluated in double
+    return rho != nullptr && fabs((double)(*rho)) < 1e-10;
+}
+
+// Sum of the 256 lane values of a CTA in the documented order; result valid in thread 0.
+__device__ __forceinline__ float cta_reduce_256(float acc, float* warp_sum) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc = add(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    float total = 0.0f;
+    if (threadIdx.x == 0) {
+        total = warp_sum[0];
+#pragma unroll
+        for (int w = 1; w < kDotThreads / 32; ++w) total = add(total, warp_sum[w]);
+    }
+    __syncthreads();
+    return total;
+}
+
+__global__ void __launch_bounds__(kDotThreads)
+lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
+                  unsigned int* __restrict__ ticket) {
+    __shared__ float warp_sum[kDotThreads / 32];
+    __shared__ int is_last;
+    const int tid = threadIdx.x;
+    const int T = tb.T;
+
+    const bool skip_axpy = (op.kind == 1 || op.kind == 2) && rho_skips(op.rho_axpy);
+    const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot) && (op.kind != 3 || op.have_pair);
+    const float coef = (op.kind == 1 || op.kind == 2) ? *op.coef : 0.0f;
+    const bool touches_data = op.kind == 0 || op.kind == 3 || op.kind == 4 || !skip_axpy || want_dot;
+
+    if (touches_data) {
+        for (int c = blockIdx.x; c < tb.num_chunks; c += gridDim.x) {
+            const int t = find_tensor(tb.chunk_prefix, T, c);
+            const long long n = __ldg(tb.numel + t);
+            const long long base = (long long)(c - __ldg(tb.chunk_prefix + t)) * kDotChunk;
+            const bool vec_ok = __ldg(tb.aligned + t) != 0;
+            auto col = [&](int cidx) -> float* {
+                return reinterpret_cast<float*>(__ldg(tb.ptrs + (size_t)cidx * T + t));
+            };
+            float* dir = op.kind == 4 ? nullptr : col(COL_DIR);
+            float acc = 0.0f;
+
+            if (op.kind == 4) {
+                const float* a = col(op.col_axpy);
+                const float* b = col(op.col_dot);
+#pragma unroll
+                for (int i = 0; i < kDotChunk / (kDotThreads * 4); ++i) {
+                    const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
+                    if (vec_ok && e0 + 3 < n) {
+                        const float4 av = *reinterpret_cast<const float4*>(a + e0);
+                        const float4 bv = *reinterpret_cast<const float4*>(b + e0);
+                        acc = add(acc, mul(av.x, bv.x)); acc = add(acc, mul(av.y, bv.y));
+                        acc = add(acc, mul(av.z, bv.z)); acc = add(acc, mul(av.w, bv.w));
+                    } else {
+                        for (int k = 0; k < 4; ++k) if (e0 + k < n) acc = add(acc, mul(a[e0 + k], b[e0 + k]));
+                    }
+                }
+            } else if (op.kind == 3) {
+                float* x = col(COL_W);
+                const float* g = col(COL_G);
+                float* og = col(COL_OLDG);
+                float* s_new = col(op.col_s_new);
+                float* y_prev = op.have_pair ? col(op.col_y_prev) : nullptr;
+                const float* s_prev = op.have_pair ? col(op.col_s_prev) : nullptr;
+                const bool same_slot = op.col_s_prev == op.col_s_new;
+                auto one = [&](long long e) {
+                    const float p = -dir[e];
+                    dir[e] = p;
+                    const float sv = mul(op.step, p);
+                    x[e] = add(x[e], sv);
+                    const float gv = g[e];
+                    if (op.have_pair) {
+                        const float sp = same_slot ? sv : s_prev[e];
+                        float yv;
+                        if (op.corrected) yv = sub(gv, og[e]);        // previous gradient still in old_g
+                        else yv = sub(gv, gv);                        // reference order: old_g already equals g
+                        y_prev[e] = yv;
+                        acc = add(acc, mul(sp, yv));
+                    }
+                    og[e] = gv;
+                    s_new[e] = sv;
+                };
+#pragma unroll
+                for (int i = 0; i < kDotChunk / (kDotThreads * 4); ++i) {
+                    const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
+                    if (vec_ok && e0 + 3 < n) {
+                        float4 dv = *reinterpret_cast<float4*>(dir + e0);
+                        float4 xv = *reinterpret_cast<float4*>(x + e0);
+                        const float4 gv = *reinterpret_cast<const float4*>(g + e0);
+                        dv.x = -dv.x; dv.y = -dv.y; dv.z = -dv.z; dv.w = -dv.w;
+                        const float4 sv = make_float4(mul(op.step, dv.x), mul(op.step, dv.y), mul(op.step, dv.z), mul(op.step, dv.w));
+                        xv.x = add(xv.x, sv.x); xv.y = add(xv.y, sv.y); xv.z = add(xv.z, sv.z); xv.w = add(xv.w, sv.w);
+                        if (op.have_pair) {
+                            float4 yv;
+                            if (op.corrected) {
+                                const float4 ov = *reinterpret_cast<const float4*>(og + e0);
+                                yv = make_float4(sub(gv.x, ov.x), sub(gv.y, ov.y), sub(gv.z, ov.z), sub(gv.w, ov.w));
+                            } else {
+                                yv = make_float4(sub(gv.x, gv.x), sub(gv.y, gv.y), sub(gv.z, gv.z), sub(gv.w, gv.w));
+                            }
+                            const float4 sp = same_slot ? sv : *reinterpret_cast<const float4*>(s_prev + e0);
+                            acc = add(acc, mul(sp.x, yv.x)); acc = add(acc, mul(sp.y, yv.y));
+                            acc = add(acc, mul(sp.z, yv.z)); acc = add(acc, mul(sp.w, yv.w));
+                            *reinterpret_cast<float4*>(y_prev + e0) = yv;
+                        }
+                        *reinterpret_cast<float4*>(dir + e0) = dv;
+                        *reinterpret_cast<float4*>(x + e0) = xv;
+                        *reinterpret_cast<float4*>(og + e0) = gv;
+                        *reinterpret_cast<float4*>(s_new + e0) = sv;
+                    } else {
+                        for (int k = 0; k < 4; ++k) if (e0 + k < n) one(e0 + k);
+                    }
+                }
+            } else {
+                // kinds 0,1,2: produce the new direction, optionally dot it with col_dot
+                const float* g = op.kind == 0 ? col(COL_G) : nullptr;
+                const float* vec = (op.kind != 0 && !skip_axpy) ? col(op.col_axpy) : nullptr;
+                const float* dv = want_dot ? col(op.col_dot) : nullptr;
+                auto new_dir = [&](float d_old, float g_or_vec) -> float {
+                    if (op.kind == 0) return op.descent ? g_or_vec : -g_or_vec;
+                    if (op.kind == 1) return sub(d_old, mul(coef, g_or_vec));
+                    return add(d_old, mul(coef, g_or_vec));
+                };
+                const bool writes = op.kind == 0 || !skip_axpy;
+#pragma unroll
+                for (int i = 0; i < kDotChunk / (kDotThreads * 4); ++i) {
+                    const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
+                    if (vec_ok && e0 + 3 < n) {
+                        float4 d4;
+                        if (op.kind == 0) {
+                            const float4 g4 = *reinterpret_cast<const float4*>(g + e0);
+                            d4 = op.descent ? g4 : make_float4(-g4.x, -g4.y, -g4.z, -g4.w);
+                        } else {
+                            d4 = *reinterpret_cast<const float4*>(dir + e0);
+                            if (!skip_axpy) {
+                                const float4 v4 = *reinterpret_cast<const float4*>(vec + e0);
+                                d4 = make_float4(new_dir(d4.x, v4.x), new_dir(d4.y, v4.y), new_dir(d4.z, v4.z), new_dir(d4.w, v4.w));
+                            }
+                        }
+                        if (writes) *reinterpret_cast<float4*>(dir + e0) = d4;
+                        if (want_dot) {
+                            const float4 o4 = *reinterpret_cast<const float4*>(dv + e0);
+                            acc = add(acc, mul(o4.x, d4.x)); acc = add(acc, mul(o4.y, d4.y));
+                            acc = add(acc, mul(o4.z, d4.z)); acc = add(acc, mul(o4.w, d4.w));
+                        }
+                    } else {
+                        for (int k = 0; k < 4; ++k) {
+                            const long long e = e0 + k;
+                            if (e < n) {
+                                float dn;
+                                if (op.kind == 0) dn = op.descent ? g[e] : -g[e];
+                                else dn = skip_axpy ? dir[e] : new_dir(dir[e], vec[e]);
+                                if (writes) dir[e] = dn;
+                                if (want_dot) acc = add(acc, mul(dv[e], dn));
+                            }
+                        }
+                    }
+                }
+            }
+
+            if (want_dot || op.kind == 4) {
+                const float total = cta_reduce_256(acc, warp_sum);
+                if (tid == 0) partials[c] = total;
+            }
+        }
+    }
+
+    if (op.epilogue == 0) return;
+
+    // The CTA that takes the last ticket sees every chunk sum and finishes the
+    // reduction in a fixed order.
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned my = atomicAdd(ticket, 1u);
+        is_last = (my == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    float dot = 0.0f;
+    const bool have_dot = want_dot || op.kind == 4;
+    if (have_dot) {
+        float acc = 0.0f;
+        const volatile float* pv = partials;
+        for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, pv[c]);
+        dot = cta_reduce_256(acc, warp_sum);
+    }
+    if (tid == 0) {
+        float r = 0.0f;
+        switch (op.epilogue) {
+            case 1: r = have_dot ? mul(dot, *op.rho_dot) : 0.0f; break;                         // alpha_j
+            case 2: r = have_dot ? sub(*op.alpha_in, mul(dot, *op.rho_dot)) : 0.0f; break;      // alpha_j - beta
+            case 3: r = (op.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
+            default: r = dot; break;
+        }
+        *op.out = r;
+        *ticket = 0u;
+        __threadfence();
+    }
+}
+
+// ---- host side ----
+struct LbfgsCtx {
+    void* blob = nullptr;
+    LbfgsTable tb{};
+    std::vector<uintptr_t> key;      // every pointer + size, for exact comparison
+    int history = 0;
+};
+
+static std::mutex g_lb_mu;
+static std::map<Device*, std::vector<LbfgsCtx*>> g_lb;
+
+static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* s_flat, uintptr_t* y_flat,
+                   const int64_t* numel, LbfgsCtx** out) {
+    const int ncols = COL_HIST + 2 * m;
+    std::vector<uintptr_t> key;
+    key.reserve((size_t)ncols * T + T + 2);
+    key.push_back((uintptr_t)T); key.push_back((uintptr_t)m);
+    for (int c = 0; c < 4; ++c) for (int t = 0; t < T; ++t) key.push_back(cols4[c][t]);
+    for (int k = 0; k < m * T; ++k) key.push_back(s_flat[k]);
+    for (int k = 0; k < m * T; ++k) key.push_back(y_flat[k]);
+    for (int t = 0; t < T; ++t) key.push_back((uintptr_t)numel[t]);
+    {
+        std::lock_guard<std::mutex> lk(g_lb_mu);
+        for (LbfgsCtx* c : g_lb[d]) if (c->key == key) { *out = c; return GM_OK; }
+    }
+    std::vector<unsigned long long> ptrs((size_t)ncols * T);
+    std::vector<long long> n64(T);
+    std::vector<int> prefix(T + 1), aligned(T);
+    prefix[0] = 0;
+    for (int t = 0; t < T; ++t) {
+        bool al = true;
+        for (int c = 0; c < 4; ++c) { ptrs[(size_t)c * T + t] = cols4[c][t]; al = al && cols4[c][t] % 16 == 0; }
+        for (int k = 0; k < m; ++k) {
+            ptrs[(size_t)(COL_HIST + k) * T + t] = s_flat[(size_t)k * T + t];
+            ptrs[(size_t)(COL_HIST + m + k) * T + t] = y_flat[(size_t)k * T + t];
+            al = al && s_flat[(size_t)k * T + t] % 16 == 0 && y_flat[(size_t)k * T + t] % 16 == 0;
+        }
+        aligned[t] = al ? 1 : 0;
+        n64[t] = numel[t];
+        int64_t nc = (numel[t] + kDotChunk - 1) / kDotChunk;
+        if (prefix[t] + nc > 0x7fffffff) { set_error("L-BFGS problem too large"); return GM_ERR_BAD_SIZE; }
+        prefix[t + 1] = prefix[t] + (int)nc;
+    }
+    size_t off_n = sizeof(unsigned long long) * ptrs.size();
+    size_t off_p = off_n + sizeof(long long) * T;
+    size_t off_a = off_p + sizeof(int) * (T + 1);
+    size_t bytes = off_a + sizeof(int) * T;
+    std::vector<unsigned char> host(bytes);
+    memcpy(host.data(), ptrs.data(), off_n);
+    memcpy(host.data() + off_n, n64.data(), sizeof(long long) * T);
+    memcpy(host.data() + off_p, prefix.data(), sizeof(int) * (T + 1));
+    memcpy(host.data() + off_a, aligned.data(), sizeof(int) * T);
+    LbfgsCtx* c = new LbfgsCtx();
+    DeviceGuard g(d);
+    cudaError_t e = cudaMalloc(&c->blob, (bytes + 255) / 256 * 256);
+    if (e == cudaSuccess) e = cudaMemcpy(c->blob, host.data(), bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { if (c->blob) cudaFree(c->blob); delete c; cudaGetLastError(); return cuda_fail(e, "L-BFGS table upload"); }
+    unsigned char* b = (unsigned char*)c->blob;
+    c->tb.ptrs = (const unsigned long long*)b;
+    c->tb.numel = (const long long*)(b + off_n);
+    c->tb.chunk_prefix = (const int*)(b + off_p);
+    c->tb.aligned = (const int*)(b + off_a);
+    c->tb.T = T; c->tb.num_chunks = prefix[T]; c->tb.ncols = ncols;
+    c->key = std::move(key);
+    c->history = m;
+    int rc = ensure_partials(d, c->tb.num_chunks);
+    if (rc != GM_OK) { cudaFree(c->blob); delete c; return rc; }
+    std::lock_guard<std::mutex> lk(g_lb_mu);
+    auto& v = g_lb[d];
+    if (v.size() >= 8) {                      // bounded: forget the oldest table
+        cudaStreamSynchronize(d->stream);
+        cudaFree(v.front()->blob);
+        delete v.front();
+        v.erase(v.begin());
+    }
+    v.push_back(c);
+    *out = c;
+    return GM_OK;
+}
+
+static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op) {
+    int grid = persistent_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
+    lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+    d->launches++;
+}
+
+static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_t* old_g, uintptr_t* dir,
+                      uintptr_t* s_flat, uintptr_t* y_flat, uintptr_t* rho_bufs, uintptr_t alpha_buf, int T,
+                      int* buffer_sizes, int m, int hc, int hi, float initial_step, float* step_size) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (T <= 0 || m <= 0 || hc < 0 || hc > m || hi < 0 || hi >= m) {
+        set_error("bad L-BFGS shape: tensors %d history %d count %d index %d", T, m, hc, hi);
+        return GM_ERR_BAD_ARG;
+    }
+    if (!w || !g || !old_g || !dir || !s_flat || !y_flat || !rho_bufs || !alpha_buf || !buffer_sizes) {
+        set_error("a buffer array is nil");
+        return GM_ERR_NIL_BUFFER;
+    }
+    std::vector<int64_t> numel(T);
+    for (int t = 0; t < T; ++t) {
+        if (buffer_sizes[t] <= 0 || buffer_sizes[t] % 4) { set_error("buffer_sizes[%d]=%d is not a positive multiple of 4", t, buffer_sizes[t]); return GM_ERR_BAD_SIZE; }
+        numel[t] = buffer_sizes[t] / 4;
+        if (!w[t] || !g[t] || !old_g[t] || !dir[t]) { set_error("tensor %d has a nil buffer", t); return GM_ERR_NIL_BUFFER; }
+    }
+    for (int k = 0; k < m * T; ++k) if (!s_flat[k] || !y_flat[k]) { set_error("history buffer %d is nil", k); return GM_ERR_NIL_BUFFER; }
+    for (int k = 0; k < m; ++k) if (!rho_bufs[k]) { set_error("rho buffer %d is nil", k); return GM_ERR_NIL_BUFFER; }
+
+    uintptr_t* cols4[4] = {w, g, old_g, dir};
+    LbfgsCtx* c = nullptr;
+    int rc = get_ctx(d, T, m, cols4, s_flat, y_flat, numel.data(), &c);
+    if (rc != GM_OK) return rc;
+
+    DeviceGuard guard(d);
+    float* alpha = (float*)alpha_buf;
+    float* coeff = d->scalars;                 // alpha_j - beta_j of the pair being applied
+    auto slot = [&](int j) { return (hi - hc + j + m) % m; };        // bridge_optimizer.m:1050
+    auto rho_of = [&](int idx) { return (const float*)rho_bufs[idx]; };
+    auto col_s = [&](int idx) { return COL_HIST + idx; };
+    auto col_y = [&](int idx) { return COL_HIST + m + idx; };
+
+    LbfgsOp op{};
+    // q = -g, fused with the dot the newest pair needs
+    op.kind = 0; op.col_dot = -1; op.epilogue = 0; op.descent = (d->lbfgs_mode & 2) ? 1 : 0;
+    if (hc > 0) {
+        const int idx = slot(hc - 1);
+        op.col_dot = col_s(idx); op.rho_dot = rho_of(idx); op.epilogue = 1; op.out = alpha + (hc - 1);
+    }
+    launch_pass(d, c, op);
+
+    // first loop, newest to oldest: q -= alpha_j * y_j, fused with the next dot
+    for (int j = hc - 1; j >= 0; --j) {
+        const int idx = slot(j);
+        LbfgsOp o{};
+        o.kind = 1; o.col_axpy = col_y(idx); o.rho_axpy = rho_of(idx); o.coef = alpha + j;
+        if (j > 0) {
+            const int nx = slot(j - 1);
+            o.col_dot = col_s(nx); o.rho_dot = rho_of(nx); o.epilogue = 1; o.out = alpha + (j - 1);
+        } else {
+            const int nx = slot(0);                                  // second loop starts with beta_0 = rho_0 * y_0.r
+            o.col_dot = col_y(nx); o.rho_dot = rho_of(nx); o.epilogue = 2; o.out = coeff; o.alpha_in = alpha + 0;
+        }
+        launch_pass(d, c, o);
+    }
+
+    // second loop, oldest to newest: r += (alpha_j - beta_j) * s_j, fused with the next dot
+    for (int j = 0; j < hc; ++j) {
+        const int idx = slot(j);
+        LbfgsOp o{};
+        o.kind = 2; o.col_axpy = col_s(idx); o.rho_axpy = rho_of(idx); o.coef = coeff;
+        o.col_dot = -1; o.epilogue = 0;
+        if (j + 1 < hc) {
+            const int nx = slot(j + 1);
+            o.col_dot = col_y(nx); o.rho_dot = rho_of(nx); o.epilogue = 2; o.out = coeff; o.alpha_in = alpha + (j + 1);
+        }
+        launch_pass(d, c, o);
+    }
+
+    // p = -r ; x += step*p ; old_g <- g ; s[hi] = step*p ; y[prev], rho[prev]
+    {
+        const int prev = (hi - 1 + m) % m;
+        LbfgsOp o{};
+        o.kind = 3; o.step = initial_step; o.corrected = (d->lbfgs_mode & 1) ? 1 : 0;
+        o.col_s_new = col_s(hi); o.have_pair = hc > 0 ? 1 : 0;
+        o.col_y_prev = col_y(prev); o.col_s_prev = col_s(prev);
+        o.col_dot = hc > 0 ? col_s(prev) : -1;
+        o.epilogue = hc > 0 ? 3 : 0; o.out = (float*)rho_bufs[prev];
+        launch_pass(d, c, o);
+    }
+    GM_CUDA_CHECK(cudaGetLastError());
+    if (step_size) *step_size = initial_step;       // no line search (bridge_optimizer.m:1216-1217)
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    return GM_OK;
+}
+
+}  // namespace gm
+
+using namespace gm;
+
+extern "C" {
+
+int execute_lbfgs_step_cuda(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_t* old_g, uintptr_t* dir,
+                            uintptr_t* s_flat, uintptr_t* y_flat, uintptr_t* rho_bufs, uintptr_t alpha_buf,
+                            int num_weights, int* buffer_sizes, int history_size, int history_count,
+                            int history_index, float initial_step, float c1, float c2, int max_line_search,
+                            float current_loss, float prev_loss, float* step_size) {
+    // c1, c2, max_line_search and the losses are accepted and unused, as in the
+    // reference (bridge_optimizer.m:1216-1217).
+    (void)c1; (void)c2; (void)max_line_search; (void)current_loss; (void)prev_loss;
+    return lbfgs_step(device_ptr, w, g, old_g, dir, s_flat, y_flat, rho_bufs, alpha_buf, num_weights,
+                      buffer_sizes, history_size, history_count, history_index, initial_step, step_size);
+}
+
+int execute_lbfgs_step_cuda_pooled(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_t* old_g,
+                                   uintptr_t* dir, uintptr_t* s_flat, uintptr_t* y_flat, uintptr_t* rho_bufs,
+                                   uintptr_t alpha_buf, int num_weights, int* buffer_sizes, int history_size,
+                                   int history_count, int history_index, float initial_step, float c1, float c2,
+                                   int max_line_search, float current_loss, float prev_loss,
+                                   uintptr_t command_pool, float* step_size) {
+    (void)command_pool;                       // bridge_optimizer.m:1324-1393 forwards to the plain entry
+    return execute_lbfgs_step_cuda(device_ptr, w, g, old_g, dir, s_flat, y_flat, rho_bufs, alpha_buf, num_weights,
+                                   buffer_sizes, history_size, history_count, history_index, initial_step, c1, c2,
+                                   max_line_search, current_loss, prev_loss, step_size);
+}
+
+int gm_lbfgs_set_mode(uintptr_t device_ptr, int mode) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (mode < 0 || mode > 3) { set_error("L-BFGS mode must be in 0..3"); return GM_ERR_BAD_ARG; }
+    d->lbfgs_mode = mode;
+    return GM_OK;
+}
+
+int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, float* out) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!a || !b || !out) { set_error("nil argument"); return GM_ERR_NIL_BUFFER; }
+    if (n <= 0) { set_error("length %lld is not positive", (long long)n); return GM_ERR_BAD_SIZE; }
+    // A one-tensor table with the two operands in columns 0 and 1.
+    const int64_t nc = (n + kDotChunk - 1) / kDotChunk;
+    if (nc > 0x7fffffff) { set_error("vector too long"); return GM_ERR_BAD_SIZE; }
+    int rc = ensure_partials(d, nc);
+    if (rc != GM_OK) return rc;
+    DeviceGuard guard(d);
+    struct { unsigned long long ptrs[2]; long long numel; int prefix[2]; int aligned; } host;
+    host.ptrs[0] = a; host.ptrs[1] = b; host.numel = n; host.prefix[0] = 0; host.prefix[1] = (int)nc;
+    host.aligned = (a % 16 == 0 && b % 16 == 0) ? 1 : 0;
+    unsigned char* blob = nullptr;
+    GM_CUDA_CHECK(cudaMalloc((void**)&blob, 256));
+    cudaError_t e = cudaMemcpy(blob, &host, sizeof(host), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(blob); return cuda_fail(e, "dot table upload"); }
+    LbfgsTable tb;
+    tb.ptrs = (const unsigned long long*)blob;
+    tb.numel = (const long long*)(blob + offsetof(decltype(host), numel));
+    tb.chunk_prefix = (const int*)(blob + offsetof(decltype(host), prefix));
+    tb.aligned = (const int*)(blob + offsetof(decltype(host), aligned));
+    tb.T = 1; tb.num_chunks = (int)nc; tb.ncols = 2;
+    LbfgsOp op{};
+    op.kind = 4; op.col_axpy = 0; op.col_dot = 1; op.epilogue = 4; op.out = d->scalars + 1;
+    int grid = persistent_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, tb.num_chunks);
+    lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(tb, op, d->partials, d->ticket);
+    d->launches++;
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(out, d->scalars + 1, sizeof(float), cudaMemcpyDeviceToHost);
+    cudaFree(blob);
+    if (e != cudaSuccess) return cuda_fail(e, "canonical dot");
+    return GM_OK;
+}
+
+}  // extern "C"

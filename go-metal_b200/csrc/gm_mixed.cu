@@ -1,0 +1,436 @@
+// gm_mixed.cu -- mixed-precision Adam with a device-resident dynamic loss
+// scale, and the gradient sum-of-squares reduction.
+//
+// The reference only carries the configuration of this feature
+// (training/model_trainer.go:79-87, 258-270: scale 65536, growth 2, backoff
+// 0.5, interval 2000) and a standalone fp32<->fp16 conversion kernel
+// (cgo_bridge/bridge_memory.m:362-376); the policy text is
+// docs/tutorials/mixed-precision.md:617-629: on overflow halve the scale and
+// skip the update, after N clean steps double it.  One step here is two
+// launches and no host synchronisation:
+//   1. mixed_check_kernel   reads the fp16 gradients once, ORs an overflow
+//                           flag (warp vote, one atomic per CTA at most);
+//   2. mixed_update_kernel  if the flag is clear: unscale, Adam on the fp32
+//                           master copy (AdamRule, same order as the fp32
+//                           path), write master/m/v and the fp16 copy; the
+//                           last CTA to finish advances the loss-scale state
+//                           machine and the Adam step counter on the device.
+// Bias corrections come from a host-computed table indexed by the device-side
+// step counter, because libm's powf and CUDA's powf do not round alike.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <set>
+
+#include "gm_apply.cuh"
+
+namespace gm {
+
+constexpr int kMagicMixed = 0x474d4d58;   // "GMMX"
+
+struct Mixed {
+    int magic = kMagicMixed;
+    Device* dev = nullptr;
+    gm_loss_scale_t* d_state = nullptr;
+    unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] ticket
+    float2* d_table = nullptr;             // [table_len+1] {1-b1^t, 1-b2^t}
+    int table_len = 0;
+    bool saturated = false;                // table[table_len] == {1,1}: later steps reuse it
+    float beta1 = 0.9f, beta2 = 0.999f;
+    int64_t calls = 0;                     // upper bound of the device step counter
+};
+
+static std::mutex g_mixed_mu;
+static std::set<Mixed*> g_mixed;
+
+static Mixed* as_mixed(uintptr_t h) {
+    if (!h) { set_error("mixed-precision handle is nil"); return nullptr; }
+    std::lock_guard<std::mutex> lk(g_mixed_mu);
+    Mixed* m = reinterpret_cast<Mixed*>(h);
+    if (!g_mixed.count(m)) { set_error("handle %p is not a live mixed-precision state", (void*)h); return nullptr; }
+    return m;
+}
+
+static int upload_table(Mixed* m, int len) {
+    std::vector<float2> host((size_t)len + 1);
+    host[0] = make_float2(1.0f, 1.0f);
+    for (int t = 1; t <= len; ++t) {
+        host[t].x = 1.0f - powf(m->beta1, (float)t);     // bridge_optimizer.m:398
+        host[t].y = 1.0f - powf(m->beta2, (float)t);     // bridge_optimizer.m:399
+    }
+    // From the first step at which both corrections equal 1 they stay 1.
+    m->saturated = host[len].x == 1.0f && host[len].y == 1.0f;
+    DeviceGuard g(m->dev);
+    GM_CUDA_CHECK(cudaStreamSynchronize(m->dev->stream));
+    if (m->d_table) cudaFree(m->d_table);
+    m->d_table = nullptr;
+    GM_CUDA_CHECK(cudaMalloc((void**)&m->d_table, sizeof(float2) * ((size_t)len + 1)));
+    GM_CUDA_CHECK(cudaMemcpy(m->d_table, host.data(), sizeof(float2) * ((size_t)len + 1), cudaMemcpyHostToDevice));
+    m->table_len = len;
+    return GM_OK;
+}
+
+// 1 bits at 0x8000 / 0x80000000 mark halves whose exponent field is all ones.
+__device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
+    return ((w & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
+}
+
+__global__ void __launch_bounds__(kApplyThreads)
+mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag) {
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+    unsigned bad = 0;
+    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+        const int t = find_tensor(L.chunk_prefix, T, c);
+        const int k = c - __ldg(L.chunk_prefix + t);
+        const long long n = __ldg(L.numel + t);
+        const int h = __ldg(L.head + t);
+        const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + t));
+        if (h < 0) {
+            const long long b = (long long)k * chunk;
+            const long long e = (b + chunk < n) ? b + chunk : n;
+            for (long long i = b + tid; i < e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
+            continue;
+        }
+        const long long b = (long long)h + (long long)k * chunk;
+        const long long e = (b + chunk < n) ? b + chunk : n;
+        if (k == 0 && tid < h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
+        const long long nvec = (e - b) >> 3;
+        const uint4* q = reinterpret_cast<const uint4*>(g + b);
+        for (long long i = tid; i < nvec; i += NT) {
+            const uint4 v = __ldg(q + i);
+            bad |= nonfinite_mask(v.x) | nonfinite_mask(v.y) | nonfinite_mask(v.z) | nonfinite_mask(v.w);
+        }
+        const long long tb = b + (nvec << 3);
+        if (tb + tid < e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
+    }
+    // warp vote, then one atomic for the whole CTA (and only when needed)
+    const int any_bad = __syncthreads_or(bad != 0);
+    if (tid == 0 && any_bad) atomicOr(flag, 1u);
+}
+
+struct MixedScalars { float lr, beta1, beta2, omb1, omb2, eps, wd; int use_wd; };
+
+__device__ __forceinline__ void mixed_elem(float g16_as_f32, float inv_scale, float& w, float& m, float& v,
+                                           unsigned short& p16, const AdamRule::P& p) {
+    float x[4] = {w, mul(g16_as_f32, inv_scale), m, v};
+    AdamRule::elem(x, p);
+    w = x[0]; m = x[2]; v = x[3];
+    p16 = __half_as_ushort(__float2half_rn(x[0]));
+}
+
+__device__ __forceinline__ float half_bits_to_float(unsigned short h) { return __half2float(__ushort_as_half(h)); }
+
+__global__ void __launch_bounds__(kApplyThreads)
+mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
+                    const float2* __restrict__ table, int table_len, const MixedScalars sc) {
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+
+    // Every CTA reads the step's inputs before any CTA can have finished, and
+    // the state is only rewritten by the CTA that finishes last.
+    const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
+    const float scale = *reinterpret_cast<volatile float*>(&state->scale);
+    const int t_prev = *reinterpret_cast<volatile int*>(&state->adam_t);
+
+    if (!overflow) {
+        const int tstep = t_prev + 1;
+        const float2 bc = __ldg(table + (tstep < table_len ? tstep : table_len));
+        AdamRule::P p;
+        p.lr = sc.lr; p.beta1 = sc.beta1; p.beta2 = sc.beta2; p.omb1 = sc.omb1; p.omb2 = sc.omb2;
+        p.bc1 = bc.x; p.bc2 = bc.y; p.eps = sc.eps; p.wd = sc.wd; p.use_wd = sc.use_wd;
+        const float inv_scale = dvd(1.0f, scale);
+
+        for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+            const int t = find_tensor(L.chunk_prefix, T, c);
+            const int k = c - __ldg(L.chunk_prefix + t);
+            const long long n = __ldg(L.numel + t);
+            const int h = __ldg(L.head + t);
+            const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + 0 * (size_t)T + t));
+            float* w = reinterpret_cast<float*>(__ldg(L.ptrs + 1 * (size_t)T + t));
+            float* m = reinterpret_cast<float*>(__ldg(L.ptrs + 2 * (size_t)T + t));
+            float* v = reinterpret_cast<float*>(__ldg(L.ptrs + 3 * (size_t)T + t));
+            unsigned short* o = reinterpret_cast<unsigned short*>(__ldg(L.ptrs + 4 * (size_t)T + t));
+
+            auto scalar_at = [&](long long i) {
+                float wi = w[i], mi = m[i], vi = v[i];
+                unsigned short pi;
+                mixed_elem(half_bits_to_float(g[i]), inv_scale, wi, mi, vi, pi, p);
+                w[i] = wi; m[i] = mi; v[i] = vi; o[i] = pi;
+            };
+
+            if (h < 0) {
+                const long long b = (long long)k * chunk;
+                const long long e = (b + chunk < n) ? b + chunk : n;
+                for (long long i = b + tid; i < e; i += NT) scalar_at(i);
+                continue;
+            }
+            const long long b = (long long)h + (long long)k * chunk;
+            const long long e = (b + chunk < n) ? b + chunk : n;
+            if (k == 0 && tid < h) scalar_at(tid);
+
+            const long long nvec = (e - b) >> 3;                       // 8 elements per thread
+            const uint4* gq = reinterpret_cast<const uint4*>(g + b);
+            float4* wq = reinterpret_cast<float4*>(w + b);
+            float4* mq = reinterpret_cast<float4*>(m + b);
+            float4* vq = reinterpret_cast<float4*>(v + b);
+            uint4* oq = reinterpret_cast<uint4*>(o + b);
+            for (long long i = tid; i < nvec; i += NT) {
+                const uint4 gv = __ldcs(gq + i);
+                float4 w0 = __ldcs(wq + 2 * i), w1 = __ldcs(wq + 2 * i + 1);
+                float4 m0 = __ldcs(mq + 2 * i), m1 = __ldcs(mq + 2 * i + 1);
+                float4 v0 = __ldcs(vq + 2 * i), v1 = __ldcs(vq + 2 * i + 1);
+                unsigned short h0, h1, h2, h3, h4, h5, h6, h7;
+                mixed_elem(half_bits_to_float((unsigned short)(gv.x & 0xffffu)), inv_scale, w0.x, m0.x, v0.x, h0, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.x >> 16)), inv_scale, w0.y, m0.y, v0.y, h1, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.y & 0xffffu)), inv_scale, w0.z, m0.z, v0.z, h2, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.y >> 16)), inv_scale, w0.w, m0.w, v0.w, h3, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.z & 0xffffu)), inv_scale, w1.x, m1.x, v1.x, h4, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.z >> 16)), inv_scale, w1.y, m1.y, v1.y, h5, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.w & 0xffffu)), inv_scale, w1.z, m1.z, v1.z, h6, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gv.w >> 16)), inv_scale, w1.w, m1.w, v1.w, h7, p);
+                __stcs(wq + 2 * i, w0); __stcs(wq + 2 * i + 1, w1);
+                __stcs(mq + 2 * i, m0); __stcs(mq + 2 * i + 1, m1);
+                __stcs(vq + 2 * i, v0); __stcs(vq + 2 * i + 1, v1);
+                uint4 ov;
+                ov.x = (unsigned)h0 | ((unsigned)h1 << 16);
+                ov.y = (unsigned)h2 | ((unsigned)h3 << 16);
+                ov.z = (unsigned)h4 | ((unsigned)h5 << 16);
+                ov.w = (unsigned)h6 | ((unsigned)h7 << 16);
+                __stcs(oq + i, ov);
+            }
+            const long long tb = b + (nvec << 3);
+            if (tb + tid < e) scalar_at(tb + tid);
+        }
+    }
+
+    // last CTA to arrive runs the loss-scale state machine
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned ticket = atomicAdd(flag + 1, 1u);
+        if (ticket == gridDim.x - 1) {
+            gm_loss_scale_t s = *state;
+            if (overflow) {
+                s.scale = mul(s.scale, s.backoff);
+                s.good_steps = 0;
+                s.skipped += 1;
+                s.last_overflow = 1;
+            } else {
+                s.adam_t += 1;
+                s.last_overflow = 0;
+                s.good_steps += 1;
+                if (s.good_steps >= s.interval) {
+                    float grown = mul(s.scale, s.growth);
+                    if (grown > s.max_scale) grown = s.max_scale;
+                    s.scale = grown;
+                    s.good_steps = 0;
+                }
+            }
+            *state = s;
+            flag[0] = 0u;
+            flag[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+// ---- sum of squares (grad-norm): warp shuffle tree, one float atomic per CTA ----
+template <bool HALF>
+__global__ void __launch_bounds__(kApplyThreads)
+sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+    float acc = 0.0f;
+    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+        const int t = find_tensor(L.chunk_prefix, T, c);
+        const int k = c - __ldg(L.chunk_prefix + t);
+        const long long n = __ldg(L.numel + t);
+        const long long b = (long long)k * chunk + (k > 0 && __ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
+        long long e = (long long)(k + 1) * chunk + (__ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
+        if (e > n) e = n;
+        if (HALF) {
+            const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + t));
+            for (long long i = b + tid; i < e; i += NT) {
+                const float x = half_bits_to_float(g[i]) * inv_scale;
+                acc = fmaf(x, x, acc);
+            }
+        } else {
+            const float* g = reinterpret_cast<const float*>(__ldg(L.ptrs + t));
+            for (long long i = b + tid; i < e; i += NT) {
+                const float x = g[i] * inv_scale;
+                acc = fmaf(x, x, acc);
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    __shared__ float warp_sum[NT / 32];
+    if ((tid & 31) == 0) warp_sum[tid >> 5] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NT / 32; ++w) total += warp_sum[w];
+        atomicAdd(out, total);
+    }
+}
+
+}  // namespace gm
+
+using namespace gm;
+
+extern "C" {
+
+uintptr_t gm_mixed_create(uintptr_t device_ptr, const gm_loss_scale_t* initial, float beta1, float beta2,
+                          int table_steps) {
+    Device* d = as_device(device_ptr);
+    if (!d) return 0;
+    gm_loss_scale_t init;
+    if (initial) {
+        init = *initial;
+    } else {                                   // training/model_trainer.go:258-270
+        init.scale = 65536.0f; init.growth = 2.0f; init.backoff = 0.5f; init.max_scale = 16777216.0f;
+        init.interval = 2000; init.good_steps = 0; init.adam_t = 0; init.skipped = 0; init.last_overflow = 0;
+    }
+    if (!(init.scale > 0.0f) || !(init.growth >= 1.0f) || !(init.backoff > 0.0f && init.backoff <= 1.0f)
+        || init.interval < 1 || !(init.max_scale >= init.scale)) {
+        set_error("invalid loss-scale configuration (scale %g growth %g backoff %g interval %d max %g)",
+                  (double)init.scale, (double)init.growth, (double)init.backoff, init.interval, (double)init.max_scale);
+        return 0;
+    }
+    if (!(beta1 >= 0.0f && beta1 < 1.0f && beta2 >= 0.0f && beta2 < 1.0f)) {
+        set_error("betas must lie in [0,1)");
+        return 0;
+    }
+    Mixed* m = new Mixed();
+    m->dev = d; m->beta1 = beta1; m->beta2 = beta2;
+    m->calls = init.adam_t;
+    DeviceGuard g(d);
+    cudaError_t e = cudaMalloc((void**)&m->d_state, 256);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->d_flag, 256);
+    if (e == cudaSuccess) e = cudaMemset(m->d_flag, 0, 256);
+    if (e == cudaSuccess) e = cudaMemcpy(m->d_state, &init, sizeof(init), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess || upload_table(m, table_steps > 0 ? table_steps : 32768) != GM_OK) {
+        if (e != cudaSuccess) cuda_fail(e, "mixed state allocation");
+        if (m->d_state) cudaFree(m->d_state);
+        if (m->d_flag) cudaFree(m->d_flag);
+        if (m->d_table) cudaFree(m->d_table);
+        delete m;
+        return 0;
+    }
+    std::lock_guard<std::mutex> lk(g_mixed_mu);
+    g_mixed.insert(m);
+    return (uintptr_t)m;
+}
+
+void gm_mixed_destroy(uintptr_t h) {
+    Mixed* m = as_mixed(h);
+    if (!m) return;
+    {
+        std::lock_guard<std::mutex> lk(g_mixed_mu);
+        g_mixed.erase(m);
+    }
+    DeviceGuard g(m->dev);
+    cudaStreamSynchronize(m->dev->stream);
+    cudaFree(m->d_state); cudaFree(m->d_flag); cudaFree(m->d_table);
+    delete m;
+}
+
+int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    TensorList* l = as_list(list);
+    if (!m || !l) return GM_ERR_BAD_ARG;
+    if (m->dev != d || l->dev != d) { set_error("handles belong to different devices"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams != 5 || l->elem_bytes[0] != 2 || l->elem_bytes[1] != 4 || l->elem_bytes[2] != 4
+        || l->elem_bytes[3] != 4 || l->elem_bytes[4] != 2) {
+        set_error("mixed-precision list must be g16(2B), master, m, v (4B), p16(2B)");
+        return GM_ERR_BAD_ARG;
+    }
+    // The device counter can be at most `calls` before this step; make sure the
+    // table reaches calls+1 unless its tail is already constant.
+    if (!m->saturated && m->calls + 1 > m->table_len) {
+        int rc = upload_table(m, m->table_len * 2);
+        if (rc != GM_OK) return rc;
+    }
+    m->calls += 1;
+    MixedScalars sc;
+    sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
+    sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
+    DeviceGuard g(d);
+    int grid_c = persistent_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
+    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag);
+    int grid_u = persistent_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
+    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, m->d_table,
+                                                                 m->table_len, sc);
+    d->launches += 2;
+    GM_CUDA_CHECK(cudaGetLastError());
+    return GM_OK;
+}
+
+int gm_mixed_get_state(uintptr_t device_ptr, uintptr_t mixed, gm_loss_scale_t* out) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    if (!m || !out) { if (m) set_error("output is nil"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    GM_CUDA_CHECK(cudaMemcpy(out, m->d_state, sizeof(*out), cudaMemcpyDeviceToHost));
+    return GM_OK;
+}
+
+int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scale_t* in) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    if (!m || !in) { if (m) set_error("input is nil"); return GM_ERR_BAD_ARG; }
+    if (!(in->scale > 0.0f) || in->interval < 1 || in->adam_t < 0) { set_error("invalid loss-scale state"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    GM_CUDA_CHECK(cudaMemcpy(m->d_state, in, sizeof(*in), cudaMemcpyHostToDevice));
+    m->calls = in->adam_t;
+    while (!m->saturated && m->calls + 1 > m->table_len) {
+        int rc = upload_table(m, m->table_len * 2);
+        if (rc != GM_OK) return rc;
+    }
+    return GM_OK;
+}
+
+uintptr_t gm_mixed_state_device_ptr(uintptr_t mixed) {
+    Mixed* m = as_mixed(mixed);
+    return m ? (uintptr_t)m->d_state : 0;
+}
+
+int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, float inv_scale, uintptr_t out) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    TensorList* l = as_list(list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (!out) { set_error("output buffer is nil"); return GM_ERR_NIL_BUFFER; }
+    if (elem_bytes != l->elem_bytes[0] || (elem_bytes != 2 && elem_bytes != 4)) {
+        set_error("gradient stream holds %d-byte elements, caller said %d", l->elem_bytes[0], elem_bytes);
+        return GM_ERR_BAD_ARG;
+    }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaMemsetAsync((void*)out, 0, sizeof(float), d->stream));
+    if (elem_bytes == 2) {
+        int grid = persistent_grid(d, (const void*)sumsq_kernel<true>, kApplyThreads, l->dl.num_chunks);
+        sumsq_kernel<true><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, inv_scale, (float*)out);
+    } else {
+        int grid = persistent_grid(d, (const void*)sumsq_kernel<false>, kApplyThreads, l->dl.num_chunks);
+        sumsq_kernel<false><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, inv_scale, (float*)out);
+    }
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    return GM_OK;
+}
+
+}  // extern "C"

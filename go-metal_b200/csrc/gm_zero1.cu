@@ -1,0 +1,319 @@
+// gm_zero1.cu -- ZeRO-1 style sharding of the optimizer step across the GPUs
+// of one node: every rank keeps the full parameter arena, owns the optimizer
+// state (and the gradients) of one contiguous shard, updates that shard, and
+// the updated parameters are exchanged with an all-gather over NVLink.
+//
+// The reference has no multi-device code at all; this file has no counterpart
+// there.  NCCL is loaded at run time (dlopen of libnccl.so.2) so the library
+// itself loads on machines without NCCL; the ZeRO-1 entries then report
+// GM_ERR_UNSUPPORTED.
+//
+// Two exchange paths:
+//   * gm_zero1_allgather_async / gm_zero1_adam_step_async: the update kernel
+//     followed by ncclAllGather on the same stream (in place: rank r's shard
+//     already sits at arena + r*count).
+//   * gm_zero1_adam_push_step_async: one kernel that updates the shard and
+//     stores each new parameter vector to the local arena and to every peer's
+//     arena through peer-mapped pointers (plain st.global over NVLink; no TMA,
+//     no multicast), so the transfer overlaps the update tile by tile.  A
+//     one-word ncclAllReduce behind it on the same stream is the barrier that
+//     tells every rank that all pushes into its arena have landed.  There is
+//     no device-side waiting in the kernel.
+#include <dlfcn.h>
+#include <math.h>
+#include <string.h>
+
+#include <set>
+
+#include "gm_apply.cuh"
+
+namespace gm {
+
+// Minimal NCCL surface (matches nccl.h 2.x; types kept opaque).
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;
+constexpr int kNcclFloat16 = 6, kNcclFloat32 = 7, kNcclInt32 = 2, kNcclSum = 0;
+
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+
+static NcclApi& nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) return;
+        api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(api.handle, "ncclGetUniqueId");
+        api.CommInitRank = (decltype(api.CommInitRank))dlsym(api.handle, "ncclCommInitRank");
+        api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
+        api.AllGather = (decltype(api.AllGather))dlsym(api.handle, "ncclAllGather");
+        api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+        api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.AllReduce
+                 && api.GetErrorString;
+    });
+    return api;
+}
+
+static int nccl_fail(ncclResult_t r, const char* what) {
+    set_error("NCCL error %d (%s) in %s", r, nccl().GetErrorString ? nccl().GetErrorString(r) : "?", what);
+    return GM_ERR_CUDA;
+}
+
+constexpr int kMaxPeers = 8;
+
+struct Zero1 {
+    Device* dev = nullptr;
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    // peer-mapped arena bases for the push path (index = rank; own entry = local base)
+    uintptr_t peer_base[kMaxPeers] = {0};
+    bool peer_opened[kMaxPeers] = {false};
+    uintptr_t local_base = 0;
+    int* barrier_word = nullptr;       // device int used by the closing all-reduce
+};
+
+static std::mutex g_z_mu;
+static std::set<Zero1*> g_z;
+
+static Zero1* as_zero1(uintptr_t h) {
+    if (!h) { set_error("ZeRO-1 handle is nil"); return nullptr; }
+    std::lock_guard<std::mutex> lk(g_z_mu);
+    Zero1* z = reinterpret_cast<Zero1*>(h);
+    if (!g_z.count(z)) { set_error("handle %p is not a live ZeRO-1 group", (void*)h); return nullptr; }
+    return z;
+}
+
+// ---- fused update + push ----
+struct PeerDst {
+    long long delta[kMaxPeers];   // byte offset from the local arena to each peer's mapping
+    int count;                    // number of peers (excluding self)
+};
+
+// Adam over this rank's shard list; every new parameter vector is stored to the
+// local arena and to the same offset of each peer's arena.
+__global__ void __launch_bounds__(kApplyThreads)
+zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst peers) {
+    constexpr int NS = 4;
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+
+    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+        const int t = find_tensor(L.chunk_prefix, T, c);
+        const int k = c - __ldg(L.chunk_prefix + t);
+        const long long n = __ldg(L.numel + t);
+        const int h = __ldg(L.head + t);
+        float* p[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) p[s] = reinterpret_cast<float*>(__ldg(L.ptrs + (size_t)s * T + t));
+
+        auto scalar_at = [&](long long i) {
+            float x[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) x[s] = p[s][i];
+            AdamRule::elem(x, prm);
+            p[0][i] = x[0]; p[2][i] = x[2]; p[3][i] = x[3];
+            for (int r = 0; r < peers.count; ++r)
+                *reinterpret_cast<float*>(reinterpret_cast<char*>(p[0] + i) + peers.delta[r]) = x[0];
+        };
+
+        if (h < 0) {
+            const long long b = (long long)k * chunk;
+            const long long e = (b + chunk < n) ? b + chunk : n;
+            for (long long i = b + tid; i < e; i += NT) scalar_at(i);
+            continue;
+        }
+        const long long b = (long long)h + (long long)k * chunk;
+        const long long e = (b + chunk < n) ? b + chunk : n;
+        if (k == 0 && tid < h) scalar_at(tid);
+        const long long nvec = (e - b) >> 2;
+        float4* q[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) q[s] = reinterpret_cast<float4*>(p[s] + b);
+        for (long long i = tid; i < nvec; i += NT) {
+            float4 v[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) v[s] = ld_stream(q[s] + i);
+            float x0[NS], x1[NS], x2[NS], x3[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) { x0[s] = v[s].x; x1[s] = v[s].y; x2[s] = v[s].z; x3[s] = v[s].w; }
+            AdamRule::elem(x0, prm); AdamRule::elem(x1, prm); AdamRule::elem(x2, prm); AdamRule::elem(x3, prm);
+            const float4 wn = make_float4(x0[0], x1[0], x2[0], x3[0]);
+            *(q[0] + i) = wn;                                            // local copy stays cacheable
+            st_stream(q[2] + i, make_float4(x0[2], x1[2], x2[2], x3[2]));
+            st_stream(q[3] + i, make_float4(x0[3], x1[3], x2[3], x3[3]));
+            for (int r = 0; r < peers.count; ++r)
+                *reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[r]) = wn;
+        }
+        const long long tb = b + (nvec << 2);
+        if (tb + tid < e) scalar_at(tb + tid);
+    }
+}
+
+}  // namespace gm
+
+using namespace gm;
+
+extern "C" {
+
+int gm_zero1_unique_id(void* out_id) {
+    if (!out_id) { set_error("output is nil"); return GM_ERR_BAD_ARG; }
+    if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded: %s", dlerror() ? dlerror() : "symbols missing"); return GM_ERR_UNSUPPORTED; }
+    ncclUniqueId id;
+    ncclResult_t r = nccl().GetUniqueId(&id);
+    if (r != 0) return nccl_fail(r, "ncclGetUniqueId");
+    memcpy(out_id, &id, sizeof(id));
+    return GM_OK;
+}
+
+uintptr_t gm_zero1_create(uintptr_t device_ptr, const void* unique_id, int rank, int world) {
+    Device* d = as_device(device_ptr);
+    if (!d) return 0;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) { set_error("bad rank %d / world %d (max %d)", rank, world, kMaxPeers); return 0; }
+    Zero1* z = new Zero1();
+    z->dev = d; z->rank = rank; z->world = world;
+    DeviceGuard g(d);
+    if (cudaMalloc((void**)&z->barrier_word, 256) != cudaSuccess) { cuda_fail(cudaGetLastError(), "cudaMalloc"); delete z; return 0; }
+    cudaMemset(z->barrier_word, 0, 256);
+    if (world > 1) {
+        if (!unique_id) { set_error("unique id is nil"); cudaFree(z->barrier_word); delete z; return 0; }
+        if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded"); cudaFree(z->barrier_word); delete z; return 0; }
+        ncclUniqueId id;
+        memcpy(&id, unique_id, sizeof(id));
+        ncclResult_t r = nccl().CommInitRank(&z->comm, world, id, rank);
+        if (r != 0) { nccl_fail(r, "ncclCommInitRank"); cudaFree(z->barrier_word); delete z; return 0; }
+    }
+    std::lock_guard<std::mutex> lk(g_z_mu);
+    g_z.insert(z);
+    return (uintptr_t)z;
+}
+
+void gm_zero1_destroy(uintptr_t h) {
+    Zero1* z = as_zero1(h);
+    if (!z) return;
+    {
+        std::lock_guard<std::mutex> lk(g_z_mu);
+        g_z.erase(z);
+    }
+    DeviceGuard g(z->dev);
+    cudaStreamSynchronize(z->dev->stream);
+    for (int r = 0; r < z->world; ++r)
+        if (z->peer_opened[r]) cudaIpcCloseMemHandle((void*)z->peer_base[r]);
+    if (z->comm) nccl().CommDestroy(z->comm);
+    cudaFree(z->barrier_word);
+    delete z;
+}
+
+int gm_zero1_rank(uintptr_t h) { Zero1* z = as_zero1(h); return z ? z->rank : -1; }
+int gm_zero1_world(uintptr_t h) { Zero1* z = as_zero1(h); return z ? z->world : -1; }
+
+int gm_zero1_allgather_async(uintptr_t h, uintptr_t arena_base, int64_t count, int elem_bytes) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    if (!arena_base) { set_error("arena is nil"); return GM_ERR_NIL_BUFFER; }
+    if (count <= 0 || (elem_bytes != 2 && elem_bytes != 4)) { set_error("bad count/element size"); return GM_ERR_BAD_SIZE; }
+    if (z->world == 1) return GM_OK;
+    DeviceGuard g(z->dev);
+    const char* send = (const char*)arena_base + (size_t)z->rank * count * elem_bytes;
+    ncclResult_t r = nccl().AllGather(send, (void*)arena_base, (size_t)count,
+                                      elem_bytes == 4 ? kNcclFloat32 : kNcclFloat16, z->comm, z->dev->stream);
+    if (r != 0) return nccl_fail(r, "ncclAllGather");
+    z->dev->launches++;
+    return GM_OK;
+}
+
+int gm_zero1_adam_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper, uintptr_t arena_base,
+                             int64_t count) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
+    int rc = launch_rule(z->dev, GM_RULE_ADAM, l, *hyper);
+    if (rc != GM_OK) return rc;
+    return gm_zero1_allgather_async(h, arena_base, count, 4);
+}
+
+// ---- peer mapping for the push path ----
+int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 64 bytes */) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    if (!arena_base || !out_handle) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(z->dev);
+    cudaIpcMemHandle_t mh;
+    GM_CUDA_CHECK(cudaIpcGetMemHandle(&mh, (void*)arena_base));
+    static_assert(sizeof(mh) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(out_handle, &mh, sizeof(mh));
+    z->local_base = arena_base;
+    return GM_OK;
+}
+
+int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, rank order */) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    if (!handles) { set_error("handles are nil"); return GM_ERR_BAD_ARG; }
+    if (!z->local_base) { set_error("call gm_zero1_ipc_handle first"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(z->dev);
+    for (int r = 0; r < z->world; ++r) {
+        if (r == z->rank) { z->peer_base[r] = z->local_base; continue; }
+        cudaIpcMemHandle_t mh;
+        memcpy(&mh, (const char*)handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        GM_CUDA_CHECK(cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
+        z->peer_base[r] = (uintptr_t)p;
+        z->peer_opened[r] = true;
+    }
+    return GM_OK;
+}
+
+int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams != 4) { set_error("Adam shard list needs w,g,m,v"); return GM_ERR_BAD_ARG; }
+    if (hyper->step < 1) { set_error("Adam step count %d must be >= 1", hyper->step); return GM_ERR_BAD_ARG; }
+    Device* d = z->dev;
+    PeerDst peers{};
+    peers.count = 0;
+    for (int r = 0; r < z->world; ++r) {
+        if (r == z->rank) continue;
+        if (!z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
+        peers.delta[peers.count++] = (long long)z->peer_base[r] - (long long)z->local_base;
+    }
+    AdamRule::P p;
+    p.lr = hyper->lr; p.beta1 = hyper->beta1; p.beta2 = hyper->beta2; p.eps = hyper->eps;
+    p.wd = hyper->weight_decay; p.use_wd = hyper->weight_decay > 0.0f ? 1 : 0;
+    p.bc1 = 1.0f - powf(hyper->beta1, (float)hyper->step);
+    p.bc2 = 1.0f - powf(hyper->beta2, (float)hyper->step);
+    p.omb1 = 1.0f - hyper->beta1;
+    p.omb2 = 1.0f - hyper->beta2;
+    DeviceGuard g(d);
+    int grid = persistent_grid(d, (const void*)zero1_adam_push_kernel, kApplyThreads, l->dl.num_chunks);
+    zero1_adam_push_kernel<<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers);
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    if (z->world > 1) {
+        // Completes only after every rank's push kernel has finished.
+        ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, d->stream);
+        if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
+        d->launches++;
+    }
+    return GM_OK;
+}
+
+}  // extern "C"

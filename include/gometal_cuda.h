@@ -129,8 +129,7 @@ int execute_nadam_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
  * s_vectors_flat / y_vectors_flat are history_size*num_weights pointers laid
  * out [slot*num_weights + tensor] (cgo_bridge/bridge.go:1987-1998);
  * rho_buffers are history_size device buffers of one float; alpha_buffer holds
- * history_size floats.  Uses the corrected curvature pair by default; see
- * gm_lbfgs_set_mode(). */
+ * history_size floats.  Runs in mode 3 unless gm_lbfgs_set_mode() says otherwise. */
 int execute_lbfgs_step_cuda(uintptr_t device_ptr, uintptr_t* weight_buffers,
                             uintptr_t* gradient_buffers, uintptr_t* old_gradient_buffers,
                             uintptr_t* search_dir_buffers, uintptr_t* s_vectors_flat,
@@ -242,9 +241,12 @@ int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, fl
                         uintptr_t out_sumsq_device);
 
 /* ---- L-BFGS controls ---- */
-/* mode 0: statement order of the reference (curvature pairs are always
- * rejected because y is formed after old_g is overwritten);
- * mode 1 (default): y is formed from the previous gradient first. */
+/* mode is a bit set.  Bit 0: y[prev] = g - old_g is formed before old_g is
+ * overwritten (the reference overwrites first, bridge_optimizer.m:1232-1239,
+ * so its y is always zero and every curvature pair is rejected).  Bit 1: the
+ * recursion starts from q = +g so the step descends (the reference starts from
+ * q = -g, :1026-1038, negates again at :1204-1213 and so moves along +H*g).
+ * 0 = the reference's statement order; 3 (default) = a working L-BFGS. */
 int gm_lbfgs_set_mode(uintptr_t device_ptr, int mode);
 int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, float* out);
 
@@ -260,6 +262,22 @@ int gm_zero1_allgather_async(uintptr_t zero1, uintptr_t arena_base, int64_t coun
 /* Update of this rank's shard, then the all-gather, on one stream. */
 int gm_zero1_adam_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper,
                              uintptr_t arena_base, int64_t count_per_rank);
+int gm_zero1_rank(uintptr_t zero1);
+int gm_zero1_world(uintptr_t zero1);
+/* Fused update + exchange: one kernel updates the shard and stores every new
+ * parameter to the same offset of each peer's arena through peer-mapped
+ * pointers (plain stores over NVLink).  Setup: each rank exports its arena
+ * with gm_zero1_ipc_handle (64 bytes), the caller exchanges the handles by
+ * any host channel, and gm_zero1_open_peers maps them (rank order).  The
+ * step ends with a one-word all-reduce that acts as the cross-rank barrier. */
+#define GM_IPC_HANDLE_BYTES 64
+int gm_zero1_ipc_handle(uintptr_t zero1, uintptr_t arena_base, void* out_handle);
+int gm_zero1_open_peers(uintptr_t zero1, const void* handles);
+int gm_zero1_adam_push_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper);
+
+/* ---- timing on the device's stream (CUDA events) ---- */
+int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */
+int gm_timer_stop(uintptr_t device_ptr, float* elapsed_ms);/* records the stop event, waits, reports */
 
 #ifdef __cplusplus
 }

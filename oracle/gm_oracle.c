@@ -513,9 +513,13 @@ int gmo_lbfgs_step(int nt, const size_t* numel,
                    float* rho, float* alpha,
                    int hs, int hc, int hi,
                    float initial_step, int mode, int order, float* step_size) {
-    /* q = -g  (:1026-1038) */
+    const int corrected = (mode & 1) != 0;   /* y formed before old_g is overwritten */
+    const int descent = (mode & 2) != 0;     /* recursion starts from +g, so p = -H*g */
+
+    /* q = -g  (:1026-1038).  With the final p = -r (:1204-1213) this makes the
+     * reference move along +H*g; descent mode starts from q = +g instead. */
     for (int t = 0; t < nt; ++t)
-        for (size_t k = 0; k < numel[t]; ++k) dir[t][k] = -g[t][k];
+        for (size_t k = 0; k < numel[t]; ++k) dir[t][k] = descent ? g[t][k] : -g[t][k];
 
     /* first loop, newest to oldest (:1049-1126) */
     for (int j = hc - 1; j >= 0; --j) {
@@ -562,7 +566,7 @@ int gmo_lbfgs_step(int nt, const size_t* numel,
     int prev = (hi - 1 + hs) % hs;
 
     /* corrected mode forms y from the previous gradient before it is lost */
-    if (mode == 1 && hc > 0) {
+    if (corrected && hc > 0) {
         for (int t = 0; t < nt; ++t) {
             float* yt = y[(size_t)prev * nt + t];
             for (size_t k = 0; k < numel[t]; ++k) yt[k] = g[t][k] - old_g[t][k];
@@ -586,7 +590,7 @@ int gmo_lbfgs_step(int nt, const size_t* numel,
 
     /* curvature pair for the previous slot (:1262-1312) */
     if (hc > 0) {
-        if (mode == 0) {
+        if (!corrected) {
             for (int t = 0; t < nt; ++t) {
                 float* yt = y[(size_t)prev * nt + t];
                 for (size_t k = 0; k < numel[t]; ++k) yt[k] = g[t][k] - old_g[t][k];

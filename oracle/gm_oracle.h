@@ -113,8 +113,13 @@ double gmo_sumsq_f16(const uint16_t* g, size_t n, float inv_scale);
 /* ---- L-BFGS (cgo_bridge/bridge_optimizer.m:980-1321) ----
  * s and y are arrays of history_size*num_tensors pointers, slot-major
  * ([slot*num_tensors + tensor], cgo_bridge/bridge.go:1987-1998).
- * mode 0 = faithful statement order (old_g overwritten before y is formed),
- * mode 1 = corrected (y formed from the previous gradient first).
+ * mode is a bit set.  Bit 0 (1): y[prev] is formed from the previous gradient
+ * before old_g is overwritten (the reference overwrites first, :1232-1239,
+ * so its y is always zero and every pair is rejected).  Bit 1 (2): the
+ * recursion starts from q = +g so that p = -H*g is a descent direction (the
+ * reference starts from q = -g and negates again at the end, :1026-1038 and
+ * :1204-1213, which moves along +H*g).  0 = the reference's statement order,
+ * 3 = a working L-BFGS.
  * order 0 = canonical dot order, 1 = sequential (reference) order. */
 int gmo_lbfgs_step(int num_tensors, const size_t* numel,
                    float* const* w, const float* const* g, float* const* old_g,
