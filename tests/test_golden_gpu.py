@@ -14,6 +14,13 @@ def bits(a):
     return np.asarray(a, dtype=np.float32).view(np.uint32)
 
 
+def same_bits(a, b):
+    """Bitwise equality; NaNs match NaNs whatever their payload (x86 and the GPU differ there)."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    na, nb = np.isnan(a), np.isnan(b)
+    return np.array_equal(na, nb) and np.array_equal(bits(a)[~na], bits(b)[~nb])
+
+
 @pytest.fixture(scope="module")
 def G():
     return np.load(GOLDEN)
@@ -110,8 +117,9 @@ def test_golden_lbfgs(gm, dev, G, mode):
             assert rc == 0, gm.last_error()
             hi, hc = (hi + 1) % hs, min(hc + 1, hs)
             rho = np.array([dev.to_host(p, 1)[0] for p in drho], np.float32)
-            assert np.array_equal(bits(rho), bits(G[f"lbfgs_rho_mode{mode}"][it])), f"iteration {it}"
-        assert np.array_equal(bits(dev.to_host(dx, n)), bits(G[f"lbfgs_x_mode{mode}"]))
+            assert same_bits(rho, G[f"lbfgs_rho_mode{mode}"][it]), f"iteration {it}"
+        # mode 1 ascends (reference signs) and has overflowed to NaN by iteration 8
+        assert same_bits(dev.to_host(dx, n), G[f"lbfgs_x_mode{mode}"])
     finally:
         gm.check(L.gm_lbfgs_set_mode(dev.h, 3), "mode")
         for p in [dx, dg, dold, ddir, dalpha] + ds + dy + drho:
