@@ -108,6 +108,7 @@ _SIGS = {
     "gm_grad_sumsq_async": (i, [u, u, i, f, u]),
     "gm_lbfgs_set_mode": (i, [u, i]),
     "gm_dot_canonical": (i, [u, u, u, i64, C.POINTER(f)]),
+    "gm_dot_canonical_static": (i, [u, u, i64, u, u]),
     "gm_zero1_unique_id": (i, [vp]),
     "gm_zero1_create": (u, [u, vp, i, i]),
     "gm_zero1_destroy": (None, [u]),

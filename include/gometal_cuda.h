@@ -249,6 +249,18 @@ int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, fl
  * 0 = the reference's statement order; 3 (default) = a working L-BFGS. */
 int gm_lbfgs_set_mode(uintptr_t device_ptr, int mode);
 int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, float* out);
+/* No counterpart in the reference.  The same dot product for hosts that must
+ * not allocate: a trainer whose own arenas already hold all of HBM, or a loop
+ * that cannot take the device-wide synchronisation of cudaMalloc/cudaFree.
+ * The chunk sums live in a ~64 KB array built into the library (one copy per
+ * GPU that loads it, kept until exit), so n is limited to
+ * GM_DOT_STATIC_MAX_ELEMENTS; longer vectors are rejected with GM_ERR_BAD_SIZE.
+ * a, b, out (one float) are device pointers on the current device; stream is a
+ * cudaStream_t (0 = default).  Asynchronous.  The first call on a device looks
+ * up the array's address and should come before any stream capture.  Calls on
+ * one device share the array: calls that can overlap on the GPU race. */
+#define GM_DOT_STATIC_MAX_ELEMENTS 67108864LL
+int gm_dot_canonical_static(uintptr_t a, uintptr_t b, int64_t n, uintptr_t out_device, uintptr_t stream);
 
 /* ---- ZeRO-1: sharded state + all-gather of updated parameters ---- */
 #define GM_NCCL_UNIQUE_ID_BYTES 128
