@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "optimizer_step_throughput"
 UNIT = "Gparams/s"
-NUM_TENSORS = 256
+NUM_TENSORS = 256               # --tensors shrinks this for profiler captures only
 TENSOR_ELEMS = 4_194_304
 TOTAL = NUM_TENSORS * TENSOR_ELEMS
 BYTES_PER_PARAM = 28            # read w,g,m,v (16) + write w,m,v (12)
@@ -169,6 +169,10 @@ def run_gpu(args):
     import torch
     import gometal_cuda as gm
     L = gm.lib
+    global NUM_TENSORS, TOTAL
+    if args.tensors != NUM_TENSORS:
+        NUM_TENSORS = args.tensors
+        TOTAL = NUM_TENSORS * TENSOR_ELEMS
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -300,6 +304,9 @@ def run_gpu(args):
                 "kernel_ms": update_ms, "frac_of_8TBs_nominal": achieved / 8000.0}
 
     # --- end to end: host buffers through the drop-in entry ---
+    if args.skip_e2e:
+        return _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks,
+                       launches, roofline, None, exchange, shard_elems)
     e2e_steps = min(args.steps, 3)
     host_g = torch.empty(shard_elems, dtype=torch.float32).pin_memory()
     host_g.copy_(grads[0].cpu())
@@ -332,6 +339,12 @@ def run_gpu(args):
            "api": "execute_adam_step_cuda (synchronous drop-in entry), pinned host gradients in, "
                   "updated parameters out"}
 
+    return _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks,
+                   launches, roofline, e2e, exchange, shard_elems)
+
+
+def _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks, launches,
+            roofline, e2e, exchange, shard_elems):
     line = None
     if rank == 0:
         cpu = None
@@ -344,7 +357,8 @@ def run_gpu(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "params": TOTAL, "tensors": NUM_TENSORS,
+            "config": {"workload": WORKLOAD if NUM_TENSORS == 256 else f"REDUCED for profiling: {NUM_TENSORS} tensors",
+                       "params": TOTAL, "tensors": NUM_TENSORS,
                        "parallelism": f"zero1x{world}", "exchange": exchange,
                        "l2": "inputs (>= 2 GiB per rank) far exceed the 126 MB L2; no flush needed",
                        "hbm_gbs_algorithmic": BYTES_PER_PARAM * TOTAL / (ms_per_step * 1e-3) / 1e9},
@@ -375,6 +389,9 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--exchange", choices=["nccl", "push"], default="nccl")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
+    ap.add_argument("--tensors", type=int, default=256,
+                    help="profiling runs only: fewer 4 Mi tensors than the 256 of the workload")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

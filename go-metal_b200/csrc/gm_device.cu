@@ -132,7 +132,14 @@ static Device* make_device(int ordinal) {
     Device* d = new Device();
     d->ordinal = ordinal;
     cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, ordinal);
-    e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    if (const char* e2 = getenv("GOMETAL_GRID_WAVES")) d->grid_waves = atoi(e2);
+    if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);
+    // A blocking stream on purpose: the synchronous copies of the drop-in ABI
+    // (cudaMemcpy/cudaMemset on the legacy default stream) may return before a
+    // small transfer has landed, and only a blocking stream is ordered after
+    // them.  A non-blocking stream let a kernel read a table a few hundred
+    // bytes long before its upload had completed.
+    e = cudaStreamCreateWithFlags(&d->stream, cudaStreamDefault);
     if (e != cudaSuccess) { cuda_fail(e, "cudaStreamCreate"); delete d; return nullptr; }
     cudaEventCreate(&d->ev_start);
     cudaEventCreate(&d->ev_stop);
@@ -156,12 +163,20 @@ int ensure_partials(Device* d, int64_t count) {
     return GM_OK;
 }
 
-int persistent_grid(Device* d, const void* kernel, int threads, int64_t work_items) {
-    int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
-    if (e != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
-    int64_t grid = (int64_t)per_sm * d->sm_count;
-    if (grid > work_items) grid = work_items;
+int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items) {
+    // grid_waves == 0: one CTA per chunk.  Measured on B200, a large grid of
+    // short-lived CTAs streams about 15 % faster than resident CTAs looping
+    // over chunks (the block scheduler keeps more loads in flight).
+    // grid_waves > 0: that many waves of resident CTAs, each looping.
+    int64_t grid = work_items;
+    if (d->grid_waves > 0) {
+        int per_sm = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+        if (e != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+        grid = (int64_t)per_sm * d->sm_count * d->grid_waves;
+        if (grid > work_items) grid = work_items;
+    }
+    if (grid > 0x7fffffff) grid = 0x7fffffff;
     if (grid < 1) grid = 1;
     return (int)grid;
 }
@@ -247,12 +262,11 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     for (int t = 0; t < nt; ++t) total += numel[t];
     l->total = total;
 
-    // Chunk size: large chunks amortise the per-chunk lookup on big lists;
-    // small lists get small chunks so every SM has work.
-    const int tile = kApplyThreads * 8;                 // elements one CTA pass covers
-    int chunk = tile * 8;                               // 16384
-    int64_t want = (int64_t)d->sm_count * 8;
-    while (chunk > tile && total / chunk < want) chunk /= 2;
+    // Chunk = the elements one CTA pass covers (256 threads x 8 elements).
+    // With one CTA per chunk this is also the CTA's whole job.
+    const int tile = kApplyThreads * 8;
+    int chunk = 2 * tile;                               // 4096: best of a 2048..65536 sweep on B200
+    if (d->chunk_elems > 0) chunk = (d->chunk_elems + tile - 1) / tile * tile;
 
     // head[t]: number of leading elements to peel so that every stream of the
     // tensor sits on a 16-byte boundary; the vector tile is 8 elements for
@@ -277,9 +291,11 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
         prefix[t + 1] = prefix[t] + (int)nchunks;
     }
 
+    const int num_chunks = prefix[nt];
     size_t off_ptrs = 0;
     size_t off_numel = off_ptrs + sizeof(unsigned long long) * ns * nt;
-    size_t off_head = off_numel + sizeof(long long) * nt;
+    size_t off_rec = off_numel + sizeof(long long) * nt;
+    size_t off_head = off_rec + sizeof(int2) * (size_t)num_chunks;
     size_t off_prefix = off_head + sizeof(int) * nt;
     size_t bytes = off_prefix + sizeof(int) * (nt + 1);
     std::vector<unsigned char> host(bytes);
@@ -287,6 +303,11 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
         for (int t = 0; t < nt; ++t)
             ((unsigned long long*)(host.data() + off_ptrs))[(size_t)s * nt + t] = (unsigned long long)sp[s][t];
     for (int t = 0; t < nt; ++t) ((long long*)(host.data() + off_numel))[t] = numel[t];
+    {
+        int2* rec = (int2*)(host.data() + off_rec);
+        for (int t = 0; t < nt; ++t)
+            for (int c = prefix[t]; c < prefix[t + 1]; ++c) rec[c] = make_int2(t, c - prefix[t]);
+    }
     memcpy(host.data() + off_head, head.data(), sizeof(int) * nt);
     memcpy(host.data() + off_prefix, prefix.data(), sizeof(int) * (nt + 1));
 
@@ -301,6 +322,7 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     l->dl.numel = (const long long*)(b + off_numel);
     l->dl.head = (const int*)(b + off_head);
     l->dl.chunk_prefix = (const int*)(b + off_prefix);
+    l->dl.chunk_rec = (const int2*)(b + off_rec);
     l->dl.num_tensors = nt;
     l->dl.num_chunks = prefix[nt];
     l->dl.chunk_elems = chunk;

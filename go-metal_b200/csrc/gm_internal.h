@@ -26,6 +26,7 @@ struct DevList {
     const long long* numel;           // [num_tensors]
     const int* head;                  // [num_tensors] scalar elements before the 16-B aligned body; -1 = no aligned body
     const int* chunk_prefix;          // [num_tensors+1] first chunk of each tensor
+    const int2* chunk_rec;            // [num_chunks] {tensor, chunk index inside the tensor}
     int num_tensors;
     int num_chunks;
     int chunk_elems;                  // elements per chunk (multiple of the vector tile)
@@ -55,6 +56,8 @@ struct Device {
     std::mutex mu;
     std::unordered_map<uint64_t, TensorList*> list_cache;
     int64_t launches = 0;
+    int grid_waves = 0;                 // 0: one CTA per chunk; >0: waves of resident CTAs (GOMETAL_GRID_WAVES)
+    int chunk_elems = 0;                // 0: default tile; else elements per chunk (GOMETAL_CHUNK_ELEMS)
     int lbfgs_mode = 3;                 // bit 0: corrected curvature pair, bit 1: descent direction
     // scratch for reductions (dot partials, tickets); grown on demand
     float* partials = nullptr;
@@ -95,8 +98,8 @@ TensorList* build_list(Device* d, int num_streams, int num_tensors,
                        const int* elem_bytes, bool cache, int* err);
 void free_list(TensorList* l);
 
-// Grid size for a persistent kernel: resident CTAs x SMs, capped by the work.
-int persistent_grid(Device* d, const void* kernel, int threads, int64_t work_items);
+// Grid size for a chunked kernel: one CTA per chunk, or waves of resident CTAs when the device asks for it.
+int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items);
 
 int ensure_partials(Device* d, int64_t count);
 

@@ -353,7 +353,7 @@ static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* 
 }
 
 static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op) {
-    int grid = persistent_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
+    int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
     lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
     d->launches++;
 }
@@ -511,7 +511,7 @@ int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, 
     tb.T = 1; tb.num_chunks = (int)nc; tb.ncols = 2;
     LbfgsOp op{};
     op.kind = 4; op.col_axpy = 0; op.col_dot = 1; op.epilogue = 4; op.out = d->scalars + 1;
-    int grid = persistent_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, tb.num_chunks);
+    int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, tb.num_chunks);
     lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(tb, op, d->partials, d->ticket);
     d->launches++;
     e = cudaGetLastError();

@@ -83,8 +83,8 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag) {
     const long long chunk = L.chunk_elems;
     unsigned bad = 0;
     for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
-        const int t = find_tensor(L.chunk_prefix, T, c);
-        const int k = c - __ldg(L.chunk_prefix + t);
+        const int2 rec = __ldg(L.chunk_rec + c);
+        const int t = rec.x, k = rec.y;
         const long long n = __ldg(L.numel + t);
         const int h = __ldg(L.head + t);
         const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + t));
@@ -146,8 +146,8 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
         const float inv_scale = dvd(1.0f, scale);
 
         for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
-            const int t = find_tensor(L.chunk_prefix, T, c);
-            const int k = c - __ldg(L.chunk_prefix + t);
+            const int2 rec = __ldg(L.chunk_rec + c);
+            const int t = rec.x, k = rec.y;
             const long long n = __ldg(L.numel + t);
             const int h = __ldg(L.head + t);
             const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + 0 * (size_t)T + t));
@@ -249,8 +249,8 @@ sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
     const long long chunk = L.chunk_elems;
     float acc = 0.0f;
     for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
-        const int t = find_tensor(L.chunk_prefix, T, c);
-        const int k = c - __ldg(L.chunk_prefix + t);
+        const int2 rec = __ldg(L.chunk_rec + c);
+        const int t = rec.x, k = rec.y;
         const long long n = __ldg(L.numel + t);
         const long long b = (long long)k * chunk + (k > 0 && __ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
         long long e = (long long)(k + 1) * chunk + (__ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
@@ -366,9 +366,9 @@ int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, f
     sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
     sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
     DeviceGuard g(d);
-    int grid_c = persistent_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
+    int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
     mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag);
-    int grid_u = persistent_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
+    int grid_u = launch_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
     mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, m->d_table,
                                                                  m->table_len, sc);
     d->launches += 2;
@@ -422,10 +422,10 @@ int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, fl
     DeviceGuard g(d);
     GM_CUDA_CHECK(cudaMemsetAsync((void*)out, 0, sizeof(float), d->stream));
     if (elem_bytes == 2) {
-        int grid = persistent_grid(d, (const void*)sumsq_kernel<true>, kApplyThreads, l->dl.num_chunks);
+        int grid = launch_grid(d, (const void*)sumsq_kernel<true>, kApplyThreads, l->dl.num_chunks);
         sumsq_kernel<true><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, inv_scale, (float*)out);
     } else {
-        int grid = persistent_grid(d, (const void*)sumsq_kernel<false>, kApplyThreads, l->dl.num_chunks);
+        int grid = launch_grid(d, (const void*)sumsq_kernel<false>, kApplyThreads, l->dl.num_chunks);
         sumsq_kernel<false><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, inv_scale, (float*)out);
     }
     d->launches++;

@@ -11,8 +11,6 @@
 
 namespace gm {
 
-constexpr int kUnroll = 2;
-
 // ---- NAdam: bridge_optimizer.m:2061-2066 (host), :2114-2200 (graph) ----
 struct NadamRule {
     static constexpr int NS = 4;
@@ -148,7 +146,7 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.bc2 = 1.0f - powf(h.beta2, (float)h.step);
             p.omb1 = 1.0f - h.beta1;
             p.omb2 = 1.0f - h.beta2;
-            return launch_apply<AdamRule, kUnroll>(d, l, p);
+            return launch_apply<AdamRule>(d, l, p);
         }
         case GM_RULE_NADAM: {
             if (h.step < 1) { set_error("NAdam step count %d must be >= 1", h.step); return GM_ERR_BAD_ARG; }
@@ -160,13 +158,13 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.omb2 = 1.0f - h.beta2;
             p.mu_next = h.beta1 * (1.0f - 0.5f * powf(0.96f, (float)(h.step + 1) * 0.004f));
             p.om_mu = 1.0f - p.mu_next;
-            return launch_apply<NadamRule, kUnroll>(d, l, p);
+            return launch_apply<NadamRule>(d, l, p);
         }
         case GM_RULE_SGD: {
             SgdScalars p;
             p.lr = h.lr; p.momentum = h.beta1; p.wd = h.weight_decay; p.use_wd = use_wd; p.nesterov = h.nesterov ? 1 : 0;
-            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule, kUnroll>(d, l, p);
-            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule, kUnroll>(d, l, p);
+            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule>(d, l, p);
+            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule>(d, l, p);
             set_error("SGD needs streams w,g (momentum==0) or w,g,mom (momentum>0); got %d streams, momentum %g",
                       l->dl.num_streams, (double)h.beta1);
             return GM_ERR_BAD_ARG;
@@ -176,20 +174,20 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.lr = h.lr; p.alpha = h.beta1; p.oma = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay;
             p.momentum = h.momentum; p.use_wd = use_wd;
             const bool mom = h.momentum > 0.0f, cen = h.centered != 0;
-            if (mom && cen) return launch_apply<RmsPropRule<true, true>, kUnroll>(d, l, p);
-            if (mom) return launch_apply<RmsPropRule<true, false>, kUnroll>(d, l, p);
-            if (cen) return launch_apply<RmsPropRule<false, true>, kUnroll>(d, l, p);
-            return launch_apply<RmsPropRule<false, false>, kUnroll>(d, l, p);
+            if (mom && cen) return launch_apply<RmsPropRule<true, true>>(d, l, p);
+            if (mom) return launch_apply<RmsPropRule<true, false>>(d, l, p);
+            if (cen) return launch_apply<RmsPropRule<false, true>>(d, l, p);
+            return launch_apply<RmsPropRule<false, false>>(d, l, p);
         }
         case GM_RULE_ADAGRAD: {
             AdaGradRule::P p;
             p.lr = h.lr; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaGradRule, kUnroll>(d, l, p);
+            return launch_apply<AdaGradRule>(d, l, p);
         }
         case GM_RULE_ADADELTA: {
             AdaDeltaRule::P p;
             p.rho = h.beta1; p.omr = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaDeltaRule, kUnroll>(d, l, p);
+            return launch_apply<AdaDeltaRule>(d, l, p);
         }
         default:
             set_error("unknown rule %d", rule);

@@ -114,8 +114,8 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
     const long long chunk = L.chunk_elems;
 
     for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
-        const int t = find_tensor(L.chunk_prefix, T, c);
-        const int k = c - __ldg(L.chunk_prefix + t);
+        const int2 rec = __ldg(L.chunk_rec + c);
+        const int t = rec.x, k = rec.y;
         const long long n = __ldg(L.numel + t);
         const int h = __ldg(L.head + t);
         float* p[NS];
@@ -303,7 +303,7 @@ int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hy
     p.omb1 = 1.0f - hyper->beta1;
     p.omb2 = 1.0f - hyper->beta2;
     DeviceGuard g(d);
-    int grid = persistent_grid(d, (const void*)zero1_adam_push_kernel, kApplyThreads, l->dl.num_chunks);
+    int grid = launch_grid(d, (const void*)zero1_adam_push_kernel, kApplyThreads, l->dl.num_chunks);
     zero1_adam_push_kernel<<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers);
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
