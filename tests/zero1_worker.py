@@ -1,0 +1,106 @@
+"""One rank of the multi-GPU ZeRO-1 parity check (launched by
+tests/test_zero1_multigpu.py through torch.distributed.run).
+
+Every rank keeps the full parameter arena, updates its own shard with the CUDA
+library and exchanges parameters, first with the NCCL all-gather path and then
+with the fused update+push kernel; after each step every rank's arena must
+equal, bit for bit, the oracle's update of ALL tensors.
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "go-metal_b200", "python"))
+import gometal_cuda as gm  # noqa: E402
+import zero1_plan as ZP  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+T, E, STEPS = 16, 100_003, 4          # tensor starts are not 16-byte aligned inside the arena
+LR, B1, B2, EPS, WD = 1e-3, 0.9, 0.999, 1e-8, 0.0
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    L = gm.lib
+    dev = gm.Device(local)
+    plan = ZP.make_plan(T, E, world, rank)
+
+    uid = (C.c_ubyte * 128)()
+    if rank == 0:
+        gm.check(L.gm_zero1_unique_id(uid), "unique id")
+    t = torch.tensor(list(bytes(uid)), dtype=torch.uint8, device="cuda")
+    dist.broadcast(t, 0)
+    uid = (C.c_ubyte * 128)(*t.cpu().tolist())
+    z = L.gm_zero1_create(dev.h, uid, rank, world)
+    assert z, gm.last_error()
+    assert L.gm_zero1_rank(z) == rank and L.gm_zero1_world(z) == world
+
+    for exchange in ("nccl", "push"):
+        w0 = O.fill_uniform(T * E, -0.1, 0.1, 91, 1)
+        full, fm, fv = w0.copy(), np.zeros(T * E, np.float32), np.zeros(T * E, np.float32)
+        arena = dev.to_device(w0)
+        dg = dev.alloc(4 * plan.shard_elems)
+        dm = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+        dv = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+        w_ptrs = [arena + 4 * plan.tensor_offset(k) for k in plan.owned]
+        loc = lambda base: [base + 4 * plan.local_offset(k) for k in plan.owned]
+        lst = dev.tensor_list([w_ptrs, loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
+        if exchange == "push":
+            mine = (C.c_ubyte * 64)()
+            gm.check(L.gm_zero1_ipc_handle(z, arena, mine), "ipc handle")
+            mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
+            all_t = [torch.empty_like(mine_t) for _ in range(world)]
+            dist.all_gather(all_t, mine_t)
+            blob = bytes(b for tt in all_t for b in tt.cpu().tolist())
+            gm.check(L.gm_zero1_open_peers(z, (C.c_ubyte * len(blob))(*blob)), "open peers")
+            dist.barrier()
+        for step in range(1, STEPS + 1):
+            grads = [O.fill_normal(E, 0.0, 0.01, 91, 1000 * step + k) for k in range(T)]
+            shard_g = np.concatenate([grads[k] for k in plan.owned])
+            dev.upload(dg, shard_g)
+            dist.barrier()                       # nobody pushes into an arena that is still being read
+            hy = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=step)
+            if exchange == "nccl":
+                gm.check(L.gm_zero1_adam_step_async(z, lst, C.byref(hy), arena, plan.shard_elems), "zero1 step")
+            else:
+                gm.check(L.gm_zero1_adam_push_step_async(z, lst, C.byref(hy)), "zero1 push step")
+            dev.sync()
+            for k in range(T):
+                a = k * E
+                ws, ms, vs = (np.ascontiguousarray(x[a:a + E]) for x in (full, fm, fv))
+                O.adam_step(ws, grads[k], ms, vs, LR, B1, B2, EPS, WD, step)
+                full[a:a + E], fm[a:a + E], fv[a:a + E] = ws, ms, vs
+            got = dev.to_host(arena, T * E)
+            bad = np.flatnonzero(got.view(np.uint32) != full.view(np.uint32))
+            assert bad.size == 0, (f"rank {rank} {exchange} step {step}: {bad.size} parameters differ, first at "
+                                   f"{bad[0]} (tensor {bad[0] // E})")
+            got_m = dev.to_host(dm, plan.shard_elems)
+            want_m = fm[plan.shard_offset:plan.shard_offset + plan.shard_elems]
+            assert np.array_equal(got_m.view(np.uint32), want_m.view(np.uint32)), f"rank {rank}: m differs"
+            dist.barrier()
+        L.gm_tensor_list_destroy(lst)
+        dist.barrier()
+        for p in (dg, dm, dv):
+            dev.free(p)
+        if exchange == "nccl":
+            dev.free(arena)
+        # the pushed arena stays mapped by the peers until the group is destroyed
+    dist.barrier()
+    L.gm_zero1_destroy(z)
+    dist.barrier()
+    dev.close()
+    dist.destroy_process_group()
+    print(f"rank {rank} ok")
+
+
+if __name__ == "__main__":
+    main()
