@@ -169,7 +169,7 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
                             } else {
                                 yv = make_float4(sub(gv.x, gv.x), sub(gv.y, gv.y), sub(gv.z, gv.z), sub(gv.w, gv.w));
                             }
-                            const float4 sp = same_slot ? sv : *reinterpret_cast<const float4*>(s_prev + e0);
+                            const float4 sp = same_slot ? sv : __ldcs(reinterpret_cast<const float4*>(s_prev + e0));
                             acc = add(acc, mul(sp.x, yv.x)); acc = add(acc, mul(sp.y, yv.y));
                             acc = add(acc, mul(sp.z, yv.z)); acc = add(acc, mul(sp.w, yv.w));
                             *reinterpret_cast<float4*>(y_prev + e0) = yv;
@@ -204,13 +204,13 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
                         } else {
                             d4 = *reinterpret_cast<const float4*>(dir + e0);
                             if (!skip_axpy) {
-                                const float4 v4 = *reinterpret_cast<const float4*>(vec + e0);
+                                const float4 v4 = __ldcs(reinterpret_cast<const float4*>(vec + e0));   // history: streamed once, keep dir in L2
                                 d4 = make_float4(new_dir(d4.x, v4.x), new_dir(d4.y, v4.y), new_dir(d4.z, v4.z), new_dir(d4.w, v4.w));
                             }
                         }
                         if (writes) *reinterpret_cast<float4*>(dir + e0) = d4;
                         if (want_dot) {
-                            const float4 o4 = *reinterpret_cast<const float4*>(dv + e0);
+                            const float4 o4 = __ldcs(reinterpret_cast<const float4*>(dv + e0));
                             acc = add(acc, mul(o4.x, d4.x)); acc = add(acc, mul(o4.y, d4.y));
                             acc = add(acc, mul(o4.z, d4.z)); acc = add(acc, mul(o4.w, d4.w));
                         }

@@ -32,7 +32,7 @@ struct Mixed {
     int magic = kMagicMixed;
     Device* dev = nullptr;
     gm_loss_scale_t* d_state = nullptr;
-    unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] ticket
+    unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] update ticket, [2] check ticket, [16..] StepPrep
     float2* d_table = nullptr;             // [table_len+1] {1-b1^t, 1-b2^t}
     int table_len = 0;
     bool saturated = false;                // table[table_len] == {1,1}: later steps reuse it
@@ -75,8 +75,13 @@ __device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
     return ((w & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
 }
 
+// What the update kernel needs to know about the step, written once by the
+// check kernel so that every update CTA starts with a single 16-byte load.
+struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; };
+
 __global__ void __launch_bounds__(kApplyThreads)
-mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag) {
+mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
+                   const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep) {
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
@@ -99,16 +104,38 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag) {
         if (k == 0 && tid < h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
         const long long nvec = (e - b) >> 3;
         const uint4* q = reinterpret_cast<const uint4*>(g + b);
-        for (long long i = tid; i < nvec; i += NT) {
+        for (long long i = tid; i < nvec; i += 2 * NT) {                 // two loads in flight per thread
             const uint4 v = __ldg(q + i);
+            uint4 u = make_uint4(0u, 0u, 0u, 0u);
+            if (i + NT < nvec) u = __ldg(q + i + NT);
             bad |= nonfinite_mask(v.x) | nonfinite_mask(v.y) | nonfinite_mask(v.z) | nonfinite_mask(v.w);
+            bad |= nonfinite_mask(u.x) | nonfinite_mask(u.y) | nonfinite_mask(u.z) | nonfinite_mask(u.w);
         }
         const long long tb = b + (nvec << 3);
         if (tb + tid < e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
     }
     // warp vote, then one atomic for the whole CTA (and only when needed)
     const int any_bad = __syncthreads_or(bad != 0);
-    if (tid == 0 && any_bad) atomicOr(flag, 1u);
+    if (tid == 0) {
+        if (any_bad) atomicOr(flag, 1u);
+        __threadfence();
+        const unsigned ticket = atomicAdd(flag + 2, 1u);
+        if (ticket == gridDim.x - 1) {
+            // last CTA: every vote is in; publish the step's scalars
+            __threadfence();
+            const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
+            const float scale = state->scale;
+            const int tstep = state->adam_t + 1;
+            const float2 bc = table[tstep < table_len ? tstep : table_len];
+            StepPrep sp;
+            sp.overflow = overflow;
+            sp.inv_scale = dvd(1.0f, scale);
+            sp.bc1 = bc.x;
+            sp.bc2 = bc.y;
+            *prep = sp;
+            flag[2] = 0u;
+        }
+    }
 }
 
 struct MixedScalars { float lr, beta1, beta2, omb1, omb2, eps, wd; int use_wd; };
@@ -123,27 +150,25 @@ __device__ __forceinline__ void mixed_elem(float g16_as_f32, float inv_scale, fl
 
 __device__ __forceinline__ float half_bits_to_float(unsigned short h) { return __half2float(__ushort_as_half(h)); }
 
-__global__ void __launch_bounds__(kApplyThreads)
+__global__ void __launch_bounds__(kApplyThreads, 4)
 mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
-                    const float2* __restrict__ table, int table_len, const MixedScalars sc) {
+                    const StepPrep* __restrict__ prep, const MixedScalars sc) {
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
     const long long chunk = L.chunk_elems;
 
-    // Every CTA reads the step's inputs before any CTA can have finished, and
-    // the state is only rewritten by the CTA that finishes last.
-    const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
-    const float scale = *reinterpret_cast<volatile float*>(&state->scale);
-    const int t_prev = *reinterpret_cast<volatile int*>(&state->adam_t);
+    // The step's scalars were published by the check kernel; the loss-scale
+    // state itself is only rewritten by the CTA that finishes last.
+    const uint4 raw = *reinterpret_cast<const uint4*>(prep);
+    const unsigned overflow = raw.x;
 
     if (!overflow) {
-        const int tstep = t_prev + 1;
-        const float2 bc = __ldg(table + (tstep < table_len ? tstep : table_len));
         AdamRule::P p;
         p.lr = sc.lr; p.beta1 = sc.beta1; p.beta2 = sc.beta2; p.omb1 = sc.omb1; p.omb2 = sc.omb2;
-        p.bc1 = bc.x; p.bc2 = bc.y; p.eps = sc.eps; p.wd = sc.wd; p.use_wd = sc.use_wd;
-        const float inv_scale = dvd(1.0f, scale);
+        p.bc1 = __uint_as_float(raw.z); p.bc2 = __uint_as_float(raw.w);
+        p.eps = sc.eps; p.wd = sc.wd; p.use_wd = sc.use_wd;
+        const float inv_scale = __uint_as_float(raw.y);
 
         for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
             const int2 rec = __ldg(L.chunk_rec + c);
@@ -173,37 +198,33 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
             const long long e = (b + chunk < n) ? b + chunk : n;
             if (k == 0 && tid < h) scalar_at(tid);
 
-            const long long nvec = (e - b) >> 3;                       // 8 elements per thread
-            const uint4* gq = reinterpret_cast<const uint4*>(g + b);
+            // 4 elements per thread per pass: one 8-byte access on the fp16 streams,
+            // one 16-byte access on each fp32 stream; the next pass's loads are
+            // issued before this pass's arithmetic.
+            const int nvec = (int)((e - b) >> 2);
+            const uint2* gq = reinterpret_cast<const uint2*>(g + b);
             float4* wq = reinterpret_cast<float4*>(w + b);
             float4* mq = reinterpret_cast<float4*>(m + b);
             float4* vq = reinterpret_cast<float4*>(v + b);
-            uint4* oq = reinterpret_cast<uint4*>(o + b);
-            for (long long i = tid; i < nvec; i += NT) {
-                const uint4 gv = __ldcs(gq + i);
-                float4 w0 = __ldcs(wq + 2 * i), w1 = __ldcs(wq + 2 * i + 1);
-                float4 m0 = __ldcs(mq + 2 * i), m1 = __ldcs(mq + 2 * i + 1);
-                float4 v0 = __ldcs(vq + 2 * i), v1 = __ldcs(vq + 2 * i + 1);
-                unsigned short h0, h1, h2, h3, h4, h5, h6, h7;
-                mixed_elem(half_bits_to_float((unsigned short)(gv.x & 0xffffu)), inv_scale, w0.x, m0.x, v0.x, h0, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.x >> 16)), inv_scale, w0.y, m0.y, v0.y, h1, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.y & 0xffffu)), inv_scale, w0.z, m0.z, v0.z, h2, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.y >> 16)), inv_scale, w0.w, m0.w, v0.w, h3, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.z & 0xffffu)), inv_scale, w1.x, m1.x, v1.x, h4, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.z >> 16)), inv_scale, w1.y, m1.y, v1.y, h5, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.w & 0xffffu)), inv_scale, w1.z, m1.z, v1.z, h6, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gv.w >> 16)), inv_scale, w1.w, m1.w, v1.w, h7, p);
-                __stcs(wq + 2 * i, w0); __stcs(wq + 2 * i + 1, w1);
-                __stcs(mq + 2 * i, m0); __stcs(mq + 2 * i + 1, m1);
-                __stcs(vq + 2 * i, v0); __stcs(vq + 2 * i + 1, v1);
-                uint4 ov;
-                ov.x = (unsigned)h0 | ((unsigned)h1 << 16);
-                ov.y = (unsigned)h2 | ((unsigned)h3 << 16);
-                ov.z = (unsigned)h4 | ((unsigned)h5 << 16);
-                ov.w = (unsigned)h6 | ((unsigned)h7 << 16);
-                __stcs(oq + i, ov);
+            uint2* oq = reinterpret_cast<uint2*>(o + b);
+            int i = tid;
+            uint2 gc; float4 wc, mc, vc;
+            if (i < nvec) { gc = __ldcs(gq + i); wc = __ldcs(wq + i); mc = __ldcs(mq + i); vc = __ldcs(vq + i); }
+            while (i < nvec) {
+                const int nx = i + NT;
+                uint2 gn; float4 wn, mn, vn;
+                if (nx < nvec) { gn = __ldcs(gq + nx); wn = __ldcs(wq + nx); mn = __ldcs(mq + nx); vn = __ldcs(vq + nx); }
+                unsigned short h0, h1, h2, h3;
+                mixed_elem(half_bits_to_float((unsigned short)(gc.x & 0xffffu)), inv_scale, wc.x, mc.x, vc.x, h0, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gc.x >> 16)), inv_scale, wc.y, mc.y, vc.y, h1, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gc.y & 0xffffu)), inv_scale, wc.z, mc.z, vc.z, h2, p);
+                mixed_elem(half_bits_to_float((unsigned short)(gc.y >> 16)), inv_scale, wc.w, mc.w, vc.w, h3, p);
+                __stcs(wq + i, wc); __stcs(mq + i, mc); __stcs(vq + i, vc);
+                __stcs(oq + i, make_uint2((unsigned)h0 | ((unsigned)h1 << 16), (unsigned)h2 | ((unsigned)h3 << 16)));
+                gc = gn; wc = wn; mc = mn; vc = vn;
+                i = nx;
             }
-            const long long tb = b + (nvec << 3);
+            const long long tb = b + ((long long)nvec << 2);
             if (tb + tid < e) scalar_at(tb + tid);
         }
     }
@@ -367,10 +388,11 @@ int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, f
     sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
     DeviceGuard g(d);
     int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
-    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag);
+    StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
+    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
+                                                                m->table_len, prep);
     int grid_u = launch_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
-    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, m->d_table,
-                                                                 m->table_len, sc);
+    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
     d->launches += 2;
     GM_CUDA_CHECK(cudaGetLastError());
     return GM_OK;
