@@ -1,0 +1,59 @@
+/* Recording stand-in for libgometal_cuda.so used by the CPU tests of the host
+ * mirror.  Buffers are host memory; the execute_* entries do NO arithmetic --
+ * they only record that they were called and with which scalars, so host logic
+ * (argument marshalling, step counters, state save/restore, pool tiers) can be
+ * checked without a GPU.  Never loaded by product code. */
+#include <stdbool.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+static int g_calls[16];
+static float g_last[16];
+static int g_last_int[16];
+static int g_allocs, g_frees, g_fail_after = -1, g_next_rc;
+enum { SGD, ADAM, ADAM_POOLED, RMSPROP, ADAGRAD, ADADELTA, NADAM, LBFGS };
+
+int fake_calls(int which) { return g_calls[which]; }
+float fake_last_float(int i) { return g_last[i]; }
+int fake_last_int(int i) { return g_last_int[i]; }
+int fake_allocs(void) { return g_allocs; }
+int fake_frees(void) { return g_frees; }
+void fake_fail_alloc_after(int n) { g_fail_after = n; }
+void fake_next_return(int rc) { g_next_rc = rc; }
+void fake_reset(void) { memset(g_calls, 0, sizeof g_calls); g_allocs = g_frees = 0; g_fail_after = -1; g_next_rc = 0; }
+static int take_rc(void) { int rc = g_next_rc; g_next_rc = 0; return rc; }
+
+const char* gm_last_error(void) { return "fake backend"; }
+uintptr_t create_cuda_device(void) { return 0x1000; }      /* memory/manager.go:322-333 uses the same mock value */
+void destroy_cuda_device(uintptr_t d) { (void)d; }
+uintptr_t allocate_cuda_buffer(uintptr_t dev, int size, int type) {
+    (void)type;
+    if (!dev || size <= 0) return 0;
+    if (g_fail_after >= 0 && g_allocs >= g_fail_after) return 0;
+    g_allocs++;
+    return (uintptr_t)calloc(1, (size_t)size);
+}
+void deallocate_cuda_buffer(uintptr_t p) { if (p) { g_frees++; free((void*)p); } }
+int zero_cuda_buffer(uintptr_t dev, uintptr_t p, int size) { if (!dev) return -1; if (!p) return -4; memset((void*)p, 0, (size_t)size); return 0; }
+int copy_float32_array_to_cuda_buffer(uintptr_t p, float* data, int n) { if (!p) return -4; memcpy((void*)p, data, (size_t)n * 4); return 0; }
+int copy_cuda_buffer_to_float32_array(uintptr_t p, float* data, int n) { if (!p) return -4; memcpy(data, (void*)p, (size_t)n * 4); return 0; }
+
+int execute_sgd_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* m, int n, int* s, float lr, float mom, float wd, int nest, int step) {
+    (void)d; (void)w; (void)g; (void)s; g_calls[SGD]++; g_last[0] = lr; g_last[1] = mom; g_last[2] = wd; g_last_int[0] = nest; g_last_int[1] = step; g_last_int[2] = n; g_last_int[3] = m != 0; return take_rc(); }
+int execute_adam_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* m, uintptr_t* v, int n, int* s, float lr, float b1, float b2, float eps, float wd, int step) {
+    (void)d; (void)w; (void)g; (void)m; (void)v; g_calls[ADAM]++; g_last[0] = lr; g_last[1] = b1; g_last[2] = b2; g_last[3] = eps; g_last[4] = wd; g_last_int[1] = step; g_last_int[2] = n; g_last_int[4] = s[0]; return take_rc(); }
+int execute_adam_step_cuda_pooled(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* m, uintptr_t* v, int n, int* s, float lr, float b1, float b2, float eps, float wd, int step, uintptr_t pool) {
+    (void)pool; g_calls[ADAM_POOLED]++; int rc = execute_adam_step_cuda(d, w, g, m, v, n, s, lr, b1, b2, eps, wd, step); g_calls[ADAM]--; return rc; }
+int execute_rmsprop_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* sq, uintptr_t* m, uintptr_t* ga, int n, int* s, float lr, float a, float eps, float wd, float mom, bool cen, int step) {
+    (void)d; (void)w; (void)g; (void)sq; (void)s; g_calls[RMSPROP]++; g_last[0] = lr; g_last[1] = a; g_last[2] = eps; g_last[3] = wd; g_last[4] = mom; g_last_int[0] = cen; g_last_int[1] = step; g_last_int[2] = n; g_last_int[3] = (m != 0) + 2 * (ga != 0); return take_rc(); }
+int execute_adagrad_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* sq, int n, int* s, float lr, float eps, float wd) {
+    (void)d; (void)w; (void)g; (void)sq; (void)s; g_calls[ADAGRAD]++; g_last[0] = lr; g_last[1] = eps; g_last[2] = wd; g_last_int[2] = n; return take_rc(); }
+int execute_adadelta_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* sq, uintptr_t* u, int n, int* s, float rho, float eps, float wd) {
+    (void)d; (void)w; (void)g; (void)sq; (void)u; (void)s; g_calls[ADADELTA]++; g_last[0] = rho; g_last[1] = eps; g_last[2] = wd; g_last_int[2] = n; return take_rc(); }
+int execute_nadam_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* m, uintptr_t* v, int n, int* s, float lr, float b1, float b2, float eps, float wd, int step) {
+    (void)d; (void)w; (void)g; (void)m; (void)v; (void)s; g_calls[NADAM]++; g_last[0] = lr; g_last[1] = b1; g_last[2] = b2; g_last[3] = eps; g_last[4] = wd; g_last_int[1] = step; g_last_int[2] = n; return take_rc(); }
+int execute_lbfgs_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* og, uintptr_t* dir, uintptr_t* s, uintptr_t* y, uintptr_t* rho, uintptr_t alpha,
+                            int n, int* sizes, int m, int hc, int hi, float step0, float c1, float c2, int mls, float loss, float prev, float* out) {
+    (void)d; (void)w; (void)g; (void)og; (void)dir; (void)s; (void)y; (void)rho; (void)alpha; (void)sizes; (void)c1; (void)c2; (void)mls;
+    g_calls[LBFGS]++; g_last[0] = step0; g_last[1] = loss; g_last[2] = prev; g_last_int[0] = m; g_last_int[1] = hc; g_last_int[2] = n; g_last_int[3] = hi; if (out) *out = step0; return take_rc(); }

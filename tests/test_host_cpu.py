@@ -1,0 +1,357 @@
+"""Host-side logic of the optimizer package (C++ mirror of optimizer/*.go,
+memory/manager.go, training/scheduler.go) against the known-answer tables the
+reference's own tests hold, driven through a recording fake backend: no GPU,
+no arithmetic.  Each test names the reference test it restates."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import hostlib as HL
+
+
+@pytest.fixture(scope="module")
+def H():
+    lib = HL.load_host()
+    assert lib.gmh_init(HL.build_fake().encode()) == 0, HL.err(lib)
+    return lib
+
+
+@pytest.fixture(scope="module")
+def fake():
+    F = C.CDLL(HL.build_fake())
+    F.fake_last_float.restype = C.c_float
+    return F
+
+
+@pytest.fixture()
+def env(H, fake):
+    fake.fake_reset()
+    dev = H.gmh_device_create()
+    mm = H.gmh_mm_create(dev)
+    yield H, fake, mm, dev
+    H.gmh_mm_destroy(mm)
+
+
+# ---------------- helper tables ----------------
+
+def test_extract_buffer_index_table(H):
+    """optimizer/state_helpers_test.go:310-376"""
+    table = {"momentum_0": 0, "variance_5": 5, "squared_grad_avg_10": 10, "momentum": -1, "momentum_abc": -1,
+             "": -1, "_": -1, "momentum_buffer_5": 5, "momentum_-1": -1, "momentum_999": 999}
+    for name, want in table.items():
+        assert H.gmh_extract_buffer_index(name.encode()) == want, name
+
+
+def test_calculate_tensor_size_table(H):
+    """optimizer/state_helpers_test.go:206-258"""
+    for shape, want in [([], 1), ([10], 10), ([10, 20], 200), ([5, 10, 20], 1000), ([2, 3, 4, 5], 120), ([1], 1), ([0], 0)]:
+        arr = (C.c_int * max(len(shape), 1))(*shape)
+        assert H.gmh_calculate_tensor_size(arr, len(shape)) == want
+
+
+def test_extract_params_follow_json_float64_convention(H):
+    """optimizer/state_helpers_test.go:11-163: numbers are read only when they are
+    float64 (what JSON decoding produces); bools only when bool; else the default."""
+    st = H.gmh_state_new(b"Adam")
+    H.gmh_state_set_float64(st, b"learning_rate", 0.01)
+    H.gmh_state_set_bool(st, b"nesterov", 1)
+    H.gmh_state_set_float64(st, b"step_count", 42.0)
+    H.gmh_state_set_uint64(st, b"as_uint", 7)
+    assert abs(H.gmh_extract_float32_param(st, b"learning_rate", 0.5) - 0.01) < 1e-9
+    assert H.gmh_extract_float32_param(st, b"missing", 0.5) == 0.5
+    assert H.gmh_extract_float32_param(st, b"nesterov", 0.25) == 0.25          # wrong kind -> default
+    assert H.gmh_extract_bool_param(st, b"nesterov", 0) == 1
+    assert H.gmh_extract_bool_param(st, b"learning_rate", 1) == 1              # wrong kind -> default
+    assert H.gmh_extract_uint64_param(st, b"step_count", 0) == 42
+    assert H.gmh_extract_uint64_param(st, b"as_uint", 3) == 3                  # uint64 is not float64 -> default
+    assert H.gmh_validate_state_type(b"Adam", st) == 0
+    assert H.gmh_validate_state_type(b"SGD", st) != 0
+    assert HL.err(H) == "state type mismatch: expected SGD, got Adam"          # interface.go:79-84
+    H.gmh_state_destroy(st)
+
+
+def test_pool_tier_tables(H):
+    """memory/memory_test.go:215-266"""
+    for size, want in [(100, 1024), (1024, 1024), (5000, 16384), (100000000, 100000000)]:
+        assert H.gmh_find_pool_size(size) == want
+    for size, want in [(1024, 100), (4096, 100), (16384, 50), (65536, 50), (262144, 20), (1048576, 20),
+                       (4194304, 20), (16777216, 20), (67108864, 15)]:
+        assert H.gmh_calculate_max_pool_size(size) == want
+
+
+def test_memory_manager_reuses_and_caps(env):
+    """memory/manager.go:20-98, 289-317: buffers come back from the tier's free
+    list; a tier refuses to grow past its cap; AllocateBuffer then returns nil."""
+    H, fake, mm, dev = env
+    a = H.gmh_mm_allocate(mm, 3000)
+    assert a and H.gmh_mm_tracked_size(mm, a) == 4096 and fake.fake_allocs() == 1
+    H.gmh_mm_release(mm, a)
+    b = H.gmh_mm_allocate(mm, 4000)
+    assert b == a and fake.fake_allocs() == 1                   # reused, no new device allocation
+    av, al, mx = C.c_int(), C.c_int(), C.c_int()
+    assert H.gmh_mm_stats(mm, 4096, C.byref(av), C.byref(al), C.byref(mx)) == 0
+    assert (av.value, al.value, mx.value) == (0, 1, 100)
+    big = [H.gmh_mm_allocate(mm, 70_000_000) for _ in range(3)]      # beyond the last tier: exact size, own pool
+    assert all(big) and H.gmh_mm_tracked_size(mm, big[0]) == 70_000_000
+    held = [H.gmh_mm_allocate(mm, 20_000_000) for _ in range(16)]    # 64 MB tier holds 15
+    assert all(held[:15]) and held[15] == 0
+    assert H.gmh_mm_allocate(mm, 0) == 0 and H.gmh_mm_allocate(mm, -5) == 0
+    for p in big + held[:15] + [b]:
+        H.gmh_mm_release(mm, p)
+    H.gmh_mm_release(mm, 0)                                          # nil is ignored
+
+
+# ---------------- constructors ----------------
+
+SHAPES = [[784, 128], [128], [128, 10], [10]]
+
+
+def test_default_configs_reach_the_bridge(env):
+    """Default*Config values (adam_test.go:129-154, sgd_test.go:13-39, rmsprop_test.go:19-52,
+    adagrad_test.go:210-245, adadelta_test.go:235-269, nadam_test.go:298-320) arrive at the C entry unchanged."""
+    H, fake, mm, dev = env
+    w = HL.uarr([0x10, 0x20, 0x30, 0x40])
+    want = {
+        "Adam": (HL.ADAM, [0.001, 0.9, 0.999, 1e-8, 0.0]),
+        "SGD": (HL.SGD, [0.01, 0.0, 0.0]),
+        "RMSProp": (HL.RMSPROP, [0.01, 0.99, 1e-8, 0.0, 0.0]),
+        "AdaGrad": (HL.ADAGRAD, [0.01, 1e-10, 0.0]),
+        "AdaDelta": (HL.ADADELTA, [0.95, 1e-6, 0.0]),
+        "Nadam": (HL.NADAM, [0.002, 0.9, 0.999, 1e-8, 0.0]),
+    }
+    for kind, (slot, scalars) in want.items():
+        o = HL.make_optimizer(H, kind, [], SHAPES, mm, dev)
+        assert o, HL.err(H)
+        assert H.gmh_optimizer_set_weight_buffers(o, w, 4) == 0
+        assert H.gmh_optimizer_step(o, w, 4, 0.0) == 0, HL.err(H)
+        assert fake.fake_calls(slot) == 1
+        for i, v in enumerate(scalars):
+            assert fake.fake_last_float(i) == np.float32(v), (kind, i)
+        assert fake.fake_last_int(2) == 4
+        H.gmh_optimizer_destroy(o)
+
+
+def test_constructor_validation_messages(env):
+    """sgd_test.go:94-178, nadam_test.go:153-296, adadelta_test.go:144-233, lbfgs_test.go:101-162"""
+    H, fake, mm, dev = env
+    cases = [
+        ("SGD", [-0.1], "learning rate cannot be negative: -0.100000"),
+        ("SGD", [0.01, -0.5], "momentum cannot be negative: -0.500000"),
+        ("SGD", [0.01, 1.5], "momentum cannot be greater than 1.0: 1.500000"),
+        ("SGD", [0.01, 0.9, -1.0], "weight decay cannot be negative: -1.000000"),
+        ("Nadam", [0.0], "learning rate must be positive, got 0.000000"),
+        ("Nadam", [0.002, 1.0], "beta1 must be in [0, 1), got 1.000000"),
+        ("Nadam", [0.002, 0.9, -0.1], "beta2 must be in [0, 1), got -0.100000"),
+        ("Nadam", [0.002, 0.9, 0.999, 0.0], "epsilon must be positive, got 0.000000e+00"),
+        ("Nadam", [0.002, 0.9, 0.999, 1e-8, -1.0], "weight decay must be non-negative, got -1.000000"),
+        ("AdaDelta", [0.0], "rho must be in range (0, 1), got 0.000000"),
+        ("AdaDelta", [1.0], "rho must be in range (0, 1), got 1.000000"),
+        ("LBFGS", [0], "history size must be positive, got 0"),
+    ]
+    for kind, cfg, msg in cases:
+        assert not HL.make_optimizer(H, kind, cfg, SHAPES, mm, dev)
+        assert HL.err(H) == msg
+    for kind in ("SGD", "Adam", "RMSProp", "AdaGrad", "AdaDelta", "Nadam", "LBFGS"):
+        assert not HL.make_optimizer(H, kind, [], SHAPES, None, dev) and HL.err(H) == "memory manager cannot be nil"
+        assert not HL.make_optimizer(H, kind, [], SHAPES, mm, 0) and HL.err(H) == "device cannot be nil"
+        assert not HL.make_optimizer(H, kind, [], [], mm, dev) and HL.err(H) == "no weight shapes provided"
+
+
+def test_allocation_failure_cleans_up(env):
+    """adam.go:98-136: a failed allocation releases what was already taken."""
+    H, fake, mm, dev = env
+    fake.fake_fail_alloc_after(3)
+    assert not HL.make_optimizer(H, "Adam", [], SHAPES, mm, dev)
+    assert "failed to allocate" in HL.err(H) and "buffer for weight 1" in HL.err(H)
+    fake.fake_fail_alloc_after(-1)
+    o = HL.make_optimizer(H, "Adam", [], SHAPES, mm, dev)        # the three released buffers are reused
+    assert o and fake.fake_allocs() <= 8
+    H.gmh_optimizer_destroy(o)
+
+
+def test_state_buffer_counts(env):
+    """adam_test.go:248-251 and rmsprop_test.go:238-358: TotalBufferSize = state slots x sum of tensor bytes;
+    SGD without momentum and plain RMSProp allocate nothing extra."""
+    H, fake, mm, dev = env
+    total = sum(int(np.prod(s)) for s in SHAPES) * 4
+    for kind, cfg, slots in [("Adam", [], 2), ("Nadam", [], 2), ("AdaDelta", [], 2), ("AdaGrad", [], 1), ("SGD", [], 0),
+                             ("SGD", [0.01, 0.9], 1), ("RMSProp", [], 1), ("RMSProp", [0.01, 0.99, 1e-8, 0, 0.9, 0], 2),
+                             ("RMSProp", [0.01, 0.99, 1e-8, 0, 0.9, 1], 3), ("RMSProp", [0.01, 0.99, 1e-8, 0, 0.0, 1], 2)]:
+        o = HL.make_optimizer(H, kind, cfg, SHAPES, mm, dev)
+        assert o, HL.err(H)
+        assert H.gmh_optimizer_stat(o, b"TotalBufferSize") == slots * total, (kind, cfg)
+        assert H.gmh_optimizer_stat(o, b"NumWeights") == 4
+        H.gmh_optimizer_destroy(o)
+
+
+# ---------------- Step / SetWeightBuffers / LR ----------------
+
+def test_step_counter_and_length_checks(env):
+    """adam.go:160-234: SetWeightBuffers and Step reject wrong lengths; the counter is bumped before the bridge call
+    and passed to it; a failing bridge call is reported with its code."""
+    H, fake, mm, dev = env
+    o = HL.make_optimizer(H, "Adam", [], SHAPES, mm, dev)
+    w = HL.uarr([1, 2, 3, 4])
+    assert H.gmh_optimizer_set_weight_buffers(o, w, 3) != 0
+    assert HL.err(H) == "expected 4 weight buffers, got 3"
+    assert H.gmh_optimizer_set_weight_buffers(o, w, 4) == 0
+    assert H.gmh_optimizer_step(o, w, 2, 0.0) != 0
+    assert HL.err(H) == "gradient buffers length (2) doesn't match weight buffers length (4)"
+    assert H.gmh_optimizer_step_count(o) == 0
+    for k in range(1, 4):
+        assert H.gmh_optimizer_step(o, w, 4, 0.0) == 0
+        assert H.gmh_optimizer_step_count(o) == k and fake.fake_last_int(1) == k
+    assert fake.fake_last_int(4) == 784 * 128 * 4                       # byte sizes, as in adam.go:100
+    fake.fake_next_return(-4)
+    assert H.gmh_optimizer_step(o, w, 4, 0.0) != 0
+    assert HL.err(H).startswith("Adam step execution failed: Adam step failed with error code: -4")
+    H.gmh_optimizer_set_command_pool(o, 0x2000)                         # pooled entry once a pool is set
+    assert H.gmh_optimizer_step(o, w, 4, 0.0) == 0 and fake.fake_calls(HL.ADAM_POOLED) == 1
+    H.gmh_optimizer_destroy(o)
+
+
+def test_update_learning_rate_and_scheduler_hook(env):
+    """adam.go:254-256 stores the value for the next step; adadelta.go:222-225 ignores it;
+    lbfgs.go:330-332 refuses; model_trainer.go:1476-1582 feeds scheduler output (float64 -> float32)."""
+    H, fake, mm, dev = env
+    w = HL.uarr([1, 2, 3, 4])
+    o = HL.make_optimizer(H, "Adam", [], SHAPES, mm, dev)
+    H.gmh_optimizer_set_weight_buffers(o, w, 4)
+    assert H.gmh_optimizer_update_lr(o, 0.5) == 0 and H.gmh_optimizer_lr(o) == 0.5
+    H.gmh_optimizer_step(o, w, 4, 0.0)
+    assert fake.fake_last_float(0) == 0.5
+    sched = H.gmh_sched_create(0, 2, 0.1, 0.0, b"")
+    for epoch, want in [(0, 0.1), (2, 0.01), (4, 0.001)]:
+        assert H.gmh_apply_scheduler(sched, o, epoch, 0, 0.1) == 0
+        H.gmh_optimizer_step(o, w, 4, 0.0)
+        assert fake.fake_last_float(0) == np.float32(0.1 * 0.1 ** (epoch // 2))
+        assert abs(fake.fake_last_float(0) - want) < 1e-8
+    H.gmh_sched_destroy(sched)
+    H.gmh_optimizer_destroy(o)
+    d = HL.make_optimizer(H, "AdaDelta", [], SHAPES, mm, dev)
+    assert H.gmh_optimizer_update_lr(d, 0.5) == 0 and H.gmh_optimizer_lr(d) == 0.0
+    H.gmh_optimizer_destroy(d)
+    l = HL.make_optimizer(H, "LBFGS", [3], [[50]], mm, dev)
+    assert H.gmh_optimizer_update_lr(l, 0.5) != 0
+    assert HL.err(H) == "L-BFGS does not use a fixed learning rate; it uses line search"      # lbfgs_test.go:549
+    H.gmh_optimizer_destroy(l)
+
+
+def test_lbfgs_history_bookkeeping(env):
+    """lbfgs.go:245-301: the circular index advances and the count saturates at HistorySize;
+    the previous loss is handed to the next call."""
+    H, fake, mm, dev = env
+    o = HL.make_optimizer(H, "LBFGS", [3], [[50], [7]], mm, dev)
+    assert o, HL.err(H)
+    w = HL.uarr([1, 2])
+    assert H.gmh_optimizer_set_weight_buffers(o, w, 2) == 0
+    cnt, idx = C.c_int(), C.c_int()
+    seen = []
+    for k in range(5):
+        assert H.gmh_optimizer_step(o, w, 2, float(10 - k)) == 0
+        assert (fake.fake_last_int(0), fake.fake_last_int(2)) == (3, 2)
+        seen.append((fake.fake_last_int(1), fake.fake_last_int(3), fake.fake_last_float(1), fake.fake_last_float(2)))
+        H.gmh_lbfgs_history(o, C.byref(cnt), C.byref(idx))
+    assert [s[:2] for s in seen] == [(0, 0), (1, 1), (2, 2), (3, 0), (3, 1)]       # (count, index) passed to the bridge
+    assert [s[2:] for s in seen] == [(10.0, 0.0), (9.0, 10.0), (8.0, 9.0), (7.0, 8.0), (6.0, 7.0)]
+    assert (cnt.value, idx.value) == (3, 2) and H.gmh_optimizer_step_count(o) == 5
+    # (2m+2) vectors per weight + m rho + 1 alpha (lbfgs.go:113-190)
+    assert fake.fake_allocs() == (2 * 3 + 2) * 2 + 3 + 1
+    H.gmh_optimizer_destroy(o)
+
+
+# ---------------- GetState / LoadState ----------------
+
+def test_state_structure_and_round_trip(env):
+    """adam.go:333-452 and the *GetStateStructure / *LoadStateValidation tests: names "<kind>_<i>", flat [numel] shapes,
+    state types, error texts for a wrong type, a bad index and a size mismatch."""
+    H, fake, mm, dev = env
+    shapes = [[6], [2, 3]]
+    o = HL.make_optimizer(H, "RMSProp", [0.01, 0.99, 1e-8, 0.0, 0.9, 1], shapes, mm, dev)
+    st = H.gmh_optimizer_get_state(o)
+    assert st and H.gmh_state_type(st) == b"RMSProp"
+    names = [(H.gmh_state_tensor_name(st, i).decode(), H.gmh_state_tensor_type(st, i).decode(),
+              H.gmh_state_tensor_shape0(st, i)) for i in range(H.gmh_state_num_tensors(st))]
+    assert names == [("squared_grad_avg_0", "squared_grad_avg", 6), ("squared_grad_avg_1", "squared_grad_avg", 6),
+                     ("momentum_0", "momentum", 6), ("momentum_1", "momentum", 6),
+                     ("gradient_avg_0", "gradient_avg", 6), ("gradient_avg_1", "gradient_avg", 6)]
+    val = C.c_double()
+    assert H.gmh_state_get_param(st, b"step_count", C.byref(val)) == 2 and val.value == 0       # stored as uint64
+    assert H.gmh_state_get_param(st, b"centered", C.byref(val)) == 1 and val.value == 1
+    assert H.gmh_state_get_param(st, b"alpha", C.byref(val)) == 3 and abs(val.value - 0.99) < 1e-6
+    H.gmh_state_destroy(st)
+
+    # a checkpoint as JSON decoding would deliver it: float64 numbers
+    new = H.gmh_state_new(b"RMSProp")
+    H.gmh_state_set_float64(new, b"learning_rate", 0.25)
+    H.gmh_state_set_float64(new, b"alpha", 0.5)
+    H.gmh_state_set_float64(new, b"step_count", 17.0)
+    data = np.arange(6, dtype=np.float32) + 1
+    H.gmh_state_add_tensor(new, b"momentum_1", b"momentum", data.ctypes.data, 6)
+    assert H.gmh_optimizer_load_state(o, new) == 0, HL.err(H)
+    assert H.gmh_optimizer_lr(o) == 0.25 and H.gmh_optimizer_step_count(o) == 17
+    back = H.gmh_optimizer_get_state(o)
+    got = np.zeros(6, np.float32)
+    H.gmh_state_tensor_data(back, 3, got.ctypes.data)                    # momentum_1
+    assert np.array_equal(got, data)
+    H.gmh_state_destroy(back)
+    H.gmh_state_destroy(new)
+
+    wrong = H.gmh_state_new(b"Adam")
+    assert H.gmh_optimizer_load_state(o, wrong) != 0 and HL.err(H) == "state type mismatch: expected RMSProp, got Adam"
+    H.gmh_state_destroy(wrong)
+    for name, stype, n, msg in [(b"momentum_7", b"momentum", 6, "invalid buffer index in tensor name: momentum_7"),
+                                (b"momentum", b"momentum", 6, "invalid buffer index in tensor name: momentum"),
+                                (b"momentum_0", b"momentum", 5, "data size mismatch for momentum_0: expected 6 elements, got 5"),
+                                (b"variance_0", b"variance", 6, "unknown state type: variance")]:
+        bad = H.gmh_state_new(b"RMSProp")
+        H.gmh_state_add_tensor(bad, name, stype, data.ctypes.data, n)
+        assert H.gmh_optimizer_load_state(o, bad) != 0 and HL.err(H) == msg
+        H.gmh_state_destroy(bad)
+    # step_count stored as uint64 (what GetState itself produces) is accepted too
+    u = H.gmh_state_new(b"RMSProp")
+    H.gmh_state_set_uint64(u, b"step_count", 99)
+    assert H.gmh_optimizer_load_state(o, u) == 0 and H.gmh_optimizer_step_count(o) == 99
+    H.gmh_state_destroy(u)
+    H.gmh_optimizer_cleanup(o)
+    assert H.gmh_optimizer_stat(o, b"TotalBufferSize") == 0
+    H.gmh_optimizer_destroy(o)
+
+
+# ---------------- schedulers ----------------
+
+def test_scheduler_tables(H):
+    """training/scheduler_test.go:8-109"""
+    s = H.gmh_sched_create(0, 2, 0.1, 0.0, b"")
+    for epoch, want in [(0, 0.1), (1, 0.1), (2, 0.01), (3, 0.01), (4, 0.001), (5, 0.001), (6, 0.0001)]:
+        assert abs(H.gmh_sched_get_lr(s, epoch, 0, 0.1) - want) <= 1e-8
+    assert H.gmh_sched_name(s) == b"StepLR"
+    H.gmh_sched_destroy(s)
+    s = H.gmh_sched_create(1, 0, 0.9, 0.0, b"")
+    for epoch, want in [(0, 0.1), (1, 0.09), (2, 0.081), (3, 0.0729), (4, 0.06561), (5, 0.059049)]:
+        assert abs(H.gmh_sched_get_lr(s, epoch, 0, 0.1) - want) <= 1e-8
+    assert H.gmh_sched_name(s) == b"ExponentialLR"
+    H.gmh_sched_destroy(s)
+    s = H.gmh_sched_create(2, 5, 0.0001, 0.0, b"")
+    for epoch, want in [(0, 0.01), (5, 0.0001), (2, 0.006580)]:
+        assert abs(H.gmh_sched_get_lr(s, epoch, 0, 0.01) - want) <= 1e-6
+    assert H.gmh_sched_get_lr(s, 10, 0, 0.01) == 0.0001 and H.gmh_sched_name(s) == b"CosineAnnealingLR"
+    H.gmh_sched_destroy(s)
+    s = H.gmh_sched_create(3, 2, 0.5, 0.01, b"min")
+    lr = H.gmh_sched_step(s, 1.0, 0.1)
+    assert lr == 0.1
+    lr = H.gmh_sched_step(s, 0.98, lr)
+    assert lr == 0.1
+    lr = H.gmh_sched_step(s, 0.99, lr)
+    assert lr == 0.1
+    lr = H.gmh_sched_step(s, 0.99, lr)
+    assert lr == 0.05 and H.gmh_sched_name(s) == b"ReduceLROnPlateau" and H.gmh_sched_get_lr(s, 0, 0, 0.1) == 0.05
+    H.gmh_sched_destroy(s)
+    s = H.gmh_sched_create(4, 0, 0.0, 0.0, b"")
+    assert H.gmh_sched_get_lr(s, 9, 9, 0.3) == 0.3 and H.gmh_sched_name(s) == b"ConstantLR"
+    H.gmh_sched_destroy(s)
+    # out-of-range constructor arguments fall back to the defaults (scheduler.go:27-36)
+    s = H.gmh_sched_create(0, 0, 1.5, 0.0, b"")
+    assert abs(H.gmh_sched_get_lr(s, 30, 0, 1.0) - 0.1) < 1e-12 and H.gmh_sched_get_lr(s, 29, 0, 1.0) == 1.0
+    H.gmh_sched_destroy(s)
