@@ -44,8 +44,8 @@ SEED = 0x5EED601D
 LR, B1, B2, EPS, WD = 1e-3, 0.9, 0.999, 1e-8, 0.0
 WORKLOAD = "fp32 Adam, 2^30 params in 256 flat tensors of 4 Mi (config 4), ZeRO-1 over N GPUs"
 # dram__bytes_read.sum + dram__bytes_write.sum of one mta_apply_kernel<AdamRule> launch,
-# scaled from the ncu capture described in profiles/ (None until captured).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# measured on a 16-tensor launch and scaled by the tensor count (traffic is proportional to it).
+TRAFFIC_BYTES_PER_LAUNCH = 16 * (1.07389e9 + 0.75180e9)   # ncu, 16-tensor case: 1.074 GB read + 0.752 GB written, x16
 
 
 def measured_peak_gbs():
@@ -299,7 +299,7 @@ def run_gpu(args):
     peak, peak_kind = measured_peak_gbs()
     achieved = BYTES_PER_PARAM * shard_elems / (update_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH * shard_elems / (256 * TENSOR_ELEMS), "peak_source": f"of {peak_kind}",
                 "kernel": "mta_apply_kernel<AdamRule>", "algorithmic_bytes_per_launch": BYTES_PER_PARAM * shard_elems,
                 "kernel_ms": update_ms, "frac_of_8TBs_nominal": achieved / 8000.0}
 

@@ -1,0 +1,186 @@
+#!/usr/bin/env python
+"""Per-kernel throughput report for libgometal_cuda.so (CUDA-event timed).
+
+    python go-metal_b200/python/kernel_report.py --case rules|mixed|lbfgs [--reps N] [--small]
+
+Prints one JSON line per measured kernel: time per step, algorithmic GB/s
+(bytes per parameter x parameters / time) and Gparams/s.  Inputs are seeded
+and synthetic and larger than the 126 MB L2.  `--small` shrinks the problem
+for profiler captures (nothing here is timed under a profiler).
+
+  rules  every fp32 rule on 2^28 parameters in 64 tensors (2^26 with --small)
+  mixed  mixed-precision Adam on 25,165,824 parameters in 48 ragged tensors
+         packed back to back (tensor starts off the 16-byte boundary)
+  lbfgs  L-BFGS, history 10, n = 10,000,000, once the history is full
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import gometal_cuda as gm  # noqa: E402
+
+L = gm.lib
+
+
+def emit(**kw):
+    print(json.dumps(kw))
+    sys.stdout.flush()
+
+
+def timed(dev, fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    dev.sync()
+    ms = C.c_float()
+    gm.check(L.gm_timer_start(dev.h), "timer")
+    for _ in range(reps):
+        fn()
+    gm.check(L.gm_timer_stop(dev.h, C.byref(ms)), "timer")
+    return ms.value / reps
+
+
+def fill(dev, ptr, n, scale, seed):
+    pat = (np.random.default_rng(seed).standard_normal(1 << 22) * scale).astype(np.float32)
+    for off in range(0, n, pat.size):
+        k = min(pat.size, n - off)
+        gm.check(L.gm_buffer_upload(dev.h, ptr + 4 * off, pat.ctypes.data, 4 * k), "upload")
+
+
+def case_rules(dev, reps, small):
+    n = 1 << (26 if small else 28)
+    nt = 64
+    per = n // nt
+    names = ["w", "g", "s1", "s2", "s3"]
+    buf = {k: dev.alloc(4 * n) for k in names}
+    for k in names:
+        gm.check(L.gm_buffer_zero(dev.h, buf[k], 4 * n), "zero")
+    fill(dev, buf["w"], n, 0.05, 1)
+    fill(dev, buf["g"], n, 0.01, 2)
+    ptrs = {k: [buf[k] + 4 * per * t for t in range(nt)] for k in names}
+    rules = [
+        ("adam", gm.RULE_ADAM, ["w", "g", "s1", "s2"], 28, dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)),
+        ("nadam", gm.RULE_NADAM, ["w", "g", "s1", "s2"], 28, dict(lr=2e-3, beta1=0.9, beta2=0.999, eps=1e-8)),
+        ("adadelta", gm.RULE_ADADELTA, ["w", "g", "s1", "s2"], 28, dict(beta1=0.9, eps=1e-6)),
+        ("sgd_momentum", gm.RULE_SGD, ["w", "g", "s1"], 20, dict(lr=0.01, beta1=0.9)),
+        ("rmsprop", gm.RULE_RMSPROP, ["w", "g", "s1"], 20, dict(lr=0.01, beta1=0.99, eps=1e-8)),
+        ("adagrad", gm.RULE_ADAGRAD, ["w", "g", "s1"], 20, dict(lr=0.01, eps=1e-10)),
+        ("sgd_plain", gm.RULE_SGD, ["w", "g"], 12, dict(lr=0.01, beta1=0.0)),
+    ]
+    for name, rule, streams, bpp, hp in rules:
+        lst = dev.tensor_list([ptrs[k] for k in streams], [per] * nt)
+        hy = gm.Hyper(step=1, **hp)
+        state = {"t": 0}
+
+        def one():
+            state["t"] += 1
+            hy.step = state["t"]
+            gm.check(L.gm_step_async(dev.h, rule, lst, C.byref(hy)), name)
+
+        ms = timed(dev, one, reps)
+        emit(kernel=f"mta_apply_kernel<{name}>", params=n, ms=ms, bytes_per_param=bpp,
+             gbs=bpp * n / ms / 1e6, gparams_s=n / ms / 1e6)
+        L.gm_tensor_list_destroy(lst)
+    for k in names:
+        dev.free(buf[k])
+
+
+def ragged_sizes(count, total, lo, hi, seed=0x5EED601D):
+    rng = np.random.default_rng(seed)
+    raw = np.exp(rng.uniform(np.log(lo), np.log(hi), size=count))
+    sizes = np.maximum(lo, np.floor(raw * (total / raw.sum()))).astype(np.int64)
+    sizes[sizes % 8 == 0] += 1
+    sizes[int(np.argmax(sizes))] += int(total - sizes.sum())
+    return [int(s) for s in sizes]
+
+
+def case_mixed(dev, reps, small):
+    total_params = 25_165_824 // (4 if small else 1)
+    sizes = ragged_sizes(48, total_params, 4096, 4_194_304 // (4 if small else 1))
+    n = sum(sizes)
+    total = n + 32
+    eb = {"g": 2, "w": 4, "m": 4, "v": 4, "p": 2}
+    base = {k: dev.alloc(total * eb[k]) for k in "gwmvp"}
+    for k in "gwmvp":
+        gm.check(L.gm_buffer_zero(dev.h, base[k], total * eb[k]), "zero")
+    g16 = (np.random.default_rng(1).standard_normal(total).astype(np.float32) * 65.536).astype(np.float16)
+    dev.upload(base["g"], g16.view(np.uint16))
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64) + 1
+    ptrs = {k: [base[k] + eb[k] * int(o) for o in offs] for k in "gwmvp"}
+    lst = dev.tensor_list([ptrs[k] for k in "gwmvp"], sizes, [2, 4, 4, 4, 2])
+    mx = L.gm_mixed_create(dev.h, None, 0.9, 0.999, 0)
+    ms = timed(dev, lambda: gm.check(L.gm_mixed_step_async(dev.h, mx, lst, 1e-3, 1e-8, 0.0), "mixed"), reps)
+    st = gm.LossScale()
+    gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(st)), "state")
+    emit(kernel="mixed_check_kernel+mixed_update_kernel", params=n, ms=ms, bytes_per_param=30,
+         gbs=30 * n / ms / 1e6, gparams_s=n / ms / 1e6, scale=st.scale, adam_t=st.adam_t, skipped=st.skipped)
+    L.gm_mixed_destroy(mx)
+    L.gm_tensor_list_destroy(lst)
+    for k in "gwmvp":
+        dev.free(base[k])
+
+
+def case_lbfgs(dev, reps, small):
+    n = 10_000_000 // (4 if small else 1)
+    m = 10
+    z = lambda k: dev.to_device(np.zeros(k, np.float32)) if k < 4096 else _zeros(dev, k)
+    x, g, old, d = (z(n) for _ in range(4))
+    S = [z(n) for _ in range(m)]
+    Y = [z(n) for _ in range(m)]
+    RHO = [z(64) for _ in range(m)]
+    ALPHA = z(64)
+    rng = np.random.default_rng(2)
+    D = (10 ** rng.uniform(-0.3, 0.3, n)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    xs = np.zeros(n, np.float32)
+    hc = hi = 0
+    walls = []
+    for it in range(m + max(reps, 3)):
+        dev.upload(g, (D * xs - b).astype(np.float32))
+        step = C.c_float()
+        dev.sync()
+        t0 = time.perf_counter()
+        rc = L.execute_lbfgs_step_cuda(dev.h, gm.uarray([x]), gm.uarray([g]), gm.uarray([old]), gm.uarray([d]), gm.uarray(S),
+                                       gm.uarray(Y), gm.uarray(RHO), ALPHA, 1, gm.iarray([4 * n]), m, hc, hi, 1.0, 1e-4, 0.9,
+                                       20, 0.0, 0.0, C.byref(step))
+        dt = time.perf_counter() - t0
+        gm.check(rc, "lbfgs")
+        if hc == m:
+            walls.append(dt * 1e3)
+        hi, hc = (hi + 1) % m, min(hc + 1, m)
+        xs = dev.to_host(x, n)
+    ms = float(np.median(walls))
+    bpe = 44 + 32 * m
+    emit(kernel="lbfgs_pass_kernel x 22 launches (one synchronous step)", elements=n, history=m, ms=ms,
+         bytes_per_element=bpe, gbs=bpe * n / ms / 1e6, note="host wall clock around the synchronous drop-in entry")
+
+
+def _zeros(dev, k):
+    p = dev.alloc(4 * k)
+    gm.check(L.gm_buffer_zero(dev.h, p, 4 * k), "zero")
+    return p
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", choices=["rules", "mixed", "lbfgs"], required=True)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--small", action="store_true")
+    args = ap.parse_args()
+    dev = gm.Device(0)
+    try:
+        {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs}[args.case](dev, args.reps, args.small)
+    finally:
+        dev.close()
+
+
+if __name__ == "__main__":
+    main()
