@@ -227,7 +227,7 @@ def run_gpu(args):
         if not zero1:
             raise SystemExit("ZeRO-1 group creation failed: " + gm.last_error())
         exchange = args.exchange
-        if exchange == "push":
+        if exchange in ("push", "dma"):
             mine = (C.c_ubyte * 64)()
             gm.check(L.gm_zero1_ipc_handle(zero1, w_arena.data_ptr(), mine), "ipc handle")
             mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
@@ -247,6 +247,8 @@ def run_gpu(args):
             gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hyper)), "adam step")
         elif exchange == "push":
             gm.check(L.gm_zero1_adam_push_step_async(zero1, lst, C.byref(hyper)), "zero1 push step")
+        elif exchange == "dma":
+            gm.check(L.gm_zero1_adam_dma_step_async(zero1, lst, C.byref(hyper), args.slices), "zero1 dma step")
         else:
             gm.check(L.gm_zero1_adam_step_async(zero1, lst, C.byref(hyper), w_arena.data_ptr(), shard_elems),
                      "zero1 step")
@@ -387,7 +389,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--exchange", choices=["nccl", "push"], default="push")
+    ap.add_argument("--exchange", choices=["nccl", "push", "dma"], default="push")
+    ap.add_argument("--slices", type=int, default=8, help="slices of the shard for --exchange dma")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,

@@ -163,8 +163,15 @@ int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm) {
         if (l->elem_bytes[s] != 4) { set_error("stream %d is not fp32", s); return GM_ERR_BAD_ARG; }
     }
     auto kernel = mta_apply_kernel<Rule>;
-    int grid = launch_grid(d, (const void*)kernel, kApplyThreads, l->dl.num_chunks);
-    kernel<<<grid, kApplyThreads, 0, d->stream>>>(l->dl, prm);
+    DevList dl = l->dl;
+    if (l->win_count >= 0) {                     // a slice of the list: chunks [win_begin, win_begin + win_count)
+        if (l->win_begin < 0 || l->win_begin + l->win_count > dl.num_chunks) { set_error("launch window outside the list"); return GM_ERR_BAD_ARG; }
+        if (l->win_count == 0) return GM_OK;
+        dl.chunk_rec += l->win_begin;
+        dl.num_chunks = l->win_count;
+    }
+    int grid = launch_grid(d, (const void*)kernel, kApplyThreads, dl.num_chunks);
+    kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, prm);
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
     return GM_OK;

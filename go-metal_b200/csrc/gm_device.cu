@@ -324,6 +324,7 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     l->dl.head = (const int*)(b + off_head);
     l->dl.chunk_prefix = (const int*)(b + off_prefix);
     l->dl.chunk_rec = (const int2*)(b + off_rec);
+    l->chunk_prefix = prefix;
     l->dl.num_tensors = nt;
     l->dl.num_chunks = prefix[nt];
     l->dl.chunk_elems = chunk;

@@ -45,6 +45,8 @@ struct TensorList {
     std::vector<int64_t> numel;       // host copy
     std::vector<std::vector<uintptr_t>> ptrs;   // host copy [stream][tensor]
     uint64_t key = 0;                 // cache key (0 = not cached)
+    std::vector<int> chunk_prefix;    // host copy: first chunk of each tensor, [num_tensors+1]
+    int win_begin = 0, win_count = -1; // launch window in chunks (count < 0: the whole list)
 };
 
 struct Device {

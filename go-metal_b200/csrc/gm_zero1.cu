@@ -84,6 +84,10 @@ struct Zero1 {
     bool peer_opened[kMaxPeers] = {false};
     uintptr_t local_base = 0;
     int* barrier_word = nullptr;       // device int used by the closing all-reduce
+    // copy-engine path: one stream per peer, one event per slice, one "done" event per peer
+    cudaStream_t copy_stream[kMaxPeers] = {nullptr};
+    cudaEvent_t copy_done[kMaxPeers] = {nullptr};
+    std::vector<cudaEvent_t> slice_ready;
 };
 
 static std::mutex g_z_mu;
@@ -105,7 +109,10 @@ struct PeerDst {
 
 // Adam over this rank's shard list; every new parameter vector is stored to the
 // local arena and to the same offset of each peer's arena.
-__global__ void __launch_bounds__(kApplyThreads)
+// NP = number of peers, a template parameter so that the store loop unrolls
+// and the peer offsets stay in registers.
+template <int NP>
+__global__ void __launch_bounds__(kApplyThreads, 4)
 zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst peers) {
     constexpr int NS = 4;
     constexpr int NT = kApplyThreads;
@@ -128,7 +135,8 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
             for (int s = 0; s < NS; ++s) x[s] = p[s][i];
             AdamRule::elem(x, prm);
             p[0][i] = x[0]; p[2][i] = x[2]; p[3][i] = x[3];
-            for (int r = 0; r < peers.count; ++r)
+#pragma unroll
+            for (int r = 0; r < NP; ++r)
                 *reinterpret_cast<float*>(reinterpret_cast<char*>(p[0] + i) + peers.delta[r]) = x[0];
         };
 
@@ -157,7 +165,8 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
             *(q[0] + i) = wn;                                            // local copy stays cacheable
             st_stream(q[2] + i, make_float4(x0[2], x1[2], x2[2], x3[2]));
             st_stream(q[3] + i, make_float4(x0[3], x1[3], x2[3], x3[3]));
-            for (int r = 0; r < peers.count; ++r)
+#pragma unroll
+            for (int r = 0; r < NP; ++r)
                 *reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[r]) = wn;
         }
         const long long tb = b + (nvec << 2);
@@ -212,8 +221,12 @@ void gm_zero1_destroy(uintptr_t h) {
     }
     DeviceGuard g(z->dev);
     cudaStreamSynchronize(z->dev->stream);
-    for (int r = 0; r < z->world; ++r)
+    for (int r = 0; r < z->world; ++r) {
+        if (z->copy_stream[r]) { cudaStreamSynchronize(z->copy_stream[r]); cudaStreamDestroy(z->copy_stream[r]); }
+        if (z->copy_done[r]) cudaEventDestroy(z->copy_done[r]);
         if (z->peer_opened[r]) cudaIpcCloseMemHandle((void*)z->peer_base[r]);
+    }
+    for (cudaEvent_t e : z->slice_ready) cudaEventDestroy(e);
     if (z->comm) nccl().CommDestroy(z->comm);
     cudaFree(z->barrier_word);
     delete z;
@@ -270,6 +283,12 @@ int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, ra
     DeviceGuard g(z->dev);
     for (int r = 0; r < z->world; ++r) {
         if (r == z->rank) { z->peer_base[r] = z->local_base; continue; }
+        if (z->peer_opened[r]) {                 // a new arena replaces an earlier mapping
+            cudaStreamSynchronize(z->dev->stream);
+            cudaIpcCloseMemHandle((void*)z->peer_base[r]);
+            z->peer_opened[r] = false;
+            z->peer_base[r] = 0;
+        }
         cudaIpcMemHandle_t mh;
         memcpy(&mh, (const char*)handles + (size_t)r * 64, 64);
         void* p = nullptr;
@@ -290,8 +309,9 @@ int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hy
     Device* d = z->dev;
     PeerDst peers{};
     peers.count = 0;
-    for (int r = 0; r < z->world; ++r) {
-        if (r == z->rank) continue;
+    // rank r stores to r+1, r+2, ... so that at any moment the ranks aim at different peers
+    for (int i = 1; i < z->world; ++i) {
+        const int r = (z->rank + i) % z->world;
         if (!z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
         peers.delta[peers.count++] = (long long)z->peer_base[r] - (long long)z->local_base;
     }
@@ -303,12 +323,90 @@ int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hy
     p.omb1 = 1.0f - hyper->beta1;
     p.omb2 = 1.0f - hyper->beta2;
     DeviceGuard g(d);
-    int grid = launch_grid(d, (const void*)zero1_adam_push_kernel, kApplyThreads, l->dl.num_chunks);
-    zero1_adam_push_kernel<<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers);
+    const int grid = launch_grid(d, nullptr, kApplyThreads, l->dl.num_chunks);
+    switch (peers.count) {
+        case 0: case 1: zero1_adam_push_kernel<1><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        case 2: zero1_adam_push_kernel<2><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        case 3: zero1_adam_push_kernel<3><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        case 4: zero1_adam_push_kernel<4><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        case 5: zero1_adam_push_kernel<5><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        case 6: zero1_adam_push_kernel<6><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+        default: zero1_adam_push_kernel<7><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
+    }
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
     if (z->world > 1) {
         // Completes only after every rank's push kernel has finished.
+        ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, d->stream);
+        if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
+        d->launches++;
+    }
+    return GM_OK;
+}
+
+// Update + exchange with the copy engines: the shard is cut into `num_slices`
+// groups of whole tensors; as soon as the update kernel of a slice has finished,
+// one cudaMemcpyAsync per peer (each on its own stream) copies the slice's new
+// parameters into the same offset of that peer's arena, while the SMs update
+// the next slice.  The step ends, like the push path, with a one-word all-reduce
+// after the device stream has waited for every copy stream.  The shard's
+// parameter tensors must lie back to back in the arena.
+int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper, int num_slices) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams != 4) { set_error("Adam shard list needs w,g,m,v"); return GM_ERR_BAD_ARG; }
+    Device* d = z->dev;
+    const int T = l->dl.num_tensors;
+    if (num_slices < 1) num_slices = 1;
+    if (num_slices > T) num_slices = T;
+    for (int t = 0; t + 1 < T; ++t) {
+        if (l->ptrs[0][t] + (uintptr_t)l->numel[t] * 4 != l->ptrs[0][t + 1]) {
+            set_error("parameter tensors %d and %d are not contiguous in the arena", t, t + 1);
+            return GM_ERR_BAD_ARG;
+        }
+    }
+    for (int r = 0; r < z->world; ++r) {
+        if (r != z->rank && !z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
+    }
+    DeviceGuard g(d);
+    for (int r = 0; r < z->world; ++r) {
+        if (r == z->rank || z->copy_stream[r]) continue;
+        GM_CUDA_CHECK(cudaStreamCreateWithFlags(&z->copy_stream[r], cudaStreamNonBlocking));
+        GM_CUDA_CHECK(cudaEventCreateWithFlags(&z->copy_done[r], cudaEventDisableTiming));
+    }
+    while ((int)z->slice_ready.size() < num_slices) {
+        cudaEvent_t e;
+        GM_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        z->slice_ready.push_back(e);
+    }
+    int rc = GM_OK;
+    for (int s = 0; s < num_slices && rc == GM_OK; ++s) {
+        const int t0 = (int)((long long)T * s / num_slices), t1 = (int)((long long)T * (s + 1) / num_slices);
+        if (t1 <= t0) continue;
+        l->win_begin = l->chunk_prefix[t0];
+        l->win_count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
+        rc = launch_rule(d, GM_RULE_ADAM, l, *hyper);
+        l->win_begin = 0; l->win_count = -1;
+        if (rc != GM_OK) break;
+        GM_CUDA_CHECK(cudaEventRecord(z->slice_ready[s], d->stream));
+        const uintptr_t src = l->ptrs[0][t0];
+        const size_t bytes = (size_t)(l->ptrs[0][t1 - 1] + (uintptr_t)l->numel[t1 - 1] * 4 - src);
+        for (int r = 0; r < z->world; ++r) {
+            if (r == z->rank) continue;
+            const uintptr_t dst = src - z->local_base + z->peer_base[r];
+            GM_CUDA_CHECK(cudaStreamWaitEvent(z->copy_stream[r], z->slice_ready[s], 0));
+            GM_CUDA_CHECK(cudaMemcpyAsync((void*)dst, (const void*)src, bytes, cudaMemcpyDeviceToDevice, z->copy_stream[r]));
+        }
+    }
+    if (rc != GM_OK) return rc;
+    for (int r = 0; r < z->world; ++r) {
+        if (r == z->rank) continue;
+        GM_CUDA_CHECK(cudaEventRecord(z->copy_done[r], z->copy_stream[r]));
+        GM_CUDA_CHECK(cudaStreamWaitEvent(d->stream, z->copy_done[r], 0));
+    }
+    if (z->world > 1) {
         ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, d->stream);
         if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
         d->launches++;

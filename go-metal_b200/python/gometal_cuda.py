@@ -119,6 +119,7 @@ _SIGS = {
     "gm_zero1_ipc_handle": (i, [u, u, vp]),
     "gm_zero1_open_peers": (i, [u, vp]),
     "gm_zero1_adam_push_step_async": (i, [u, u, C.POINTER(Hyper)]),
+    "gm_zero1_adam_dma_step_async": (i, [u, u, C.POINTER(Hyper), i]),
     "gm_timer_start": (i, [u]),
     "gm_timer_stop": (i, [u, C.POINTER(f)]),
 }

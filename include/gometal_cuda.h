@@ -286,6 +286,13 @@ int gm_zero1_world(uintptr_t zero1);
 int gm_zero1_ipc_handle(uintptr_t zero1, uintptr_t arena_base, void* out_handle);
 int gm_zero1_open_peers(uintptr_t zero1, const void* handles);
 int gm_zero1_adam_push_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper);
+/* Update + exchange through the copy engines: the shard is updated in
+ * `num_slices` groups of whole tensors and every finished slice is copied to
+ * the same offset of each peer's arena (one cudaMemcpyAsync per peer and
+ * slice, on per-peer streams) while the next slice is being updated.  Needs
+ * the peer mapping of gm_zero1_open_peers and parameter tensors that lie back
+ * to back in the arena.  Ends with the same one-word all-reduce barrier. */
+int gm_zero1_adam_dma_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper, int num_slices);
 
 /* ---- timing on the device's stream (CUDA events) ---- */
 int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */

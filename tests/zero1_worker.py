@@ -44,7 +44,7 @@ def main():
     assert z, gm.last_error()
     assert L.gm_zero1_rank(z) == rank and L.gm_zero1_world(z) == world
 
-    for exchange in ("nccl", "push"):
+    for exchange in ("nccl", "push", "dma"):
         w0 = O.fill_uniform(T * E, -0.1, 0.1, 91, 1)
         full, fm, fv = w0.copy(), np.zeros(T * E, np.float32), np.zeros(T * E, np.float32)
         arena = dev.to_device(w0)
@@ -54,7 +54,7 @@ def main():
         w_ptrs = [arena + 4 * plan.tensor_offset(k) for k in plan.owned]
         loc = lambda base: [base + 4 * plan.local_offset(k) for k in plan.owned]
         lst = dev.tensor_list([w_ptrs, loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
-        if exchange == "push":
+        if exchange in ("push", "dma"):
             mine = (C.c_ubyte * 64)()
             gm.check(L.gm_zero1_ipc_handle(z, arena, mine), "ipc handle")
             mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
@@ -71,8 +71,10 @@ def main():
             hy = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=step)
             if exchange == "nccl":
                 gm.check(L.gm_zero1_adam_step_async(z, lst, C.byref(hy), arena, plan.shard_elems), "zero1 step")
-            else:
+            elif exchange == "push":
                 gm.check(L.gm_zero1_adam_push_step_async(z, lst, C.byref(hy)), "zero1 push step")
+            else:
+                gm.check(L.gm_zero1_adam_dma_step_async(z, lst, C.byref(hy), 3), "zero1 dma step")
             dev.sync()
             for k in range(T):
                 a = k * E
