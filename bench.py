@@ -12,10 +12,11 @@ state and the gradients are sharded ZeRO-1 style (rank r owns tensors
 fp32 parameters over NVLink, so the total work is fixed (strong scaling).
 
 `value` is timed with CUDA events on the stream the kernels are launched on,
-inputs resident in HBM, max over ranks.  `e2e` times the drop-in C entry
-(execute_adam_step_cuda) with HOST buffers: every step copies that step's
-gradients from pinned host memory to the device and the updated parameters
-back to pinned host memory inside the timed region.
+inputs resident in HBM, max over ranks.  `e2e` times the host-buffer entry
+(gm_step_host): every step copies that step's gradients from pinned host
+memory to the device and the updated parameters back to pinned host memory
+inside the timed region, pipelined slice by slice; the same step through the
+synchronous drop-in entry with plain copies is reported beside it.
 
 `--impl reference` times the CPU restatement of the reference's Adam rule
 (the oracle; the reference itself needs Apple Metal) on the host cores.
@@ -318,7 +319,8 @@ def run_gpu(args):
     shard_bytes = 4 * shard_elems
     w_shard_ptr = w_arena.data_ptr() + 4 * first * TENSOR_ELEMS
 
-    def e2e_step():
+    def e2e_step_dropin():
+        # upload, synchronous drop-in entry, download: nothing overlaps
         step_no[0] += 1
         gm.check(L.gm_buffer_upload_async(dev.h, grads[0].data_ptr(), host_g.data_ptr(), shard_bytes), "h2d")
         rc = L.execute_adam_step_cuda(dev.h, arr["w"], arr["g"], arr["m"], arr["v"], per_rank_tensors, sizes,
@@ -329,17 +331,33 @@ def run_gpu(args):
         gm.check(L.gm_buffer_download_async(dev.h, w_shard_ptr, host_w.data_ptr(), shard_bytes), "d2h")
         dev.sync()
 
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    barrier()
+    def e2e_step_host():
+        # the host-buffer entry: upload, update and download pipelined slice by slice
+        step_no[0] += 1
+        hyper.step = step_no[0]
+        gm.check(L.gm_step_host(dev.h, gm.RULE_ADAM, lists[0], C.byref(hyper), host_g.data_ptr(), host_w.data_ptr(),
+                                args.host_slices), "gm_step_host")
+        if world > 1:
+            gm.check(L.gm_zero1_allgather_async(zero1, w_arena.data_ptr(), shard_elems, 4), "all-gather")
+            dev.sync()
+
+    def time_e2e(fn):
+        fn()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            fn()
+        dt = max_over_ranks(time.perf_counter() - t0)
+        barrier()
+        return dt
+
+    dropin_s = time_e2e(e2e_step_dropin)
+    e2e_s = time_e2e(e2e_step_host)
     e2e = {"value": TOTAL * e2e_steps / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": shard_bytes,
            "d2h_bytes_per_step": shard_bytes, "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
-           "api": "execute_adam_step_cuda (synchronous drop-in entry), pinned host gradients in, "
-                  "updated parameters out"}
+           "api": f"gm_step_host (pinned host gradients in, updated parameters out, {args.host_slices} pipelined slices)",
+           "unpipelined": {"value": TOTAL * e2e_steps / dropin_s / 1e9, "ms_per_step": dropin_s / e2e_steps * 1e3,
+                           "api": "upload + execute_adam_step_cuda (synchronous drop-in entry) + download"}}
 
     return _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks,
                    launches, roofline, e2e, exchange, shard_elems)
@@ -391,6 +409,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--exchange", choices=["nccl", "push", "dma"], default="push")
     ap.add_argument("--slices", type=int, default=8, help="slices of the shard for --exchange dma")
+    ap.add_argument("--host-slices", type=int, default=16, help="pipeline depth of the host-buffer step (e2e)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,

@@ -403,6 +403,9 @@ void destroy_cuda_device(uintptr_t h) {
     if (d->scalars) cudaFree(d->scalars);
     cudaEventDestroy(d->ev_start);
     cudaEventDestroy(d->ev_stop);
+    for (cudaEvent_t e : d->slice_events) cudaEventDestroy(e);
+    if (d->h2d_stream) cudaStreamDestroy(d->h2d_stream);
+    if (d->d2h_stream) cudaStreamDestroy(d->d2h_stream);
     cudaStreamDestroy(d->stream);
     delete d;
 }

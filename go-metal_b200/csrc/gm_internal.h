@@ -55,6 +55,8 @@ struct Device {
     int sm_count = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // host-buffer steps: copies overlap the kernels
+    std::vector<cudaEvent_t> slice_events;
     std::mutex mu;
     std::unordered_map<uint64_t, TensorList*> list_cache;
     int64_t launches = 0;

@@ -256,6 +256,74 @@ int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper
     return GM_OK;
 }
 
+// One optimizer step for a caller whose gradients and parameters live in HOST
+// memory (pinned): the list is cut into `num_slices` groups of whole tensors and
+// the three stages of each slice -- gradients host->device, update kernel,
+// parameters device->host -- run on three streams, so the upload of slice s+1
+// and the download of slice s-1 overlap the update of slice s and both PCIe
+// directions are busy at once.  host_grads / host_params hold the tensors back
+// to back in list order; the device gradient (stream 1) and parameter (stream
+// 0) tensors must be contiguous too.  Synchronous: host_params is complete on return.
+int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, const void* host_grads,
+                 void* host_params, int num_slices) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    TensorList* l = as_list(list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (!hyper || !host_grads || !host_params) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
+    if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams < 2) { set_error("list needs at least the parameter and gradient streams"); return GM_ERR_BAD_ARG; }
+    const int T = l->dl.num_tensors;
+    for (int t = 0; t + 1 < T; ++t) {
+        for (int s = 0; s < 2; ++s) {
+            if (l->ptrs[s][t] + (uintptr_t)l->numel[t] * 4 != l->ptrs[s][t + 1]) {
+                set_error("stream %d tensors %d and %d are not contiguous on the device", s, t, t + 1);
+                return GM_ERR_BAD_ARG;
+            }
+        }
+    }
+    if (num_slices < 1) num_slices = 1;
+    if (num_slices > T) num_slices = T;
+    DeviceGuard guard(d);
+    if (!d->h2d_stream) GM_CUDA_CHECK(cudaStreamCreateWithFlags(&d->h2d_stream, cudaStreamNonBlocking));
+    if (!d->d2h_stream) GM_CUDA_CHECK(cudaStreamCreateWithFlags(&d->d2h_stream, cudaStreamNonBlocking));
+    while ((int)d->slice_events.size() < 2 * num_slices) {
+        cudaEvent_t e;
+        GM_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        d->slice_events.push_back(e);
+    }
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));          // earlier work on the buffers is finished
+    size_t host_off = 0;
+    int rc = GM_OK;
+    for (int s = 0; s < num_slices; ++s) {
+        const int t0 = (int)((long long)T * s / num_slices), t1 = (int)((long long)T * (s + 1) / num_slices);
+        if (t1 <= t0) continue;
+        size_t bytes = 0;
+        for (int t = t0; t < t1; ++t) bytes += (size_t)l->numel[t] * 4;
+        cudaEvent_t in = d->slice_events[2 * s], done = d->slice_events[2 * s + 1];
+        GM_CUDA_CHECK(cudaMemcpyAsync((void*)l->ptrs[1][t0], (const char*)host_grads + host_off, bytes, cudaMemcpyHostToDevice, d->h2d_stream));
+        GM_CUDA_CHECK(cudaEventRecord(in, d->h2d_stream));
+        GM_CUDA_CHECK(cudaStreamWaitEvent(d->stream, in, 0));
+        l->win_begin = l->chunk_prefix[t0];
+        l->win_count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
+        rc = launch_rule(d, rule, l, *hyper);
+        l->win_begin = 0; l->win_count = -1;
+        if (rc != GM_OK) break;
+        GM_CUDA_CHECK(cudaEventRecord(done, d->stream));
+        GM_CUDA_CHECK(cudaStreamWaitEvent(d->d2h_stream, done, 0));
+        GM_CUDA_CHECK(cudaMemcpyAsync((char*)host_params + host_off, (const void*)l->ptrs[0][t0], bytes, cudaMemcpyDeviceToHost, d->d2h_stream));
+        host_off += bytes;
+    }
+    cudaError_t e1 = cudaStreamSynchronize(d->h2d_stream);
+    cudaError_t e2 = cudaStreamSynchronize(d->stream);
+    cudaError_t e3 = cudaStreamSynchronize(d->d2h_stream);
+    if (rc != GM_OK) return rc;
+    if (e1 != cudaSuccess) return cuda_fail(e1, "host step (upload)");
+    if (e2 != cudaSuccess) return cuda_fail(e2, "host step (update)");
+    if (e3 != cudaSuccess) return cuda_fail(e3, "host step (download)");
+    return GM_OK;
+}
+
 int execute_adam_step_cuda(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_t* m, uintptr_t* v,
                            int num_weights, int* buffer_sizes, float lr, float beta1, float beta2,
                            float epsilon, float weight_decay, int step_count) {

@@ -99,6 +99,7 @@ _SIGS = {
     "gm_tensor_list_num_chunks": (i, [u]),
     "gm_step_async": (i, [u, i, u, C.POINTER(Hyper)]),
     "gm_step_timed": (i, [u, i, u, C.POINTER(Hyper), C.POINTER(f)]),
+    "gm_step_host": (i, [u, i, u, C.POINTER(Hyper), vp, vp, i]),
     "gm_mixed_create": (u, [u, C.POINTER(LossScale), f, f, i]),
     "gm_mixed_destroy": (None, [u]),
     "gm_mixed_step_async": (i, [u, u, u, f, f, f]),

@@ -218,6 +218,15 @@ int gm_step_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper
 int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
                   float* elapsed_ms);
 
+/* One step for a caller whose gradients and parameters live in pinned HOST
+ * memory: gradients are uploaded, the rule is applied and the new parameters
+ * are downloaded slice by slice on three streams, so both PCIe directions and
+ * the SMs are busy at once.  host_grads / host_params hold the tensors back to
+ * back in list order; stream 0 (parameters) and stream 1 (gradients) of the
+ * list must be contiguous on the device.  Synchronous. */
+int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
+                 const void* host_grads, void* host_params, int num_slices);
+
 /* ---- mixed-precision Adam with a device-resident dynamic loss scale ---- */
 typedef struct {
     float scale, growth, backoff, max_scale;

@@ -286,3 +286,49 @@ def test_convert_roundtrip(gm, dev, oracle):
     assert gm.lib.convert_tensor_type_cuda(src, dst, shape, 1, 0, 1, dev.h) == -11
     for p in (src, dst, back):
         dev.free(p)
+
+
+def test_host_buffer_step_matches_oracle(gm, dev, oracle):
+    """gm_step_host: gradients come from (pinned) host memory and the new parameters
+    return to host memory, pipelined over slices; the result equals the oracle's and
+    the device copies agree with what was downloaded."""
+    import ctypes as C
+    O, L = oracle, gm.lib
+    sizes = [5000, 12, 70001, 4096, 333]
+    n = sum(sizes)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    w = O.fill_uniform(n, -0.2, 0.2, 61, 1)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dw, dg, dm, dv = dev.to_device(w), dev.alloc(4 * n), dev.to_device(m), dev.to_device(v)
+    ptrs = lambda base: [base + 4 * int(o) for o in offs]
+    lst = dev.tensor_list([ptrs(dw), ptrs(dg), ptrs(dm), ptrs(dv)], sizes)
+    hg = L.gm_host_alloc_pinned(4 * n)
+    hw = L.gm_host_alloc_pinned(4 * n)
+    assert hg and hw
+    hg_arr = np.ctypeslib.as_array(C.cast(hg, C.POINTER(C.c_float)), shape=(n,))
+    hw_arr = np.ctypeslib.as_array(C.cast(hw, C.POINTER(C.c_float)), shape=(n,))
+    try:
+        for step, slices in [(1, 1), (2, 3), (3, 5), (4, 64)]:
+            g = O.fill_normal(n, 0.0, 0.01, 61, 10 + step)
+            hg_arr[:] = g
+            hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=step)
+            gm.check(L.gm_step_host(dev.h, gm.RULE_ADAM, lst, C.byref(hy), hg, hw, slices), "gm_step_host")
+            for o, k in zip(offs, sizes):
+                sl = slice(int(o), int(o) + k)
+                ws, ms, vs = (np.ascontiguousarray(x[sl]) for x in (w, m, v))
+                O.adam_step(ws, np.ascontiguousarray(g[sl]), ms, vs, 1e-3, 0.9, 0.999, 1e-8, 0.0, step)
+                w[sl], m[sl], v[sl] = ws, ms, vs
+            assert np.array_equal(hw_arr.view(np.uint32), w.view(np.uint32)), f"step {step}: downloaded parameters"
+            assert np.array_equal(dev.to_host(dw, n).view(np.uint32), w.view(np.uint32)), f"step {step}: device parameters"
+        assert np.array_equal(dev.to_host(dv, n).view(np.uint32), v.view(np.uint32))
+        # non-contiguous device tensors are refused
+        bad = dev.tensor_list([[dw, dw + 4 * 6000], [dg, dg + 4 * 6000], [dm, dm + 4 * 6000], [dv, dv + 4 * 6000]], [5000, 100])
+        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
+        assert L.gm_step_host(dev.h, gm.RULE_ADAM, bad, C.byref(hy), hg, hw, 2) == -10
+        L.gm_tensor_list_destroy(bad)
+    finally:
+        L.gm_tensor_list_destroy(lst)
+        L.gm_host_free_pinned(hg)
+        L.gm_host_free_pinned(hw)
+        for p in (dw, dg, dm, dv):
+            dev.free(p)
