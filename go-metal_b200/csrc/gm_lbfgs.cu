@@ -193,6 +193,35 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
                     return add(d_old, mul(coef, g_or_vec));
                 };
                 const bool writes = op.kind == 0 || !skip_axpy;
+                constexpr int PASSES = kDotChunk / (kDotThreads * 4);
+                if (vec_ok && base + kDotChunk <= n) {
+                    // whole, aligned chunk: every load of the chunk is issued before the
+                    // first store, so the 12 vectors per thread are in flight together
+                    float4 d4[PASSES], v4[PASSES], o4[PASSES];
+#pragma unroll
+                    for (int i = 0; i < PASSES; ++i) {
+                        const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
+                        if (op.kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(g + e0));
+                        else d4[i] = *reinterpret_cast<const float4*>(dir + e0);
+                        if (op.kind != 0 && !skip_axpy) v4[i] = __ldcs(reinterpret_cast<const float4*>(vec + e0));
+                        if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(dv + e0));
+                    }
+#pragma unroll
+                    for (int i = 0; i < PASSES; ++i) {
+                        const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
+                        if (op.kind == 0) {
+                            if (!op.descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
+                        } else if (!skip_axpy) {
+                            d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
+                                                new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
+                        }
+                        if (writes) *reinterpret_cast<float4*>(dir + e0) = d4[i];
+                        if (want_dot) {
+                            acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
+                            acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
+                        }
+                    }
+                } else
 #pragma unroll
                 for (int i = 0; i < kDotChunk / (kDotThreads * 4); ++i) {
                     const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;

@@ -76,6 +76,11 @@ def case_rules(dev, reps, small):
         ("sgd_plain", gm.RULE_SGD, ["w", "g"], 12, dict(lr=0.01, beta1=0.0)),
     ]
     for name, rule, streams, bpp, hp in rules:
+        # fresh parameters and zero state for every rule: one rule's state is not a
+        # valid state of the next (a negative first moment is no squared average)
+        fill(dev, buf["w"], n, 0.05, 1)
+        for k in ("s1", "s2", "s3"):
+            gm.check(L.gm_buffer_zero(dev.h, buf[k], 4 * n), "zero")
         lst = dev.tensor_list([ptrs[k] for k in streams], [per] * nt)
         hy = gm.Hyper(step=1, **hp)
         state = {"t": 0}
