@@ -110,6 +110,10 @@ int ensure_partials(Device* d, int64_t count);
 // ---- rule launchers (gm_rules.cu) ----
 int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h);
 
+// ---- mixed precision (gm_mixed.cu) ----
+int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd,
+                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx);
+
 // ---- buffer registry (gm_device.cu) ----
 int64_t registered_size(uintptr_t p);   // -1 if unknown
 int registered_ordinal(uintptr_t p);    // -1 if unknown

@@ -138,6 +138,21 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
     }
 }
 
+// Recomputes the published scalars after the overflow flag has been combined
+// across ranks (sharded gradients: every rank must take the same decision).
+__global__ void mixed_prep_kernel(const unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
+                                  const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int tstep = state->adam_t + 1;
+    const float2 bc = table[tstep < table_len ? tstep : table_len];
+    StepPrep sp;
+    sp.overflow = flag[0] != 0u ? 1u : 0u;
+    sp.inv_scale = dvd(1.0f, state->scale);
+    sp.bc1 = bc.x;
+    sp.bc2 = bc.y;
+    *prep = sp;
+}
+
 struct MixedScalars { float lr, beta1, beta2, omb1, omb2, eps, wd; int use_wd; };
 
 __device__ __forceinline__ void mixed_elem(float g16_as_f32, float inv_scale, float& w, float& m, float& v,
@@ -303,6 +318,51 @@ sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
     }
 }
 
+// One mixed-precision step.  `hook`, when given, runs between the check and the
+// update kernels with the device address of the overflow word, so that a sharded
+// caller can combine the flag across ranks on the same stream.
+int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd,
+                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    TensorList* l = as_list(list);
+    if (!m || !l) return GM_ERR_BAD_ARG;
+    if (m->dev != d || l->dev != d) { set_error("handles belong to different devices"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams != 5 || l->elem_bytes[0] != 2 || l->elem_bytes[1] != 4 || l->elem_bytes[2] != 4
+        || l->elem_bytes[3] != 4 || l->elem_bytes[4] != 2) {
+        set_error("mixed-precision list must be g16(2B), master, m, v (4B), p16(2B)");
+        return GM_ERR_BAD_ARG;
+    }
+    // The device counter can be at most `calls` before this step; make sure the
+    // table reaches calls+1 unless its tail is already constant.
+    if (!m->saturated && m->calls + 1 > m->table_len) {
+        int rc = upload_table(m, m->table_len * 2);
+        if (rc != GM_OK) return rc;
+    }
+    m->calls += 1;
+    MixedScalars sc;
+    sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
+    sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
+    DeviceGuard g(d);
+    int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
+    StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
+    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
+                                                                m->table_len, prep);
+    d->launches++;
+    if (hook) {
+        int rc = hook(ctx, m->d_flag);
+        if (rc != GM_OK) return rc;
+        mixed_prep_kernel<<<1, 32, 0, d->stream>>>(m->d_flag, m->d_state, m->d_table, m->table_len, prep);
+        d->launches++;
+    }
+    int grid_u = launch_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
+    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    return GM_OK;
+}
+
 }  // namespace gm
 
 using namespace gm;
@@ -365,37 +425,7 @@ void gm_mixed_destroy(uintptr_t h) {
 }
 
 int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd) {
-    Device* d = as_device(device_ptr);
-    if (!d) return GM_ERR_NIL_DEVICE;
-    Mixed* m = as_mixed(mixed);
-    TensorList* l = as_list(list);
-    if (!m || !l) return GM_ERR_BAD_ARG;
-    if (m->dev != d || l->dev != d) { set_error("handles belong to different devices"); return GM_ERR_BAD_ARG; }
-    if (l->dl.num_streams != 5 || l->elem_bytes[0] != 2 || l->elem_bytes[1] != 4 || l->elem_bytes[2] != 4
-        || l->elem_bytes[3] != 4 || l->elem_bytes[4] != 2) {
-        set_error("mixed-precision list must be g16(2B), master, m, v (4B), p16(2B)");
-        return GM_ERR_BAD_ARG;
-    }
-    // The device counter can be at most `calls` before this step; make sure the
-    // table reaches calls+1 unless its tail is already constant.
-    if (!m->saturated && m->calls + 1 > m->table_len) {
-        int rc = upload_table(m, m->table_len * 2);
-        if (rc != GM_OK) return rc;
-    }
-    m->calls += 1;
-    MixedScalars sc;
-    sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
-    sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
-    DeviceGuard g(d);
-    int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
-    StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
-    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                m->table_len, prep);
-    int grid_u = launch_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
-    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
-    d->launches += 2;
-    GM_CUDA_CHECK(cudaGetLastError());
-    return GM_OK;
+    return gm::mixed_step_with_hook(device_ptr, mixed, list, lr, eps, wd, nullptr, nullptr);
 }
 
 int gm_mixed_get_state(uintptr_t device_ptr, uintptr_t mixed, gm_loss_scale_t* out) {

@@ -414,4 +414,26 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
     return GM_OK;
 }
 
+// Mixed-precision Adam on sharded fp16 gradients: the overflow flag of every
+// rank's shard is summed across ranks between the check and the update, so all
+// ranks skip or step together and their loss-scale states stay identical; the
+// fp16 parameter copies are then all-gathered in place.
+static int zero1_flag_hook(void* ctx, unsigned int* d_flag) {
+    Zero1* z = static_cast<Zero1*>(ctx);
+    if (z->world == 1) return GM_OK;
+    ncclResult_t r = nccl().AllReduce(d_flag, d_flag, 1, kNcclInt32, kNcclSum, z->comm, z->dev->stream);
+    if (r != 0) return nccl_fail(r, "ncclAllReduce(overflow flag)");
+    z->dev->launches++;
+    return GM_OK;
+}
+
+int gm_zero1_mixed_step_async(uintptr_t h, uintptr_t mixed, uintptr_t shard_list, float lr, float eps, float wd,
+                              uintptr_t p16_arena_base, int64_t count_per_rank) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    int rc = mixed_step_with_hook((uintptr_t)z->dev, mixed, shard_list, lr, eps, wd, zero1_flag_hook, z);
+    if (rc != GM_OK) return rc;
+    return gm_zero1_allgather_async(h, p16_arena_base, count_per_rank, 2);
+}
+
 }  // extern "C"

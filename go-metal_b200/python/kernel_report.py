@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Per-kernel throughput report for libgometal_cuda.so (CUDA-event timed).
 
-    python go-metal_b200/python/kernel_report.py --case rules|mixed|lbfgs [--reps N] [--small]
+    python go-metal_b200/python/kernel_report.py --case rules|mixed|lbfgs|small [--reps N] [--small]
 
 Prints one JSON line per measured kernel: time per step, algorithmic GB/s
 (bytes per parameter x parameters / time) and Gparams/s.  Inputs are seeded
@@ -12,6 +12,9 @@ for profiler captures (nothing here is timed under a profiler).
   mixed  mixed-precision Adam on 25,165,824 parameters in 48 ragged tensors
          packed back to back (tensor starts off the 16-byte boundary)
   lbfgs  L-BFGS, history 10, n = 10,000,000, once the history is full
+  small  the two small models (MLP 101,770 parameters in 4 tensors, CNN 545,098 in
+         8): latency of one step through the synchronous drop-in entry (host wall
+         clock) and through the asynchronous entry (CUDA events, back to back)
 """
 from __future__ import annotations
 
@@ -168,6 +171,47 @@ def case_lbfgs(dev, reps, small):
          bytes_per_element=bpe, gbs=bpe * n / ms / 1e6, note="host wall clock around the synchronous drop-in entry")
 
 
+def case_small(dev, reps, small):
+    models = {"mlp_4_tensors": [100352, 128, 1280, 10],
+              "cnn_8_tensors": [864, 32, 18432, 64, 524288, 128, 1280, 10]}
+    for name, sizes in models.items():
+        n = sum(sizes)
+        bufs = {k: [_zeros(dev, s) for s in sizes] for k in "wgmv"}
+        for p, s in zip(bufs["g"], sizes):
+            dev.upload(p, (np.random.default_rng(s).standard_normal(s) * 0.01).astype(np.float32))
+        arr = {k: gm.uarray(bufs[k]) for k in "wgmv"}
+        sz = gm.iarray([4 * s for s in sizes])
+        step = [0]
+
+        def dropin():
+            step[0] += 1
+            gm.check(L.execute_adam_step_cuda(dev.h, arr["w"], arr["g"], arr["m"], arr["v"], len(sizes), sz,
+                                              1e-3, 0.9, 0.999, 1e-8, 0.0, step[0]), "adam")
+
+        for _ in range(10):
+            dropin()
+        t0 = time.perf_counter()
+        for _ in range(max(reps, 200)):
+            dropin()
+        wall_us = (time.perf_counter() - t0) / max(reps, 200) * 1e6
+        lst = dev.tensor_list([bufs[k] for k in "wgmv"], sizes)
+        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
+
+        def async_step():
+            step[0] += 1
+            hy.step = step[0]
+            gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy)), "adam")
+
+        ms = timed(dev, async_step, max(reps, 200), warm=10)
+        emit(kernel=f"mta_apply_kernel<adam> {name}", params=n, dropin_sync_us_per_step=wall_us,
+             async_us_per_step=ms * 1e3, bytes_per_step=28 * n,
+             note="L2-resident and launch-bound; a bandwidth fraction is not meaningful at this size")
+        L.gm_tensor_list_destroy(lst)
+        for k in "wgmv":
+            for p in bufs[k]:
+                dev.free(p)
+
+
 def _zeros(dev, k):
     p = dev.alloc(4 * k)
     gm.check(L.gm_buffer_zero(dev.h, p, 4 * k), "zero")
@@ -176,13 +220,13 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "lbfgs"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "lbfgs", "small"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
-        {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs}[args.case](dev, args.reps, args.small)
+        {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small}[args.case](dev, args.reps, args.small)
     finally:
         dev.close()
 

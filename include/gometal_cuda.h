@@ -303,6 +303,13 @@ int gm_zero1_adam_push_step_async(uintptr_t zero1, uintptr_t shard_list, const g
  * to back in the arena.  Ends with the same one-word all-reduce barrier. */
 int gm_zero1_adam_dma_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper, int num_slices);
 
+/* Mixed-precision Adam over sharded fp16 gradients: the overflow flags of all
+ * ranks are summed between the check and the update (one-word all-reduce on the
+ * stream), so every rank takes the same skip/step decision and keeps the same
+ * loss-scale state; then the fp16 parameter arena is all-gathered in place. */
+int gm_zero1_mixed_step_async(uintptr_t zero1, uintptr_t mixed, uintptr_t shard_list, float lr, float eps,
+                              float weight_decay, uintptr_t p16_arena_base, int64_t count_per_rank);
+
 /* ---- timing on the device's stream (CUDA events) ---- */
 int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */
 int gm_timer_stop(uintptr_t device_ptr, float* elapsed_ms);/* records the stop event, waits, reports */

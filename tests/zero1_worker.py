@@ -96,12 +96,61 @@ def main():
         if exchange == "nccl":
             dev.free(arena)
         # the pushed arena stays mapped by the peers until the group is destroyed
+    mixed_zero1(L, dev, z, plan, rank)
     dist.barrier()
     L.gm_zero1_destroy(z)
     dist.barrier()
     dev.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
+
+
+def mixed_zero1(L, dev, z, plan, rank):
+    """Mixed-precision Adam with sharded fp16 gradients: an overflow in ONE rank's shard
+    must make every rank skip; states, master shards and the gathered fp16 arena
+    must equal the oracle's run over all tensors."""
+    sizes = [E] * T
+    master = [O.fill_uniform(E, -0.05, 0.05, 93, k) for k in range(T)]
+    mm = [np.zeros(E, np.float32) for _ in range(T)]
+    vv = [np.zeros(E, np.float32) for _ in range(T)]
+    p16 = [O.f32_to_f16(a) for a in master]
+    st = O.new_loss_scale(interval=2)
+    own = list(plan.owned)
+    p16_arena = dev.to_device(np.concatenate(p16))
+    d_master = dev.to_device(np.concatenate([master[k] for k in own]))
+    d_m = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+    d_v = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+    d_g = dev.alloc(2 * plan.shard_elems)
+    loc = lambda base, eb: [base + eb * plan.local_offset(k) for k in own]
+    p_ptrs = [p16_arena + 2 * plan.tensor_offset(k) for k in own]
+    lst = dev.tensor_list([loc(d_g, 2), loc(d_master, 4), loc(d_m, 4), loc(d_v, 4), p_ptrs], [E] * len(own), [2, 4, 4, 4, 2])
+    init = gm.LossScale(scale=st.scale, growth=st.growth, backoff=st.backoff, max_scale=st.max_scale, interval=2,
+                        good_steps=0, adam_t=0, skipped=0, last_overflow=0)
+    mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
+    assert mx, gm.last_error()
+    for step in range(1, 6):
+        g16 = [O.f32_to_f16(O.fill_normal(E, 0.0, 1e-3, 93, 100 * step + k) * np.float32(st.scale)) for k in range(T)]
+        if step == 2:
+            g16[0][17] = 0x7c00                  # +inf in rank 0's shard only
+        dev.upload(d_g, np.concatenate([g16[k] for k in own]))
+        dist.barrier()
+        gm.check(L.gm_zero1_mixed_step_async(z, mx, lst, LR, EPS, WD, p16_arena, plan.shard_elems), "zero1 mixed step")
+        O.mixed_adam_step(g16, master, mm, vv, p16, LR, B1, B2, EPS, WD, st)
+        got = gm.LossScale()
+        gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(got)), "state")
+        assert (got.scale, got.good_steps, got.adam_t, got.skipped, got.last_overflow) == \
+               (st.scale, st.good_steps, st.adam_t, st.skipped, st.last_overflow), f"rank {rank} step {step}: state differs"
+        arena = dev.to_host(p16_arena, T * E, np.uint16)
+        assert np.array_equal(arena, np.concatenate(p16)), f"rank {rank} step {step}: gathered fp16 parameters differ"
+        shard = dev.to_host(d_master, plan.shard_elems)
+        want = np.concatenate([master[k] for k in own])
+        assert np.array_equal(shard.view(np.uint32), want.view(np.uint32)), f"rank {rank} step {step}: master shard differs"
+        dist.barrier()
+    assert st.skipped == 1
+    L.gm_mixed_destroy(mx)
+    L.gm_tensor_list_destroy(lst)
+    for p in (p16_arena, d_master, d_m, d_v, d_g):
+        dev.free(p)
 
 
 if __name__ == "__main__":
