@@ -37,6 +37,9 @@ namespace gm {
 
 constexpr int kDotChunk = 4096;
 constexpr int kDotThreads = 256;
+#ifndef GM_LBFGS_MINB
+#define GM_LBFGS_MINB 3          // resident CTAs per SM the pass kernel is compiled for (4 would spill)
+#endif
 
 struct LbfgsTable {
     const unsigned long long* ptrs;   // [ncols][T]
@@ -86,7 +89,7 @@ __device__ __forceinline__ float cta_reduce_256(float acc, float* warp_sum) {
     return total;
 }
 
-__global__ void __launch_bounds__(kDotThreads)
+__global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
 lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
                   unsigned int* __restrict__ ticket) {
     __shared__ float warp_sum[kDotThreads / 32];

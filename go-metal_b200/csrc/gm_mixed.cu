@@ -104,12 +104,16 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
         if (k == 0 && tid < h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
         const long long nvec = (e - b) >> 3;
         const uint4* q = reinterpret_cast<const uint4*>(g + b);
-        for (long long i = tid; i < nvec; i += 2 * NT) {                 // two loads in flight per thread
-            const uint4 v = __ldg(q + i);
-            uint4 u = make_uint4(0u, 0u, 0u, 0u);
-            if (i + NT < nvec) u = __ldg(q + i + NT);
-            bad |= nonfinite_mask(v.x) | nonfinite_mask(v.y) | nonfinite_mask(v.z) | nonfinite_mask(v.w);
-            bad |= nonfinite_mask(u.x) | nonfinite_mask(u.y) | nonfinite_mask(u.z) | nonfinite_mask(u.w);
+        for (long long i = tid; i < nvec; i += 4 * NT) {                 // four loads in flight per thread
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i + u * NT < nvec) v[u] = __ldg(q + i + u * NT);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
         }
         const long long tb = b + (nvec << 3);
         if (tb + tid < e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
