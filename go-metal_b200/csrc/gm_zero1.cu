@@ -42,6 +42,7 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
 };
@@ -61,6 +62,7 @@ static NcclApi& nccl() {
         api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
         api.AllGather = (decltype(api.AllGather))dlsym(api.handle, "ncclAllGather");
         api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+        api.ReduceScatter = (decltype(api.ReduceScatter))dlsym(api.handle, "ncclReduceScatter");
         api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
         api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.AllReduce
                  && api.GetErrorString;
@@ -434,6 +436,27 @@ int gm_zero1_mixed_step_async(uintptr_t h, uintptr_t mixed, uintptr_t shard_list
     int rc = mixed_step_with_hook((uintptr_t)z->dev, mixed, shard_list, lr, eps, wd, zero1_flag_hook, z);
     if (rc != GM_OK) return rc;
     return gm_zero1_allgather_async(h, p16_arena_base, count_per_rank, 2);
+}
+
+// Gradient hand-off for data-parallel training: every rank holds a full gradient
+// arena of its own micro-batch; after the call rank r's shard
+// [r*count, (r+1)*count) holds the SUM over ranks (in place), which is what the
+// sharded update consumes.  The summation order inside NCCL is not specified,
+// so results are reproducible run to run on one topology but not bit-defined.
+int gm_zero1_reduce_scatter_async(uintptr_t h, uintptr_t grad_arena_base, int64_t count, int elem_bytes) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    if (!grad_arena_base) { set_error("arena is nil"); return GM_ERR_NIL_BUFFER; }
+    if (count <= 0 || (elem_bytes != 2 && elem_bytes != 4)) { set_error("bad count/element size"); return GM_ERR_BAD_SIZE; }
+    if (z->world == 1) return GM_OK;
+    if (!nccl().ReduceScatter) { set_error("ncclReduceScatter is not available"); return GM_ERR_UNSUPPORTED; }
+    DeviceGuard g(z->dev);
+    char* recv = (char*)grad_arena_base + (size_t)z->rank * count * elem_bytes;
+    ncclResult_t r = nccl().ReduceScatter((const void*)grad_arena_base, recv, (size_t)count,
+                                          elem_bytes == 4 ? kNcclFloat32 : kNcclFloat16, kNcclSum, z->comm, z->dev->stream);
+    if (r != 0) return nccl_fail(r, "ncclReduceScatter");
+    z->dev->launches++;
+    return GM_OK;
 }
 
 }  // extern "C"

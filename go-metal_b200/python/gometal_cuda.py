@@ -122,6 +122,7 @@ _SIGS = {
     "gm_zero1_adam_push_step_async": (i, [u, u, C.POINTER(Hyper)]),
     "gm_zero1_adam_dma_step_async": (i, [u, u, C.POINTER(Hyper), i]),
     "gm_zero1_mixed_step_async": (i, [u, u, u, f, f, f, u, i64]),
+    "gm_zero1_reduce_scatter_async": (i, [u, u, i64, i]),
     "gm_timer_start": (i, [u]),
     "gm_timer_stop": (i, [u, C.POINTER(f)]),
 }

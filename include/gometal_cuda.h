@@ -310,6 +310,10 @@ int gm_zero1_adam_dma_step_async(uintptr_t zero1, uintptr_t shard_list, const gm
 int gm_zero1_mixed_step_async(uintptr_t zero1, uintptr_t mixed, uintptr_t shard_list, float lr, float eps,
                               float weight_decay, uintptr_t p16_arena_base, int64_t count_per_rank);
 
+/* Gradient hand-off of data-parallel training: in-place reduce-scatter (sum) of
+ * the full gradient arena; afterwards rank r's shard holds the sum over ranks. */
+int gm_zero1_reduce_scatter_async(uintptr_t zero1, uintptr_t grad_arena_base, int64_t count_per_rank, int elem_bytes);
+
 /* ---- timing on the device's stream (CUDA events) ---- */
 int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */
 int gm_timer_stop(uintptr_t device_ptr, float* elapsed_ms);/* records the stop event, waits, reports */

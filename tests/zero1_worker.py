@@ -97,12 +97,29 @@ def main():
             dev.free(arena)
         # the pushed arena stays mapped by the peers until the group is destroyed
     mixed_zero1(L, dev, z, plan, rank)
+    reduce_scatter(L, dev, z, plan, rank, world)
     dist.barrier()
     L.gm_zero1_destroy(z)
     dist.barrier()
     dev.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
+
+
+def reduce_scatter(L, dev, z, plan, rank, world):
+    """Gradient hand-off: small-integer-valued gradients make the cross-rank sum exact
+    whatever order NCCL adds in, so the shard can be compared bit for bit."""
+    n = T * E
+    mine = ((np.arange(n, dtype=np.int64) * (rank + 3)) % 17 - 8).astype(np.float32)
+    arena = dev.to_device(mine)
+    gm.check(L.gm_zero1_reduce_scatter_async(z, arena, plan.shard_elems, 4), "reduce-scatter")
+    got = dev.to_host(arena, n)[plan.shard_offset:plan.shard_offset + plan.shard_elems]
+    idx = np.arange(plan.shard_offset, plan.shard_offset + plan.shard_elems, dtype=np.int64)
+    want = np.zeros(plan.shard_elems, np.float32)
+    for r in range(world):
+        want += ((idx * (r + 3)) % 17 - 8).astype(np.float32)
+    assert np.array_equal(got, want), f"rank {rank}: reduce-scattered gradient shard differs"
+    dev.free(arena)
 
 
 def mixed_zero1(L, dev, z, plan, rank):
