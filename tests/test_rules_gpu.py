@@ -250,6 +250,48 @@ def test_misaligned_views_inside_an_arena(gm, dev, oracle):
         L.gm_arena_destroy(arena)
 
 
+def test_equal_tensors_inside_an_arena(gm, dev, oracle):
+    """Seven tensors of one size (12291 elements: three chunks and a ragged tail),
+    each starting 3 elements before a 16-byte boundary, through the drop-in Adam
+    entry with weight decay."""
+    O, L = oracle, gm.lib
+    nt, each = 7, 12291
+    stride = each + 1                                   # keeps every start at 16k + 4 bytes
+    assert (stride * 4) % 16 == 0
+    total = nt * stride + 8
+    offs = [1 + i * stride for i in range(nt)]
+    host = {k: np.zeros(total, dtype=np.float32) for k in "wgmv"}
+    host["w"][:] = O.fill_uniform(total, -1.0, 1.0, 9, 1)
+    base = {k: dev.to_device(host[k]) for k in "wgmv"}
+    ptrs = {k: [base[k] + 4 * o for o in offs] for k in "wgmv"}
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.999, 1e-8, 0.01
+
+    def expect(step):
+        want = {k: host[k].copy() for k in "wmv"}
+        for o in offs:
+            sl = slice(o, o + each)
+            w, m, v = (np.ascontiguousarray(want[k][sl]) for k in "wmv")
+            O.adam_step(w, np.ascontiguousarray(host["g"][sl]), m, v, lr, b1, b2, eps, wd, step)
+            want["w"][sl], want["m"][sl], want["v"][sl] = w, m, v
+        return want
+
+    try:
+        for step in range(1, 4):
+            host["g"][:] = O.fill_normal(total, 0.0, 0.01, 9, 10 + step)
+            dev.upload(base["g"], host["g"])
+            rc = L.execute_adam_step_cuda(dev.h, gm.uarray(ptrs["w"]), gm.uarray(ptrs["g"]), gm.uarray(ptrs["m"]),
+                                          gm.uarray(ptrs["v"]), nt, gm.iarray([4 * each] * nt), lr, b1, b2, eps, wd, step)
+            assert rc == 0, gm.last_error()
+            want = expect(step)
+            for k in "wmv":
+                got = dev.to_host(base[k], total)
+                assert np.array_equal(got.view(np.uint32), want[k].view(np.uint32)), f"stream {k} step {step}"
+                host[k] = got
+    finally:
+        for k in "wgmv":
+            dev.free(base[k])
+
+
 def test_error_codes(gm, dev):
     L = gm.lib
     p = L.allocate_cuda_buffer(dev.h, 64, 1)
@@ -288,13 +330,14 @@ def test_convert_roundtrip(gm, dev, oracle):
         dev.free(p)
 
 
-def test_host_buffer_step_matches_oracle(gm, dev, oracle):
+@pytest.mark.parametrize("sizes", [[5000, 12, 70001, 4096, 333], [12288] * 6], ids=["ragged", "equal"])
+def test_host_buffer_step_matches_oracle(gm, dev, oracle, sizes):
     """gm_step_host: gradients come from (pinned) host memory and the new parameters
     return to host memory, pipelined over slices; the result equals the oracle's and
-    the device copies agree with what was downloaded."""
+    the device copies agree with what was downloaded.  With equal tensors the slice
+    boundaries fall on tensor boundaries (1, 3 slices) or inside tensors (5, 64)."""
     import ctypes as C
     O, L = oracle, gm.lib
-    sizes = [5000, 12, 70001, 4096, 333]
     n = sum(sizes)
     offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
     w = O.fill_uniform(n, -0.2, 0.2, 61, 1)
