@@ -89,6 +89,43 @@ __device__ __forceinline__ float cta_reduce_256(float acc, float* warp_sum) {
     return total;
 }
 
+// The CTA that takes the last ticket sees every chunk sum, finishes the
+// reduction in the fixed order and applies the epilogue to the scalar.
+__device__ __forceinline__ void finish_pass(const LbfgsTable& tb, const LbfgsOp& op, const bool have_dot,
+                                            float* partials, unsigned int* ticket, float* warp_sum, int* is_last) {
+    if (op.epilogue == 0) return;
+    const int tid = threadIdx.x;
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned my = atomicAdd(ticket, 1u);
+        *is_last = (my == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    __threadfence();
+
+    float dot = 0.0f;
+    if (have_dot) {
+        float acc = 0.0f;
+        const volatile float* pv = partials;
+        for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, pv[c]);
+        dot = cta_reduce_256(acc, warp_sum);
+    }
+    if (tid == 0) {
+        float r = 0.0f;
+        switch (op.epilogue) {
+            case 1: r = have_dot ? mul(dot, *op.rho_dot) : 0.0f; break;                         // alpha_j
+            case 2: r = have_dot ? sub(*op.alpha_in, mul(dot, *op.rho_dot)) : 0.0f; break;      // alpha_j - beta
+            case 3: r = (op.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
+            default: r = dot; break;
+        }
+        *op.out = r;
+        *ticket = 0u;
+        __threadfence();
+    }
+}
+
 __global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
 lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
                   unsigned int* __restrict__ ticket) {
@@ -97,12 +134,10 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
     const int tid = threadIdx.x;
     const int T = tb.T;
 
-    const bool skip_axpy = (op.kind == 1 || op.kind == 2) && rho_skips(op.rho_axpy);
+    // kinds 3 (final update) and 4 (plain dot); kinds 0..2 run in lbfgs_axpy_dot_kernel
     const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot) && (op.kind != 3 || op.have_pair);
-    const float coef = (op.kind == 1 || op.kind == 2) ? *op.coef : 0.0f;
-    const bool touches_data = op.kind == 0 || op.kind == 3 || op.kind == 4 || !skip_axpy || want_dot;
 
-    if (touches_data) {
+    {
         for (int c = blockIdx.x; c < tb.num_chunks; c += gridDim.x) {
             const int t = find_tensor(tb.chunk_prefix, T, c);
             const long long n = __ldg(tb.numel + t);
@@ -129,7 +164,7 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
                         for (int k = 0; k < 4; ++k) if (e0 + k < n) acc = add(acc, mul(a[e0 + k], b[e0 + k]));
                     }
                 }
-            } else if (op.kind == 3) {
+            } else {
                 float* x = col(COL_W);
                 const float* g = col(COL_G);
                 float* og = col(COL_OLDG);
@@ -185,80 +220,6 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
                         for (int k = 0; k < 4; ++k) if (e0 + k < n) one(e0 + k);
                     }
                 }
-            } else {
-                // kinds 0,1,2: produce the new direction, optionally dot it with col_dot
-                const float* g = op.kind == 0 ? col(COL_G) : nullptr;
-                const float* vec = (op.kind != 0 && !skip_axpy) ? col(op.col_axpy) : nullptr;
-                const float* dv = want_dot ? col(op.col_dot) : nullptr;
-                auto new_dir = [&](float d_old, float g_or_vec) -> float {
-                    if (op.kind == 0) return op.descent ? g_or_vec : -g_or_vec;
-                    if (op.kind == 1) return sub(d_old, mul(coef, g_or_vec));
-                    return add(d_old, mul(coef, g_or_vec));
-                };
-                const bool writes = op.kind == 0 || !skip_axpy;
-                constexpr int PASSES = kDotChunk / (kDotThreads * 4);
-                if (vec_ok && base + kDotChunk <= n) {
-                    // whole, aligned chunk: every load of the chunk is issued before the
-                    // first store, so the 12 vectors per thread are in flight together
-                    float4 d4[PASSES], v4[PASSES], o4[PASSES];
-#pragma unroll
-                    for (int i = 0; i < PASSES; ++i) {
-                        const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
-                        if (op.kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(g + e0));
-                        else d4[i] = *reinterpret_cast<const float4*>(dir + e0);
-                        if (op.kind != 0 && !skip_axpy) v4[i] = __ldcs(reinterpret_cast<const float4*>(vec + e0));
-                        if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(dv + e0));
-                    }
-#pragma unroll
-                    for (int i = 0; i < PASSES; ++i) {
-                        const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
-                        if (op.kind == 0) {
-                            if (!op.descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
-                        } else if (!skip_axpy) {
-                            d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
-                                                new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
-                        }
-                        if (writes) *reinterpret_cast<float4*>(dir + e0) = d4[i];
-                        if (want_dot) {
-                            acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
-                            acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
-                        }
-                    }
-                } else
-#pragma unroll
-                for (int i = 0; i < kDotChunk / (kDotThreads * 4); ++i) {
-                    const long long e0 = base + ((long long)i * kDotThreads + tid) * 4;
-                    if (vec_ok && e0 + 3 < n) {
-                        float4 d4;
-                        if (op.kind == 0) {
-                            const float4 g4 = *reinterpret_cast<const float4*>(g + e0);
-                            d4 = op.descent ? g4 : make_float4(-g4.x, -g4.y, -g4.z, -g4.w);
-                        } else {
-                            d4 = *reinterpret_cast<const float4*>(dir + e0);
-                            if (!skip_axpy) {
-                                const float4 v4 = __ldcs(reinterpret_cast<const float4*>(vec + e0));   // history: streamed once, keep dir in L2
-                                d4 = make_float4(new_dir(d4.x, v4.x), new_dir(d4.y, v4.y), new_dir(d4.z, v4.z), new_dir(d4.w, v4.w));
-                            }
-                        }
-                        if (writes) *reinterpret_cast<float4*>(dir + e0) = d4;
-                        if (want_dot) {
-                            const float4 o4 = __ldcs(reinterpret_cast<const float4*>(dv + e0));
-                            acc = add(acc, mul(o4.x, d4.x)); acc = add(acc, mul(o4.y, d4.y));
-                            acc = add(acc, mul(o4.z, d4.z)); acc = add(acc, mul(o4.w, d4.w));
-                        }
-                    } else {
-                        for (int k = 0; k < 4; ++k) {
-                            const long long e = e0 + k;
-                            if (e < n) {
-                                float dn;
-                                if (op.kind == 0) dn = op.descent ? g[e] : -g[e];
-                                else dn = skip_axpy ? dir[e] : new_dir(dir[e], vec[e]);
-                                if (writes) dir[e] = dn;
-                                if (want_dot) acc = add(acc, mul(dv[e], dn));
-                            }
-                        }
-                    }
-                }
             }
 
             if (want_dot || op.kind == 4) {
@@ -268,40 +229,125 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
         }
     }
 
-    if (op.epilogue == 0) return;
+    finish_pass(tb, op, want_dot || op.kind == 4, partials, ticket, warp_sum, &is_last);
+}
 
-    // The CTA that takes the last ticket sees every chunk sum and finishes the
-    // reduction in a fixed order.
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        const unsigned my = atomicAdd(ticket, 1u);
-        is_last = (my == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
+// Kinds 0, 1 and 2: dir = -g | dir -= c*vec | dir += c*vec, fused with the dot
+// product of the new direction and a second column.  Each CTA walks chunks
+// blockIdx.x, blockIdx.x + gridDim.x, ...; the loads of its next chunk are issued
+// before the current chunk's sum is reduced, so the shuffles, barriers and the
+// table lookups run with a full set of loads in flight.  The chunk sums land in
+// partials[chunk], so the summation order does not depend on the grid.
+struct AxpyRef {
+    float* dir;
+    const float* src;        // kind 0: g; else dir
+    const float* vec;
+    const float* dv;
+    long long base, n;
+    bool fast;               // a whole chunk, 16-byte aligned in every column
+};
 
-    float dot = 0.0f;
-    const bool have_dot = want_dot || op.kind == 4;
-    if (have_dot) {
-        float acc = 0.0f;
-        const volatile float* pv = partials;
-        for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, pv[c]);
-        dot = cta_reduce_256(acc, warp_sum);
-    }
-    if (tid == 0) {
-        float r = 0.0f;
-        switch (op.epilogue) {
-            case 1: r = have_dot ? mul(dot, *op.rho_dot) : 0.0f; break;                         // alpha_j
-            case 2: r = have_dot ? sub(*op.alpha_in, mul(dot, *op.rho_dot)) : 0.0f; break;      // alpha_j - beta
-            case 3: r = (op.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
-            default: r = dot; break;
+__global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
+lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
+                      unsigned int* __restrict__ ticket) {
+    __shared__ float warp_sum[kDotThreads / 32];
+    __shared__ int is_last;
+    constexpr int PASSES = kDotChunk / (kDotThreads * 4);
+    const int tid = threadIdx.x;
+    const int T = tb.T;
+    const int kind = op.kind;
+
+    const bool skip_axpy = kind != 0 && rho_skips(op.rho_axpy);
+    const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot);
+    const float coef = kind != 0 ? *op.coef : 0.0f;
+    const bool has_vec = kind != 0 && !skip_axpy;
+    const bool writes = kind == 0 || !skip_axpy;
+
+    auto lookup = [&](int c) -> AxpyRef {
+        AxpyRef r;
+        const int t = find_tensor(tb.chunk_prefix, T, c);
+        r.n = __ldg(tb.numel + t);
+        r.base = (long long)(c - __ldg(tb.chunk_prefix + t)) * kDotChunk;
+        r.fast = __ldg(tb.aligned + t) != 0 && r.base + kDotChunk <= r.n;
+        auto col = [&](int cidx) -> float* { return reinterpret_cast<float*>(__ldg(tb.ptrs + (size_t)cidx * T + t)); };
+        r.dir = col(COL_DIR);
+        r.src = kind == 0 ? col(COL_G) : r.dir;
+        r.vec = has_vec ? col(op.col_axpy) : nullptr;
+        r.dv = want_dot ? col(op.col_dot) : nullptr;
+        return r;
+    };
+    auto new_dir = [&](float d_old, float v) -> float {
+        return kind == 1 ? sub(d_old, mul(coef, v)) : add(d_old, mul(coef, v));
+    };
+
+    if (writes || want_dot) {
+        float4 d4[PASSES], v4[PASSES], o4[PASSES];
+        auto issue = [&](const AxpyRef& r) {
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+                const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
+                // g and the history columns are read once per pass: streamed, so that dir stays in L2
+                if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
+                else d4[i] = *reinterpret_cast<const float4*>(r.src + e0);
+                if (has_vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
+                if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
+            }
+        };
+
+        int c = blockIdx.x;
+        AxpyRef cur{};
+        if (c < tb.num_chunks) {
+            cur = lookup(c);
+            if (cur.fast) issue(cur);
         }
-        *op.out = r;
-        *ticket = 0u;
-        __threadfence();
+        while (c < tb.num_chunks) {
+            const int cn = c + gridDim.x;
+            AxpyRef nxt{};
+            if (cn < tb.num_chunks) nxt = lookup(cn);          // resolves while this chunk's loads arrive
+            float acc = 0.0f;
+            if (cur.fast) {
+#pragma unroll
+                for (int i = 0; i < PASSES; ++i) {
+                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                    if (kind == 0) {
+                        if (!op.descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
+                    } else if (has_vec) {
+                        d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
+                                            new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
+                    }
+                    if (writes) *reinterpret_cast<float4*>(cur.dir + e0) = d4[i];
+                    if (want_dot) {
+                        acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
+                        acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
+                    }
+                }
+            } else {
+                // ragged end of a tensor, or columns off a 16-byte boundary: element by
+                // element, lane t still owning elements (i*256+t)*4+k in that order
+                for (int i = 0; i < PASSES; ++i) {
+                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                    for (int k = 0; k < 4; ++k) {
+                        const long long e = e0 + k;
+                        if (e < cur.n) {
+                            float dn;
+                            if (kind == 0) dn = op.descent ? cur.src[e] : -cur.src[e];
+                            else dn = has_vec ? new_dir(cur.dir[e], cur.vec[e]) : cur.dir[e];
+                            if (writes) cur.dir[e] = dn;
+                            if (want_dot) acc = add(acc, mul(cur.dv[e], dn));
+                        }
+                    }
+                }
+            }
+            if (cn < tb.num_chunks && nxt.fast) issue(nxt);     // in flight during the reduction below
+            if (want_dot) {
+                const float total = cta_reduce_256(acc, warp_sum);
+                if (tid == 0) partials[c] = total;
+            }
+            c = cn;
+            cur = nxt;
+        }
     }
+    finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
 }
 
 // ---- host side ----
@@ -384,9 +430,28 @@ static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* 
     return GM_OK;
 }
 
+// Grid of the pipelined kernel: the CTAs resident at once, trimmed so that every
+// CTA walks the same number of chunks (no short last round).
+static int axpy_grid(Device* d, int num_chunks) {
+    static thread_local int per_sm = 0;
+    if (per_sm == 0) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lbfgs_axpy_dot_kernel, kDotThreads, 0);
+        if (per_sm < 1) per_sm = 1;
+    }
+    int waves = d->lbfgs_waves > 0 ? d->lbfgs_waves : 1;
+    const long long resident = (long long)per_sm * d->sm_count * waves;
+    if (num_chunks <= resident) return num_chunks;
+    const long long rounds = (num_chunks + resident - 1) / resident;
+    return (int)((num_chunks + rounds - 1) / rounds);
+}
+
 static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op) {
-    int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
-    lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+    if (op.kind <= 2) {
+        lbfgs_axpy_dot_kernel<<<axpy_grid(d, c->tb.num_chunks), kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+    } else {
+        int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
+        lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+    }
     d->launches++;
 }
 
