@@ -351,11 +351,28 @@ def run_gpu(args):
         barrier()
         return dt
 
+    # the floor of any host-buffer step: the same two copies, both directions at once, no kernel
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    g_dev = grads[0][:shard_elems]
+    w_dev = w_arena[first * TENSOR_ELEMS: first * TENSOR_ELEMS + shard_elems]
+    scratch_w = torch.empty_like(host_w).pin_memory()
+
+    def copies_only():
+        with torch.cuda.stream(up):
+            g_dev.copy_(host_g, non_blocking=True)
+        with torch.cuda.stream(down):
+            scratch_w.copy_(w_dev, non_blocking=True)
+        torch.cuda.synchronize()
+
     dropin_s = time_e2e(e2e_step_dropin)
     e2e_s = time_e2e(e2e_step_host)
+    copy_s = time_e2e(copies_only)
+    del scratch_w
     e2e = {"value": TOTAL * e2e_steps / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": shard_bytes,
            "d2h_bytes_per_step": shard_bytes, "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
            "api": f"gm_step_host (pinned host gradients in, updated parameters out, {args.host_slices} pipelined slices)",
+           "copy_floor": {"ms_per_step": copy_s / e2e_steps * 1e3,
+                          "note": "the step's two host<->device copies alone, concurrent, no kernel"},
            "unpipelined": {"value": TOTAL * e2e_steps / dropin_s / 1e9, "ms_per_step": dropin_s / e2e_steps * 1e3,
                            "api": "upload + execute_adam_step_cuda (synchronous drop-in entry) + download"}}
 
@@ -409,7 +426,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--exchange", choices=["nccl", "push", "dma"], default="push")
     ap.add_argument("--slices", type=int, default=8, help="slices of the shard for --exchange dma")
-    ap.add_argument("--host-slices", type=int, default=16, help="pipeline depth of the host-buffer step (e2e)")
+    ap.add_argument("--host-slices", type=int, default=64, help="pipeline depth of the host-buffer step (e2e)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,

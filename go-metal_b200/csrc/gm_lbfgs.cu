@@ -38,7 +38,10 @@ namespace gm {
 constexpr int kDotChunk = 4096;
 constexpr int kDotThreads = 256;
 #ifndef GM_LBFGS_MINB
-#define GM_LBFGS_MINB 3          // resident CTAs per SM the pass kernel is compiled for (4 would spill)
+#define GM_LBFGS_MINB 3          // resident CTAs per SM the axpy+dot kernel is compiled for (4 would spill)
+#endif
+#ifndef GM_LBFGS_PASS_MINB
+#define GM_LBFGS_PASS_MINB 4     // the final-update / plain-dot kernel needs fewer registers
 #endif
 
 struct LbfgsTable {
@@ -65,12 +68,33 @@ struct LbfgsOp {
     // kind 3
     int col_s_new, col_y_prev, col_s_prev, have_pair, corrected;
     int descent;              // kind 0: dir = +g instead of -g
+    int keep_dir;             // kinds 0..2: the direction's lines get the evict_last L2 policy
     float step;
 };
 
 __device__ __forceinline__ bool rho_skips(const float* rho) {
     // bridge_optimizer.m:1066: fabs(rho_j) < 1e-10, evaluated in double
     return rho != nullptr && fabs((double)(*rho)) < 1e-10;
+}
+
+// L2 eviction policies.  The direction vector is read and rewritten by every
+// pass while 2m history vectors stream past it once each; marking its lines
+// evict_last (and the streams evict_first) keeps it in L2 between launches.
+__device__ __forceinline__ unsigned long long l2_policy(const bool keep) {
+    unsigned long long p;
+    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ float4 ld_l2(const float* a, const unsigned long long pol) {
+    float4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(a), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void st_l2(float* a, const float4 v, const unsigned long long pol) {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;"
+                 :: "l"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
 }
 
 // Sum of the 256 lane values of a CTA in the documented order; result valid in thread 0.
@@ -126,7 +150,7 @@ __device__ __forceinline__ void finish_pass(const LbfgsTable& tb, const LbfgsOp&
     }
 }
 
-__global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
+__global__ void __launch_bounds__(kDotThreads, GM_LBFGS_PASS_MINB)
 lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
                   unsigned int* __restrict__ ticket) {
     __shared__ float warp_sum[kDotThreads / 32];
@@ -262,6 +286,7 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
     const float coef = kind != 0 ? *op.coef : 0.0f;
     const bool has_vec = kind != 0 && !skip_axpy;
     const bool writes = kind == 0 || !skip_axpy;
+    const unsigned long long pol = l2_policy(op.keep_dir != 0);
 
     auto lookup = [&](int c) -> AxpyRef {
         AxpyRef r;
@@ -288,7 +313,7 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
                 const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
                 // g and the history columns are read once per pass: streamed, so that dir stays in L2
                 if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
-                else d4[i] = *reinterpret_cast<const float4*>(r.src + e0);
+                else d4[i] = ld_l2(r.src + e0, pol);
                 if (has_vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
                 if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
             }
@@ -315,7 +340,7 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
                         d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
                                             new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
                     }
-                    if (writes) *reinterpret_cast<float4*>(cur.dir + e0) = d4[i];
+                    if (writes) st_l2(cur.dir + e0, d4[i], pol);
                     if (want_dot) {
                         acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
                         acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
@@ -445,8 +470,10 @@ static int axpy_grid(Device* d, int num_chunks) {
     return (int)((num_chunks + rounds - 1) / rounds);
 }
 
-static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op) {
+static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in) {
+    LbfgsOp op = op_in;
     if (op.kind <= 2) {
+        op.keep_dir = d->lbfgs_keep_dir;
         lbfgs_axpy_dot_kernel<<<axpy_grid(d, c->tb.num_chunks), kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
     } else {
         int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
