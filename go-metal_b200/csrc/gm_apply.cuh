@@ -61,6 +61,34 @@ struct AdamRule {
     }
 };
 
+// L2 eviction policies for data that a later launch reads again while other
+// data streams past it once (the L-BFGS direction vector between passes, the
+// fp16 gradients between the overflow check and the update): lines loaded or
+// stored with the evict_last policy stay in L2 ahead of evict-first streams.
+__device__ __forceinline__ unsigned long long l2_policy(const bool keep) {
+    unsigned long long p;
+    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ float4 ld_l2(const float* a, const unsigned long long pol) {
+    float4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(a), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void st_l2(float* a, const float4 v, const unsigned long long pol) {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;"
+                 :: "l"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_l2(const uint4* a, const unsigned long long pol) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a), "l"(pol));
+    return v;
+}
+
 // Rule concept:
 //   static constexpr int NS;            number of streams (w, g, state...)
 //   static constexpr unsigned WMASK;    bit s set => stream s is written back

@@ -77,26 +77,6 @@ __device__ __forceinline__ bool rho_skips(const float* rho) {
     return rho != nullptr && fabs((double)(*rho)) < 1e-10;
 }
 
-// L2 eviction policies.  The direction vector is read and rewritten by every
-// pass while 2m history vectors stream past it once each; marking its lines
-// evict_last (and the streams evict_first) keeps it in L2 between launches.
-__device__ __forceinline__ unsigned long long l2_policy(const bool keep) {
-    unsigned long long p;
-    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ float4 ld_l2(const float* a, const unsigned long long pol) {
-    float4 v;
-    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(a), "l"(pol));
-    return v;
-}
-__device__ __forceinline__ void st_l2(float* a, const float4 v, const unsigned long long pol) {
-    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;"
-                 :: "l"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
-}
-
 // Sum of the 256 lane values of a CTA in the documented order; result valid in thread 0.
 __device__ __forceinline__ float cta_reduce_256(float acc, float* warp_sum) {
 #pragma unroll

@@ -81,7 +81,12 @@ struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; };
 
 __global__ void __launch_bounds__(kApplyThreads)
 mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
-                   const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep) {
+                   const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g) {
+    // Lets an update kernel launched with programmatic stream serialization become
+    // resident while this grid drains; it still waits for this grid to finish
+    // before it reads the published scalars.  Without that launch attribute: no effect.
+    asm volatile("griddepcontrol.launch_dependents;");
+    const unsigned long long pol = l2_policy(keep_g != 0);      // the update kernel reads the gradients again
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
@@ -109,7 +114,7 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 v[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (i + u * NT < nvec) v[u] = __ldg(q + i + u * NT);
+                if (i + u * NT < nvec) v[u] = ld_l2(q + i + u * NT, pol);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u)
@@ -176,6 +181,26 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
     const long long chunk = L.chunk_elems;
+
+    // Under programmatic stream serialization this CTA may start while the check
+    // grid is still draining: warm L2 with the first vectors it will read, then wait
+    // for the check grid to complete (a no-op after an ordinary launch).
+    if (blockIdx.x < L.num_chunks) {
+        const int2 rec = __ldg(L.chunk_rec + blockIdx.x);
+        const int t = rec.x;
+        const int h = __ldg(L.head + t);
+        if (h >= 0) {
+            const long long off = (long long)h + (long long)rec.y * chunk + 4LL * tid;
+            if (off + 4 <= __ldg(L.numel + t)) {
+#pragma unroll
+                for (int s = 1; s < 4; ++s) {
+                    const float* a = reinterpret_cast<const float*>(__ldg(L.ptrs + s * (size_t)T + t)) + off;
+                    asm volatile("prefetch.global.L2 [%0];" :: "l"(a));
+                }
+            }
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // The step's scalars were published by the check kernel; the loss-scale
     // state itself is only rewritten by the CTA that finishes last.
@@ -352,7 +377,7 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
     mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                m->table_len, prep);
+                                                                m->table_len, prep, d->mixed_keep_g);
     d->launches++;
     if (hook) {
         int rc = hook(ctx, m->d_flag);
@@ -361,7 +386,19 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         d->launches++;
     }
     int grid_u = launch_grid(d, (const void*)mixed_update_kernel, kApplyThreads, l->dl.num_chunks);
-    mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
+    if (!hook && d->mixed_overlap) {
+        // the update grid may become resident while the check grid drains
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid_u); cfg.blockDim = dim3(kApplyThreads); cfg.dynamicSmemBytes = 0; cfg.stream = d->stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        GM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mixed_update_kernel, l->dl, m->d_state, m->d_flag,
+                                         (const StepPrep*)prep, sc));
+    } else {
+        mixed_update_kernel<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
+    }
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
     return GM_OK;
