@@ -71,6 +71,57 @@ def test_adam_2p30_params_256_tensors_sampled(gm, dev, oracle):
         torch.cuda.empty_cache()
 
 
+def test_adam_one_tensor_past_2p31_elements(gm, dev, oracle):
+    """Maximum sizes: one tensor of 2^31 + 5,001 elements (8 GiB per stream, more than an
+    `int` can count in elements or bytes), every stream starting one element past a
+    16-byte boundary, so element offsets, chunk counts and the ragged tail all run in
+    64-bit arithmetic.  Two Adam steps; a strided sample, both ends and the elements on
+    either side of index 2^31 are compared with the oracle."""
+    torch = pytest.importorskip("torch")
+    O, L = oracle, gm.lib
+    n = 2 ** 31 + 5001
+    free_b, _ = torch.cuda.mem_get_info()
+    if free_b < 40 * 2 ** 30:
+        pytest.skip("needs 40 GiB of free device memory")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4321)
+    pad = 8
+    w = torch.empty(n + pad, dtype=torch.float32, device="cuda").uniform_(-0.04, 0.04, generator=gen)
+    g = torch.empty(n + pad, dtype=torch.float32, device="cuda")
+    m = torch.zeros(n + pad, dtype=torch.float32, device="cuda")
+    v = torch.zeros(n + pad, dtype=torch.float32, device="cuda")
+    for a in (w, m, v):
+        a[0] = 7.0
+        a[n + 1:] = 7.0
+    lst = dev.tensor_list([[a.data_ptr() + 4] for a in (w, g, m, v)], [n])
+    assert L.gm_tensor_list_total(lst) == n
+    assert L.gm_tensor_list_num_chunks(lst) == (n - 3 + 4095) // 4096      # 3 elements peeled up to the boundary
+    mid = np.arange(2 ** 31 - 64, 2 ** 31 + 64)
+    idx = np.unique(np.concatenate([sample_indices(n, stride=1_000_003), mid])).astype(np.int64)
+    flat = torch.from_numpy(idx + 1).cuda()                 # +1: the tensors start at element 1 of the allocations
+    try:
+        for step in (1, 2):
+            g.normal_(0.0, 0.01, generator=gen)
+            torch.cuda.synchronize()
+            before = {k: a[flat].cpu().numpy() for k, a in (("w", w), ("g", g), ("m", m), ("v", v))}
+            hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=step)
+            gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy)), "adam")
+            dev.sync()
+            ws, ms, vs = before["w"].copy(), before["m"].copy(), before["v"].copy()
+            O.adam_step(ws, before["g"], ms, vs, 1e-3, 0.9, 0.999, 1e-8, 0.0, step)
+            for k, a, want in (("w", w, ws), ("m", m, ms), ("v", v, vs)):
+                got = a[flat].cpu().numpy()
+                assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"step {step}: {k} sample differs"
+            for a in (w, m, v):
+                assert float(a[0]) == 7.0 and bool((a[n + 1:] == 7.0).all()), "wrote outside the tensor"
+            # no element skipped: v stays 0 only where g is 0
+            assert int((v[1:n + 1] == 0).sum()) <= int((g[1:n + 1] == 0).sum())
+    finally:
+        L.gm_tensor_list_destroy(lst)
+        del w, g, m, v
+        torch.cuda.empty_cache()
+
+
 def test_mixed_adam_25m_params_48_ragged_tensors(gm, dev, oracle):
     """The mixed-precision configuration at its full size: 25,165,824 parameters in 48
     log-uniform tensors (4 Ki - 4 Mi, none a multiple of 8) packed back to back, fp16
