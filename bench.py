@@ -142,6 +142,21 @@ def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | 
     return n * done / dt / 1e9, cores, done, dt / done
 
 
+def go_transcription_rate(sample_elems: int):
+    """Times the Go twin of the oracle (oracle/go) when a Go toolchain is on PATH."""
+    import shutil
+    import subprocess
+    if shutil.which("go") is None:
+        return "no Go toolchain on this host; the C restatement stands in"
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "go")
+    try:
+        out = subprocess.run(["go", "run", "./cmd/gmoracle_bench", "-n", str(sample_elems), "-steps", "3"],
+                             cwd=here, capture_output=True, text=True, timeout=240, check=True).stdout
+        return json.loads(out.strip().splitlines()[-1])
+    except Exception as exc:                                   # a broken toolchain must not cost the bench line
+        return f"go run failed: {exc}"
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -155,7 +170,8 @@ def run_reference(args):
         "config": {"workload": WORKLOAD, "sample": f"{sample} of {TOTAL} params per step"},
         "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{done} Adam steps over a {sample}-parameter slice (same rule, same "
-                                   "hyper-parameters), pthread split over all host cores"},
+                                   "hyper-parameters), pthread split over all host cores",
+                         "go_transcription": go_transcription_rate(sample)},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference's Adam rule (oracle); the reference itself needs Apple Metal",
     }
