@@ -162,6 +162,14 @@ int extractBufferIndex(const std::string& name) {
     return (int)(neg ? -v : v);
 }
 
+float pow(float x, float y) {
+    if (y == 0.0f) return 1.0f;
+    if (y == 1.0f) return x;
+    float result = 1.0f;
+    for (int i = 0; i < (int)y; ++i) result *= x;
+    return result;
+}
+
 std::string validateStateType(const std::string& optimizerType, const OptimizerState& state) {
     if (state.Type != optimizerType)
         return "state type mismatch: expected " + optimizerType + ", got " + state.Type;

@@ -114,6 +114,8 @@ namespace optimizer {
 // optimizer/interface.go:56-84, optimizer/state_helpers.go:52-74, adam.go (calculateTensorSize)
 int extractBufferIndex(const std::string& name);
 std::string validateStateType(const std::string& optimizerType, const OptimizerState& state);   // "" = ok
+// adam.go:237-251: repeated multiplication, int(y) factors; 1 for y == 0, x for y == 1.
+float pow(float x, float y);
 float extractFloat32Param(const std::map<std::string, Param>& p, const std::string& key, float def);
 bool extractBoolParam(const std::map<std::string, Param>& p, const std::string& key, bool def);
 uint64_t extractUint64Param(const std::map<std::string, Param>& p, const std::string& key, uint64_t def);

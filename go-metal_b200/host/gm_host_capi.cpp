@@ -74,6 +74,7 @@ GMH_API int gmh_state_get_param(void* s, const char* key, double* value) {
 GMH_API float gmh_extract_float32_param(void* s, const char* key, float def) { return optimizer::extractFloat32Param(static_cast<OptimizerState*>(s)->Parameters, key, def); }
 GMH_API int gmh_extract_bool_param(void* s, const char* key, int def) { return optimizer::extractBoolParam(static_cast<OptimizerState*>(s)->Parameters, key, def != 0) ? 1 : 0; }
 GMH_API uint64_t gmh_extract_uint64_param(void* s, const char* key, uint64_t def) { return optimizer::extractUint64Param(static_cast<OptimizerState*>(s)->Parameters, key, def); }
+GMH_API float gmh_pow(float x, float y) { return optimizer::pow(x, y); }
 GMH_API int gmh_validate_state_type(const char* type, void* s) { return fail(optimizer::validateStateType(type, *static_cast<OptimizerState*>(s))); }
 GMH_API void gmh_state_add_tensor(void* s, const char* name, const char* state_type, const float* data, int n) {
     OptimizerTensor t;

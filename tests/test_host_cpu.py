@@ -71,6 +71,13 @@ def test_extract_params_follow_json_float64_convention(H):
     H.gmh_state_destroy(st)
 
 
+def test_pow_table(H):
+    """adam_test.go:282-308."""
+    for x, y, want in [(5.0, 0.0, 1.0), (5.0, 1.0, 5.0), (3.0, 2.0, 9.0), (2.0, 3.0, 8.0), (-2.0, 2.0, 4.0),
+                       (1.5, 2.0, 2.25)]:
+        assert H.gmh_pow(x, y) == want, (x, y)
+
+
 def test_pool_tier_tables(H):
     """memory/memory_test.go:215-266"""
     for size, want in [(100, 1024), (1024, 1024), (5000, 16384), (100000000, 100000000)]:
