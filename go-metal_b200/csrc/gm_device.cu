@@ -137,6 +137,7 @@ static Device* make_device(int ordinal) {
     if (const char* e4 = getenv("GOMETAL_LBFGS_KEEP_DIR")) d->lbfgs_keep_dir = atoi(e4);
     if (const char* e5 = getenv("GOMETAL_MIXED_KEEP_G")) d->mixed_keep_g = atoi(e5);
     if (const char* e6 = getenv("GOMETAL_MIXED_OVERLAP")) d->mixed_overlap = atoi(e6);
+    if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);
     if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);
     // A blocking stream on purpose: the synchronous copies of the drop-in ABI
     // (cudaMemcpy/cudaMemset on the legacy default stream) may return before a

@@ -61,6 +61,7 @@ struct Device {
     std::unordered_map<uint64_t, TensorList*> list_cache;
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
+    int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
     int mixed_overlap = 1;              // update grid launched with programmatic stream serialization (GOMETAL_MIXED_OVERLAP)
     int lbfgs_keep_dir = 1;             // L-BFGS direction lines marked evict_last in L2 (GOMETAL_LBFGS_KEEP_DIR=0 turns it off)
     int lbfgs_waves = 1;                // resident-CTA waves of the pipelined L-BFGS pass (GOMETAL_LBFGS_WAVES)

@@ -79,7 +79,7 @@ __device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
 // check kernel so that every update CTA starts with a single 16-byte load.
 struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; };
 
-__global__ void __launch_bounds__(kApplyThreads)
+__global__ void __launch_bounds__(kApplyThreads, 8)
 mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
                    const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g) {
     // Lets an update kernel launched with programmatic stream serialization become
@@ -88,40 +88,67 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
     asm volatile("griddepcontrol.launch_dependents;");
     const unsigned long long pol = l2_policy(keep_g != 0);      // the update kernel reads the gradients again
     constexpr int NT = kApplyThreads;
+    constexpr int U = 4;                                     // 16-byte loads in flight per thread
     const int tid = threadIdx.x;
-    const int T = L.num_tensors;
     const long long chunk = L.chunk_elems;
     unsigned bad = 0;
-    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+
+    // Each CTA walks chunks blockIdx.x, blockIdx.x + gridDim.x, ...  The table
+    // lookups of the next chunk are issued while the current chunk's loads are in
+    // flight, and the next chunk's loads before the loop turns, so neither latency
+    // is exposed after the first chunk.
+    struct Ref { const unsigned short* g; long long n, b, e; int h, k; };
+    auto lookup = [&](int c) -> Ref {
+        Ref r;
         const int2 rec = __ldg(L.chunk_rec + c);
-        const int t = rec.x, k = rec.y;
-        const long long n = __ldg(L.numel + t);
-        const int h = __ldg(L.head + t);
-        const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + t));
-        if (h < 0) {
-            const long long b = (long long)k * chunk;
-            const long long e = (b + chunk < n) ? b + chunk : n;
-            for (long long i = b + tid; i < e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
-            continue;
+        r.k = rec.y;
+        r.n = __ldg(L.numel + rec.x);
+        r.h = __ldg(L.head + rec.x);
+        r.g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + rec.x));
+        r.b = (long long)(r.h > 0 ? r.h : 0) + (long long)r.k * chunk;
+        r.e = (r.b + chunk < r.n) ? r.b + chunk : r.n;
+        return r;
+    };
+    uint4 v[U];
+    auto issue = [&](const Ref& r) {
+        // first U*NT vectors of the chunk's aligned body (all of it at the default chunk size)
+        const long long nvec = (r.e - r.b) >> 3;
+        const uint4* q = reinterpret_cast<const uint4*>(r.g + r.b);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (r.h >= 0 && tid + u * NT < nvec) v[u] = ld_l2(q + tid + u * NT, pol);
         }
-        const long long b = (long long)h + (long long)k * chunk;
-        const long long e = (b + chunk < n) ? b + chunk : n;
-        if (k == 0 && tid < h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
-        const long long nvec = (e - b) >> 3;
-        const uint4* q = reinterpret_cast<const uint4*>(g + b);
-        for (long long i = tid; i < nvec; i += 4 * NT) {                 // four loads in flight per thread
-            uint4 v[4];
+    };
+
+    int c = blockIdx.x;
+    Ref cur{};
+    if (c < L.num_chunks) { cur = lookup(c); issue(cur); }
+    while (c < L.num_chunks) {
+        const int cn = c + gridDim.x;
+        Ref nxt{};
+        if (cn < L.num_chunks) nxt = lookup(cn);
+        const unsigned short* g = cur.g;
+        if (cur.h < 0) {
+            // streams off a common 16-byte boundary: element by element
+            for (long long i = cur.b + tid; i < cur.e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
+        } else {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                v[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (i + u * NT < nvec) v[u] = ld_l2(q + i + u * NT, pol);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
                 bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
+            const long long nvec = (cur.e - cur.b) >> 3;
+            const uint4* q = reinterpret_cast<const uint4*>(g + cur.b);
+            for (long long i = tid + (long long)U * NT; i < nvec; i += NT) {      // chunks larger than U*NT vectors
+                const uint4 w = ld_l2(q + i, pol);
+                bad |= nonfinite_mask(w.x) | nonfinite_mask(w.y) | nonfinite_mask(w.z) | nonfinite_mask(w.w);
+            }
+            if (cur.k == 0 && tid < cur.h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);   // elements before the boundary
+            const long long tb = cur.b + (nvec << 3);
+            if (tb + tid < cur.e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);       // fewer than 8 after the last vector
         }
-        const long long tb = b + (nvec << 3);
-        if (tb + tid < e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
+        if (cn < L.num_chunks) issue(nxt);
+        c = cn;
+        cur = nxt;
     }
     // warp vote, then one atomic for the whole CTA (and only when needed)
     const int any_bad = __syncthreads_or(bad != 0);
@@ -145,6 +172,20 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
             flag[2] = 0u;
         }
     }
+}
+
+// Grid of the check kernel: the CTAs resident at once, trimmed so that every CTA
+// walks the same number of chunks.
+static int check_grid(Device* d, int num_chunks) {
+    static thread_local int per_sm = 0;
+    if (per_sm == 0) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel, kApplyThreads, 0);
+        if (per_sm < 1) per_sm = 1;
+    }
+    const long long resident = (long long)per_sm * d->sm_count;
+    if (d->mixed_check_persistent == 0 || num_chunks <= resident) return num_chunks;
+    const long long rounds = (num_chunks + resident - 1) / resident;
+    return (int)((num_chunks + rounds - 1) / rounds);
 }
 
 // Recomputes the published scalars after the overflow flag has been combined
@@ -374,7 +415,7 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
     sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
     DeviceGuard g(d);
-    int grid_c = launch_grid(d, (const void*)mixed_check_kernel, kApplyThreads, l->dl.num_chunks);
+    int grid_c = check_grid(d, l->dl.num_chunks);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
     mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
                                                                 m->table_len, prep, d->mixed_keep_g);

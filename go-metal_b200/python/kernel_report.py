@@ -110,17 +110,21 @@ def ragged_sizes(count, total, lo, hi, seed=0x5EED601D):
     return [int(s) for s in sizes]
 
 
-def case_mixed(dev, reps, small):
-    total_params = 25_165_824 // (4 if small else 1)
-    sizes = ragged_sizes(48, total_params, 4096, 4_194_304 // (4 if small else 1))
+def case_mixed(dev, reps, small, scale_up=1):
+    # scale_up > 1: the same 48-tensor shape with every tensor that many times larger,
+    # to separate the kernels' own rate from the ramp and tail of a 0.7 GB pass
+    total_params = 25_165_824 * scale_up // (4 if small else 1)
+    sizes = ragged_sizes(48, total_params, 4096 * scale_up, 4_194_304 * scale_up // (4 if small else 1))
     n = sum(sizes)
     total = n + 32
     eb = {"g": 2, "w": 4, "m": 4, "v": 4, "p": 2}
     base = {k: dev.alloc(total * eb[k]) for k in "gwmvp"}
     for k in "gwmvp":
         gm.check(L.gm_buffer_zero(dev.h, base[k], total * eb[k]), "zero")
-    g16 = (np.random.default_rng(1).standard_normal(total).astype(np.float32) * 65.536).astype(np.float16)
-    dev.upload(base["g"], g16.view(np.uint16))
+    block = (np.random.default_rng(1).standard_normal(min(total, 1 << 25)).astype(np.float32) * 65.536).astype(np.float16)
+    for lo in range(0, total, block.size):                       # one 32 Mi block repeated
+        k = min(block.size, total - lo)
+        gm.check(L.gm_buffer_upload(dev.h, base["g"] + 2 * lo, block.ctypes.data, 2 * k), "upload")
     offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64) + 1
     ptrs = {k: [base[k] + eb[k] * int(o) for o in offs] for k in "gwmvp"}
     lst = dev.tensor_list([ptrs[k] for k in "gwmvp"], sizes, [2, 4, 4, 4, 2])
@@ -220,13 +224,15 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "lbfgs", "small"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "mixed_x16", "lbfgs", "small"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
-        {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small}[args.case](dev, args.reps, args.small)
+        cases = {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
+                 "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16)}
+        cases[args.case](dev, args.reps, args.small)
     finally:
         dev.close()
 
