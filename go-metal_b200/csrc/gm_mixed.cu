@@ -351,7 +351,6 @@ __global__ void __launch_bounds__(kApplyThreads)
 sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
-    const int T = L.num_tensors;
     const long long chunk = L.chunk_elems;
     float acc = 0.0f;
     for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
