@@ -32,7 +32,9 @@ struct Mixed {
     int magic = kMagicMixed;
     Device* dev = nullptr;
     gm_loss_scale_t* d_state = nullptr;
-    unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] update ticket, [2] check ticket, [16..] StepPrep
+    unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] update ticket, [2] check ticket, [3] sum-of-squares
+                                           // accumulator, [16..19] StepPrep, [24] last step's sum of squares
+    int want_norm = 0;
     float2* d_table = nullptr;             // [table_len+1] {1-b1^t, 1-b2^t}
     int table_len = 0;
     bool saturated = false;                // table[table_len] == {1,1}: later steps reuse it
@@ -79,7 +81,26 @@ __device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
 // check kernel so that every update CTA starts with a single 16-byte load.
 struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; };
 
-__global__ void __launch_bounds__(kApplyThreads, 8)
+// acc + the squares of the two halves packed in x, each first multiplied by inv.
+__device__ __forceinline__ float sumsq2(const unsigned x, const float inv, float acc) {
+    const float a = __half2float(__ushort_as_half((unsigned short)(x & 0xffffu))) * inv;
+    const float b = __half2float(__ushort_as_half((unsigned short)(x >> 16))) * inv;
+    acc = fmaf(a, a, acc);
+    return fmaf(b, b, acc);
+}
+__device__ __forceinline__ float sumsq8(const uint4 v, const float inv, float acc) {
+    return sumsq2(v.w, inv, sumsq2(v.z, inv, sumsq2(v.y, inv, sumsq2(v.x, inv, acc))));
+}
+__device__ __forceinline__ float sumsq1(const unsigned short h, const float inv, float acc) {
+    const float a = __half2float(__ushort_as_half(h)) * inv;
+    return fmaf(a, a, acc);
+}
+
+// NORM: the same pass also accumulates the sum of squares of the unscaled
+// gradients (warp shuffle tree, one float atomic per CTA); the last CTA moves the
+// total to flag[24] and clears the accumulator flag[3].
+template <bool NORM>
+__global__ void __launch_bounds__(kApplyThreads, NORM ? 6 : 8)
 mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
                    const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g) {
     // Lets an update kernel launched with programmatic stream serialization become
@@ -92,6 +113,8 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
     const int tid = threadIdx.x;
     const long long chunk = L.chunk_elems;
     unsigned bad = 0;
+    float ss = 0.0f;
+    const float inv = NORM ? 1.0f / state->scale : 0.0f;
 
     // Each CTA walks chunks blockIdx.x, blockIdx.x + gridDim.x, ...  The table
     // lookups of the next chunk are issued while the current chunk's loads are in
@@ -131,26 +154,51 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
         const unsigned short* g = cur.g;
         if (cur.h < 0) {
             // streams off a common 16-byte boundary: element by element
-            for (long long i = cur.b + tid; i < cur.e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
+            for (long long i = cur.b + tid; i < cur.e; i += NT) {
+                bad |= ((g[i] & 0x7c00u) == 0x7c00u);
+                if (NORM) ss = sumsq1(g[i], inv, ss);
+            }
         } else {
 #pragma unroll
-            for (int u = 0; u < U; ++u)
+            for (int u = 0; u < U; ++u) {
                 bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
+                if (NORM) ss = sumsq8(v[u], inv, ss);                       // lanes past the end hold zeros
+            }
             const long long nvec = (cur.e - cur.b) >> 3;
             const uint4* q = reinterpret_cast<const uint4*>(g + cur.b);
             for (long long i = tid + (long long)U * NT; i < nvec; i += NT) {      // chunks larger than U*NT vectors
                 const uint4 w = ld_l2(q + i, pol);
                 bad |= nonfinite_mask(w.x) | nonfinite_mask(w.y) | nonfinite_mask(w.z) | nonfinite_mask(w.w);
+                if (NORM) ss = sumsq8(w, inv, ss);
             }
-            if (cur.k == 0 && tid < cur.h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);   // elements before the boundary
+            if (cur.k == 0 && tid < cur.h) {                                         // elements before the boundary
+                bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
+                if (NORM) ss = sumsq1(g[tid], inv, ss);
+            }
             const long long tb = cur.b + (nvec << 3);
-            if (tb + tid < cur.e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);       // fewer than 8 after the last vector
+            if (tb + tid < cur.e) {                                                  // fewer than 8 after the last vector
+                bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
+                if (NORM) ss = sumsq1(g[tb + tid], inv, ss);
+            }
         }
         if (cn < L.num_chunks) issue(nxt);
         c = cn;
         cur = nxt;
     }
     // warp vote, then one atomic for the whole CTA (and only when needed)
+    if (NORM) {
+        __shared__ float warp_ss[NT / 32];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if ((tid & 31) == 0) warp_ss[tid >> 5] = ss;
+        __syncthreads();
+        if (tid == 0) {
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; ++w) total += warp_ss[w];
+            atomicAdd(reinterpret_cast<float*>(flag + 3), total);
+        }
+    }
     const int any_bad = __syncthreads_or(bad != 0);
     if (tid == 0) {
         if (any_bad) atomicOr(flag, 1u);
@@ -170,6 +218,10 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
             sp.bc2 = bc.y;
             *prep = sp;
             flag[2] = 0u;
+            if (NORM) {
+                flag[24] = *reinterpret_cast<volatile unsigned int*>(flag + 3);
+                flag[3] = 0u;
+            }
         }
     }
 }
@@ -179,7 +231,7 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
 static int check_grid(Device* d, int num_chunks) {
     static thread_local int per_sm = 0;
     if (per_sm == 0) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel, kApplyThreads, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel<true>, kApplyThreads, 0);
         if (per_sm < 1) per_sm = 1;
     }
     const long long resident = (long long)per_sm * d->sm_count;
@@ -416,8 +468,12 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     DeviceGuard g(d);
     int grid_c = check_grid(d, l->dl.num_chunks);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
-    mixed_check_kernel<<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                m->table_len, prep, d->mixed_keep_g);
+    if (m->want_norm)
+        mixed_check_kernel<true><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
+                                                                          m->table_len, prep, d->mixed_keep_g);
+    else
+        mixed_check_kernel<false><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
+                                                                           m->table_len, prep, d->mixed_keep_g);
     d->launches++;
     if (hook) {
         int rc = hook(ctx, m->d_flag);
@@ -534,6 +590,25 @@ int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scal
         int rc = upload_table(m, m->table_len * 2);
         if (rc != GM_OK) return rc;
     }
+    return GM_OK;
+}
+
+int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable) {
+    Mixed* m = as_mixed(mixed);
+    if (!m) return GM_ERR_BAD_ARG;
+    m->want_norm = enable ? 1 : 0;
+    return GM_OK;
+}
+
+int gm_mixed_last_grad_sumsq(uintptr_t device_ptr, uintptr_t mixed, float* out) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    if (!m || !out) { if (m) set_error("output is nil"); return GM_ERR_BAD_ARG; }
+    if (!m->want_norm) { set_error("the gradient norm is not enabled on this mixed-precision state"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    GM_CUDA_CHECK(cudaMemcpy(out, m->d_flag + 24, sizeof(float), cudaMemcpyDeviceToHost));
     return GM_OK;
 }
 

@@ -106,6 +106,8 @@ _SIGS = {
     "gm_mixed_get_state": (i, [u, u, C.POINTER(LossScale)]),
     "gm_mixed_set_state": (i, [u, u, C.POINTER(LossScale)]),
     "gm_mixed_state_device_ptr": (u, [u]),
+    "gm_mixed_enable_grad_norm": (i, [u, i]),
+    "gm_mixed_last_grad_sumsq": (i, [u, u, C.POINTER(f)]),
     "gm_grad_sumsq_async": (i, [u, u, i, f, u]),
     "gm_lbfgs_set_mode": (i, [u, i]),
     "gm_dot_canonical": (i, [u, u, u, i64, C.POINTER(f)]),

@@ -110,7 +110,7 @@ def ragged_sizes(count, total, lo, hi, seed=0x5EED601D):
     return [int(s) for s in sizes]
 
 
-def case_mixed(dev, reps, small, scale_up=1):
+def case_mixed(dev, reps, small, scale_up=1, norm=False):
     # scale_up > 1: the same 48-tensor shape with every tensor that many times larger,
     # to separate the kernels' own rate from the ramp and tail of a 0.7 GB pass
     total_params = 25_165_824 * scale_up // (4 if small else 1)
@@ -129,10 +129,12 @@ def case_mixed(dev, reps, small, scale_up=1):
     ptrs = {k: [base[k] + eb[k] * int(o) for o in offs] for k in "gwmvp"}
     lst = dev.tensor_list([ptrs[k] for k in "gwmvp"], sizes, [2, 4, 4, 4, 2])
     mx = L.gm_mixed_create(dev.h, None, 0.9, 0.999, 0)
+    if norm:                                                     # gradient norm taken by the overflow-check pass
+        gm.check(L.gm_mixed_enable_grad_norm(mx, 1), "enable norm")
     ms = timed(dev, lambda: gm.check(L.gm_mixed_step_async(dev.h, mx, lst, 1e-3, 1e-8, 0.0), "mixed"), reps)
     st = gm.LossScale()
     gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(st)), "state")
-    emit(kernel="mixed_check_kernel+mixed_update_kernel", params=n, ms=ms, bytes_per_param=30,
+    emit(kernel="mixed_check_kernel" + ("<norm>" if norm else "") + "+mixed_update_kernel", params=n, ms=ms, bytes_per_param=30,
          gbs=30 * n / ms / 1e6, gparams_s=n / ms / 1e6, scale=st.scale, adam_t=st.adam_t, skipped=st.skipped)
     L.gm_mixed_destroy(mx)
     L.gm_tensor_list_destroy(lst)
@@ -224,14 +226,15 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "mixed_x16", "lbfgs", "small"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
         cases = {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
-                 "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16)}
+                 "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16),
+                 "mixed_norm": lambda d, r, sm: case_mixed(d, r, sm, norm=True)}
         cases[args.case](dev, args.reps, args.small)
     finally:
         dev.close()

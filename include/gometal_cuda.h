@@ -242,6 +242,15 @@ int gm_mixed_step_async(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list,
 int gm_mixed_get_state(uintptr_t device_ptr, uintptr_t mixed, gm_loss_scale_t* out);   /* waits */
 int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scale_t* in);
 uintptr_t gm_mixed_state_device_ptr(uintptr_t mixed);   /* device address of the gm_loss_scale_t */
+/* Gradient norm from the overflow-check pass itself (no extra pass over the
+ * gradients): when enabled, every step also leaves sum((g16 / scale)^2) over the
+ * list, accumulated in fp32 with one float atomic per CTA (so the last bits vary
+ * from run to run; inf or NaN on an overflow step).  gm_mixed_last_grad_sumsq
+ * waits for the stream and returns the last step's value.  Under
+ * gm_zero1_mixed_step_async the value covers the rank's own shard.  No
+ * counterpart in the reference, which has no clipping or norm. */
+int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable);
+int gm_mixed_last_grad_sumsq(uintptr_t device_ptr, uintptr_t mixed, float* out);
 
 /* ---- gradient norm (sum of squares; one float atomic per CTA) ---- */
 /* list stream 0 is the gradient (4 B or 2 B elements).  *out_sumsq is a

@@ -55,7 +55,7 @@ def same_state(a, b):
     return all(getattr(a, f) == getattr(b, f) for f in fields)
 
 
-def run_mixed(gm, dev, O, sizes, steps, interval, p_inject, check_every, seed=11):
+def run_mixed(gm, dev, O, sizes, steps, interval, p_inject, check_every, seed=11, with_norm=False):
     L = gm.lib
     rng = np.random.default_rng(seed)
     master = [O.fill_uniform(n, -0.05, 0.05, seed, 50 + k) for k, n in enumerate(sizes)]
@@ -68,6 +68,8 @@ def run_mixed(gm, dev, O, sizes, steps, interval, p_inject, check_every, seed=11
                         interval=st.interval, good_steps=0, adam_t=0, skipped=0, last_overflow=0)
     mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 64)     # short table: exercises growth of the table
     assert mx, gm.last_error()
+    if with_norm:
+        gm.check(L.gm_mixed_enable_grad_norm(mx, 1), "enable grad norm")
     skips = 0
     scales = set()
     try:
@@ -85,6 +87,15 @@ def run_mixed(gm, dev, O, sizes, steps, interval, p_inject, check_every, seed=11
                 g16[t][e] = [0x7c00, 0xfc00, 0x7e00][int(rng.integers(3))]     # +inf, -inf or NaN
             A.put("g", g16)
             gm.check(L.gm_mixed_step_async(dev.h, mx, A.list, LR, EPS, WD), "mixed step")
+            if with_norm:
+                # the overflow-check pass also leaves sum((g16/scale)^2); float atomics, so relative
+                got_ss = C.c_float()
+                gm.check(L.gm_mixed_last_grad_sumsq(dev.h, mx, C.byref(got_ss)), "grad sumsq")
+                want_ss = sum(O.sumsq_f16(g, 1.0 / float(scale)) for g in g16)
+                if np.isfinite(want_ss):
+                    assert abs(got_ss.value - want_ss) <= 1e-5 * want_ss, f"step {step}: {got_ss.value} vs {want_ss}"
+                else:
+                    assert not np.isfinite(got_ss.value), f"step {step}: overflow step must give a non-finite norm"
             skipped = O.mixed_adam_step(g16, master, m, v, p16, LR, B1, B2, EPS, WD, st)
             skips += skipped
             scales.add(float(st.scale))
@@ -122,6 +133,9 @@ def test_mixed_adam_ragged_500_steps(gm, dev, oracle):
     sizes = W.ragged_sizes(48, 393_217, 1024, 65536)
     skips, scales, st = run_mixed(gm, dev, oracle, sizes, 500, 100, 0.02, 50)
     assert skips >= 3, "the run must contain skipped steps"
+    # the same run with the gradient norm taken in the check pass: nothing else may change
+    skips_n, scales_n, st_n = run_mixed(gm, dev, oracle, sizes, 120, 100, 0.02, 40, with_norm=True)
+    assert skips_n >= 1 and st_n.adam_t == 120 - skips_n
     assert len(scales) >= 3, "the scale must both grow and back off"
     assert st.adam_t == 500 - skips
 
@@ -172,6 +186,16 @@ def test_overflow_anywhere_skips_everything(gm, dev, oracle, case):
     finally:
         L.gm_mixed_destroy(mx)
         A.close()
+
+
+def test_grad_norm_needs_enabling(gm, dev):
+    L = gm.lib
+    mx = L.gm_mixed_create(dev.h, None, B1, B2, 0)
+    out = C.c_float()
+    assert L.gm_mixed_last_grad_sumsq(dev.h, mx, C.byref(out)) == -10
+    assert L.gm_mixed_enable_grad_norm(mx, 1) == 0
+    assert L.gm_mixed_enable_grad_norm(0, 1) == -10
+    L.gm_mixed_destroy(mx)
 
 
 def test_mixed_state_set_get(gm, dev):
