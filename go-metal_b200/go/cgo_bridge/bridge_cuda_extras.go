@@ -175,7 +175,33 @@ func (m *MixedAdam) State() (LossScale, error) {
 		int32(c.good_steps), int32(c.adam_t), int32(c.skipped), int32(c.last_overflow)}, nil
 }
 
+// EnableGradNorm makes every following step also compute the sum of squares of the
+// unscaled gradients inside the overflow-check pass; GradSumSq waits for the stream
+// and returns the last step's value (inf or NaN on an overflow step).
+func (m *MixedAdam) EnableGradNorm(on bool) error {
+	v := C.int(0)
+	if on {
+		v = 1
+	}
+	return stepError("grad norm", C.gm_mixed_enable_grad_norm(m.h, v))
+}
+
+func (m *MixedAdam) GradSumSq() (float32, error) {
+	var out C.float
+	rc := C.gm_mixed_last_grad_sumsq(handle(m.device), m.h, &out)
+	return float32(out), stepError("grad norm", rc)
+}
+
 func (m *MixedAdam) Destroy() { C.gm_mixed_destroy(m.h); m.h = 0 }
+
+// StepHost runs one step with the gradients in (pinned) host memory and the new
+// parameters returned to host memory; upload, update and download are pipelined
+// over `slices` groups of tensors.  The list's parameter and gradient tensors must
+// lie back to back on the device.
+func StepHost(device unsafe.Pointer, rule Rule, list *TensorList, hyper Hyper, hostGrads, hostParams unsafe.Pointer, slices int) error {
+	ch := hyper.c()
+	return stepError("host-buffer step", C.gm_step_host(handle(device), C.int(rule), list.h, &ch, hostGrads, hostParams, C.int(slices)))
+}
 
 // ---- ZeRO-1 ----
 
@@ -224,6 +250,24 @@ func (z *Zero1) OpenPeers(handles []byte) error {
 func (z *Zero1) AdamPushStepAsync(shard *TensorList, hyper Hyper) error {
 	ch := hyper.c()
 	return stepError("ZeRO-1 Adam push", C.gm_zero1_adam_push_step_async(z.h, shard.h, &ch))
+}
+
+// AdamDMAStepAsync updates the shard in slices and lets the copy engines carry each finished slice to the peers.
+func (z *Zero1) AdamDMAStepAsync(shard *TensorList, hyper Hyper, slices int) error {
+	ch := hyper.c()
+	return stepError("ZeRO-1 Adam dma", C.gm_zero1_adam_dma_step_async(z.h, shard.h, &ch, C.int(slices)))
+}
+
+// MixedStepAsync is the mixed-precision step on a sharded list: the overflow flag is
+// summed across ranks before the update, then the fp16 parameter arena is all-gathered.
+func (z *Zero1) MixedStepAsync(m *MixedAdam, shard *TensorList, lr, eps, weightDecay float32, p16ArenaBase unsafe.Pointer, countPerRank int64) error {
+	return stepError("ZeRO-1 mixed Adam", C.gm_zero1_mixed_step_async(z.h, m.h, shard.h, C.float(lr), C.float(eps), C.float(weightDecay),
+		handle(p16ArenaBase), C.int64_t(countPerRank)))
+}
+
+// ReduceScatterAsync sums the ranks' gradient arenas; each rank keeps the sum of its own shard, in place.
+func (z *Zero1) ReduceScatterAsync(gradArenaBase unsafe.Pointer, countPerRank int64, elemBytes int) error {
+	return stepError("reduce-scatter", C.gm_zero1_reduce_scatter_async(z.h, handle(gradArenaBase), C.int64_t(countPerRank), C.int(elemBytes)))
 }
 
 func (z *Zero1) Destroy() { C.gm_zero1_destroy(z.h); z.h = 0 }
