@@ -51,6 +51,15 @@ std::string Backend::load(const std::string& path) {
         dlclose(h);
         return "backend " + path + " lacks: " + missing;
     }
+    std::string optional;                                   // absent entries only disable mixed precision
+    resolve(h, "gm_mixed_create", &b.mixed_create, &optional);
+    resolve(h, "gm_mixed_destroy", &b.mixed_destroy, &optional);
+    resolve(h, "gm_mixed_step_async", &b.mixed_step, &optional);
+    resolve(h, "gm_mixed_get_state", &b.mixed_get_state, &optional);
+    resolve(h, "gm_mixed_set_state", &b.mixed_set_state, &optional);
+    resolve(h, "gm_tensor_list_create", &b.list_create, &optional);
+    resolve(h, "gm_tensor_list_destroy", &b.list_destroy, &optional);
+    resolve(h, "gm_device_synchronize", &b.device_synchronize, &optional);
     *this = b;
     return "";
 }

@@ -45,6 +45,22 @@ struct Backend {
                  int, int*, int, int, int, float, float, float, int, float, float, float*) = nullptr;
     const char* (*last_error)() = nullptr;
 
+    // Mixed precision (include/gometal_cuda.h part 2).  Optional: a backend without
+    // them still serves the seven reference optimizers.
+    struct LossScaleC { float scale, growth, backoff, max_scale; int32_t interval, good_steps, adam_t, skipped, last_overflow; };
+    uintptr_t (*mixed_create)(uintptr_t, const LossScaleC*, float, float, int) = nullptr;
+    void (*mixed_destroy)(uintptr_t) = nullptr;
+    int (*mixed_step)(uintptr_t, uintptr_t, uintptr_t, float, float, float) = nullptr;
+    int (*mixed_get_state)(uintptr_t, uintptr_t, LossScaleC*) = nullptr;
+    int (*mixed_set_state)(uintptr_t, uintptr_t, const LossScaleC*) = nullptr;
+    uintptr_t (*list_create)(uintptr_t, int, int, const uintptr_t* const*, const int64_t*, const int*) = nullptr;
+    void (*list_destroy)(uintptr_t) = nullptr;
+    int (*device_synchronize)(uintptr_t) = nullptr;
+    bool has_mixed() const {
+        return mixed_create && mixed_destroy && mixed_step && mixed_get_state && mixed_set_state && list_create &&
+               list_destroy && device_synchronize;
+    }
+
     // Loads `path` and resolves every entry; returns an error text or "".
     std::string load(const std::string& path);
 };
@@ -156,6 +172,53 @@ std::unique_ptr<Optimizer> NewRMSPropOptimizer(const RMSPropConfig&, const Shape
 std::unique_ptr<Optimizer> NewAdaGradOptimizer(const AdaGradConfig&, const Shapes&, memory::MemoryManager*, uintptr_t device, std::string* err);
 std::unique_ptr<Optimizer> NewAdaDeltaOptimizer(const AdaDeltaConfig&, const Shapes&, memory::MemoryManager*, uintptr_t device, std::string* err);
 std::unique_ptr<Optimizer> NewNadamOptimizer(const NadamConfig&, const Shapes&, memory::MemoryManager*, uintptr_t device, std::string* err);
+
+// Mixed-precision Adam: fp16 gradients and an fp16 parameter copy around fp32 master
+// weights, with the dynamic loss scale of training/model_trainer.go:79-87 and
+// :258-270 kept on the device.  No counterpart type exists in optimizer/*.go (the
+// reference only carries the configuration fields); the interface is the same.
+//   SetWeightBuffers: the fp16 parameter buffers the model reads (written every step)
+//   Step:             one fp16 gradient buffer per weight; returns after the launch --
+//                     overflow detection, the skipped update and the scale change happen
+//                     on the device; GetState / LossScale wait for them
+//   GetStepCount:     Step calls so far (a skipped step counts; "adam_step" in the state does not)
+struct MixedAdamConfig {
+    float LearningRate = 0.001f, Beta1 = 0.9f, Beta2 = 0.999f, Epsilon = 1e-8f, WeightDecay = 0.0f;   // adam.go:51-59
+    float InitialLossScale = 65536.0f, GrowthFactor = 2.0f, BackoffFactor = 0.5f;                     // model_trainer.go:258-270
+    int GrowthInterval = 2000;
+    float MaxLossScale = 16777216.0f;
+};
+class MixedAdamOptimizerState : public Optimizer {
+public:
+    ~MixedAdamOptimizerState() override;
+    std::string Step(const std::vector<uintptr_t>& gradientBuffers) override;
+    std::string GetState(OptimizerState* out) override;
+    std::string LoadState(const OptimizerState& state) override;
+    uint64_t GetStepCount() const override { return stepCount_; }
+    std::string UpdateLearningRate(float lr) override { config_.LearningRate = lr; return ""; }
+    std::string SetWeightBuffers(const std::vector<uintptr_t>& weightBuffers) override;
+    void SetCommandPool(uintptr_t) override {}
+    void Cleanup() override;
+    std::map<std::string, double> GetStats() const override;
+    float LearningRate() const override { return config_.LearningRate; }
+    const char* TypeName() const override { return "MixedAdam"; }
+    // fp32 master weights of tensor `index` (a fresh run starts from these; a resumed one from LoadState)
+    std::string InitMaster(int index, const float* data, int numel);
+    std::string ReadMaster(int index, float* out, int numel);
+    // waits for the stream; the device-resident loss-scale state
+    std::string LossScale(Backend::LossScaleC* out);
+
+private:
+    friend std::unique_ptr<MixedAdamOptimizerState> NewMixedAdamOptimizer(const MixedAdamConfig&, const Shapes&, memory::MemoryManager*, uintptr_t, std::string*);
+    std::string ensureList(const std::vector<uintptr_t>& grads);
+    MixedAdamConfig config_;
+    memory::MemoryManager* mm_ = nullptr;
+    uintptr_t device_ = 0, mixed_ = 0, list_ = 0;
+    std::vector<int> numel_;
+    std::vector<uintptr_t> weights16_, master_, momentum_, variance_, listGrads_, listWeights_;
+    uint64_t stepCount_ = 0;
+};
+std::unique_ptr<MixedAdamOptimizerState> NewMixedAdamOptimizer(const MixedAdamConfig&, const Shapes&, memory::MemoryManager*, uintptr_t device, std::string* err);
 
 // L-BFGS keeps its own Step signature (lbfgs.go:245) and refuses a learning rate (lbfgs.go:330-332).
 class LBFGSOptimizerState {

@@ -100,6 +100,7 @@ GMH_API void gmh_state_tensor_data(void* s, int i, float* out) {
 //   AdaDelta rho, epsilon, weight_decay
 //   Nadam    lr, beta1, beta2, epsilon, weight_decay
 //   LBFGS    history_size, line_search_tol, max_line_search, c1, c2, initial_step
+//   MixedAdam lr, beta1, beta2, epsilon, weight_decay, initial_loss_scale, growth, backoff, growth_interval, max_loss_scale
 GMH_API void* gmh_optimizer_create(const char* type, const double* cfg, int ncfg, const int* shape_flat, const int* shape_ndims,
                                    int num_weights, void* mm, uintptr_t device) {
     optimizer::Shapes shapes;
@@ -139,6 +140,12 @@ GMH_API void* gmh_optimizer_create(const char* type, const double* cfg, int ncfg
         optimizer::LBFGSConfig c; c.HistorySize = (int)get(0, c.HistorySize); c.LineSearchTol = (float)get(1, c.LineSearchTol);
         c.MaxLineSearch = (int)get(2, c.MaxLineSearch); c.C1 = (float)get(3, c.C1); c.C2 = (float)get(4, c.C2); c.InitialStep = (float)get(5, c.InitialStep);
         h->lbfgs = optimizer::NewLBFGSOptimizer(c, shapes, M, device, &err);
+    } else if (t == "MixedAdam") {
+        optimizer::MixedAdamConfig c; c.LearningRate = (float)get(0, c.LearningRate); c.Beta1 = (float)get(1, c.Beta1); c.Beta2 = (float)get(2, c.Beta2);
+        c.Epsilon = (float)get(3, c.Epsilon); c.WeightDecay = (float)get(4, c.WeightDecay); c.InitialLossScale = (float)get(5, c.InitialLossScale);
+        c.GrowthFactor = (float)get(6, c.GrowthFactor); c.BackoffFactor = (float)get(7, c.BackoffFactor);
+        c.GrowthInterval = (int)get(8, c.GrowthInterval); c.MaxLossScale = (float)get(9, c.MaxLossScale);
+        h->opt = optimizer::NewMixedAdamOptimizer(c, shapes, M, device, &err);
     } else {
         err = "unknown optimizer type: " + t;
     }
@@ -183,6 +190,25 @@ GMH_API int gmh_optimizer_load_state(void* h, void* s) {
     if (!o->opt) return fail("L-BFGS has no LoadState");
     return fail(o->opt->LoadState(*static_cast<OptimizerState*>(s)));
 }
+// ---- mixed-precision Adam extras ----
+static optimizer::MixedAdamOptimizerState* as_mixed(void* h) {
+    auto* o = static_cast<OptHandle*>(h);
+    return o && o->opt ? dynamic_cast<optimizer::MixedAdamOptimizerState*>(o->opt.get()) : nullptr;
+}
+GMH_API int gmh_mixed_init_master(void* h, int index, const float* data, int n) {
+    auto* m = as_mixed(h);
+    return m ? fail(m->InitMaster(index, data, n)) : fail("not a MixedAdam optimizer");
+}
+GMH_API int gmh_mixed_read_master(void* h, int index, float* out, int n) {
+    auto* m = as_mixed(h);
+    return m ? fail(m->ReadMaster(index, out, n)) : fail("not a MixedAdam optimizer");
+}
+// out: scale, growth, backoff, max_scale as floats, then interval, good_steps, adam_t, skipped, last_overflow as int32
+GMH_API int gmh_mixed_loss_scale(void* h, void* out) {
+    auto* m = as_mixed(h);
+    return m ? fail(m->LossScale(static_cast<Backend::LossScaleC*>(out))) : fail("not a MixedAdam optimizer");
+}
+
 GMH_API int gmh_lbfgs_history(void* h, int* count, int* index) {
     auto* o = static_cast<OptHandle*>(h);
     if (!o->lbfgs) return -1;

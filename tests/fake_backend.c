@@ -57,3 +57,42 @@ int execute_lbfgs_step_cuda(uintptr_t d, uintptr_t* w, uintptr_t* g, uintptr_t* 
                             int n, int* sizes, int m, int hc, int hi, float step0, float c1, float c2, int mls, float loss, float prev, float* out) {
     (void)d; (void)w; (void)g; (void)og; (void)dir; (void)s; (void)y; (void)rho; (void)alpha; (void)sizes; (void)c1; (void)c2; (void)mls;
     g_calls[LBFGS]++; g_last[0] = step0; g_last[1] = loss; g_last[2] = prev; g_last_int[0] = m; g_last_int[1] = hc; g_last_int[2] = n; g_last_int[3] = hi; if (out) *out = step0; return take_rc(); }
+
+/* ---- mixed precision: the loss-scale state is kept on the host side of the fake so that
+ * get/set round-trip; a step only counts the call and advances adam_t / good_steps. ---- */
+typedef struct { float scale, growth, backoff, max_scale; int32_t interval, good_steps, adam_t, skipped, last_overflow; } fake_ls_t;
+typedef struct { fake_ls_t ls; float beta1, beta2; } fake_mixed_t;
+enum { MIXED_STEP = 8, LIST_CREATE = 9, LIST_DESTROY = 10, MIXED_CREATE = 11, MIXED_DESTROY = 12 };
+static int g_list_streams, g_list_tensors, g_list_eb[8];
+int fake_list_streams(void) { return g_list_streams; }
+int fake_list_tensors(void) { return g_list_tensors; }
+int fake_list_elem_bytes(int s) { return g_list_eb[s]; }
+
+uintptr_t gm_mixed_create(uintptr_t dev, const fake_ls_t* init, float b1, float b2, int table_len) {
+    (void)table_len;
+    if (!dev) return 0;
+    fake_mixed_t* m = (fake_mixed_t*)calloc(1, sizeof *m);
+    if (init) m->ls = *init;
+    m->beta1 = b1; m->beta2 = b2;
+    g_calls[MIXED_CREATE]++; g_last[1] = b1; g_last[2] = b2;
+    return (uintptr_t)m;
+}
+void gm_mixed_destroy(uintptr_t m) { if (m) { g_calls[MIXED_DESTROY]++; free((void*)m); } }
+int gm_mixed_step_async(uintptr_t dev, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd) {
+    (void)dev; (void)list;
+    fake_mixed_t* m = (fake_mixed_t*)mixed;
+    g_calls[MIXED_STEP]++; g_last[0] = lr; g_last[3] = eps; g_last[4] = wd;
+    int rc = take_rc();
+    if (rc == 0) { m->ls.adam_t++; m->ls.good_steps++; }
+    return rc;
+}
+int gm_mixed_get_state(uintptr_t dev, uintptr_t mixed, fake_ls_t* out) { (void)dev; *out = ((fake_mixed_t*)mixed)->ls; return 0; }
+int gm_mixed_set_state(uintptr_t dev, uintptr_t mixed, const fake_ls_t* in) { (void)dev; ((fake_mixed_t*)mixed)->ls = *in; return 0; }
+uintptr_t gm_tensor_list_create(uintptr_t dev, int ns, int nt, const uintptr_t* const* ptrs, const int64_t* numel, const int* eb) {
+    (void)dev; (void)ptrs; (void)numel;
+    g_calls[LIST_CREATE]++; g_list_streams = ns; g_list_tensors = nt;
+    for (int s = 0; s < ns && s < 8; ++s) g_list_eb[s] = eb ? eb[s] : 4;
+    return (uintptr_t)malloc(8);
+}
+void gm_tensor_list_destroy(uintptr_t l) { if (l) { g_calls[LIST_DESTROY]++; free((void*)l); } }
+int gm_device_synchronize(uintptr_t dev) { (void)dev; return 0; }

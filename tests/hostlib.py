@@ -12,6 +12,14 @@ FAKE = os.path.join(HERE, "_build", "libfake_backend.so")
 CUDA = os.path.join(ROOT, "go-metal_b200", "lib", "libgometal_cuda.so")
 
 SGD, ADAM, ADAM_POOLED, RMSPROP, ADAGRAD, ADADELTA, NADAM, LBFGS = range(8)
+MIXED_STEP, LIST_CREATE, LIST_DESTROY, MIXED_CREATE, MIXED_DESTROY = range(8, 13)
+
+
+class LossScaleC(C.Structure):
+    """Layout of gm_loss_scale_t."""
+    _fields_ = [("scale", C.c_float), ("growth", C.c_float), ("backoff", C.c_float), ("max_scale", C.c_float),
+                ("interval", C.c_int32), ("good_steps", C.c_int32), ("adam_t", C.c_int32), ("skipped", C.c_int32),
+                ("last_overflow", C.c_int32)]
 
 
 def build_fake():
@@ -49,6 +57,8 @@ def load_host():
         "gmh_optimizer_step_count": (C.c_uint64, [vp]), "gmh_optimizer_update_lr": (i, [vp, f]), "gmh_optimizer_lr": (f, [vp]),
         "gmh_optimizer_type": (s, [vp]), "gmh_optimizer_set_command_pool": (None, [vp, u]), "gmh_optimizer_cleanup": (None, [vp]),
         "gmh_optimizer_stat": (d, [vp, s]), "gmh_optimizer_get_state": (vp, [vp]), "gmh_optimizer_load_state": (i, [vp, vp]),
+        "gmh_mixed_init_master": (i, [vp, i, vp, i]), "gmh_mixed_read_master": (i, [vp, i, vp, i]),
+        "gmh_mixed_loss_scale": (i, [vp, vp]),
         "gmh_lbfgs_history": (i, [vp, ip, ip]), "gmh_lbfgs_read_rho": (i, [vp, vp, i]),
         "gmh_sched_create": (vp, [i, i, d, d, s]), "gmh_sched_destroy": (None, [vp]), "gmh_sched_get_lr": (d, [vp, i, i, d]),
         "gmh_sched_step": (d, [vp, d, d]), "gmh_sched_name": (s, [vp]), "gmh_apply_scheduler": (i, [vp, vp, i, i, d]),

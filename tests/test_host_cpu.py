@@ -326,6 +326,92 @@ def test_state_structure_and_round_trip(env):
     H.gmh_optimizer_destroy(o)
 
 
+def test_mixed_adam_host_logic(env):
+    """The mixed-precision optimizer type: defaults of training/model_trainer.go:258-270 reach the backend,
+    the tensor list has the five streams (g16, master, m, v, p16) and is rebuilt only when a pointer changes,
+    the checkpoint payload carries the loss-scale fields and survives a float64 (JSON) round trip."""
+    H, fake, mm, dev = env
+    shapes = [[4, 3], [5]]
+    o = HL.make_optimizer(H, "MixedAdam", [], shapes, mm, dev)
+    assert o, HL.err(H)
+    assert H.gmh_optimizer_type(o) == b"MixedAdam" and abs(H.gmh_optimizer_lr(o) - 0.001) < 1e-9
+    assert fake.fake_calls(HL.MIXED_CREATE) == 1 and fake.fake_allocs() == 6          # master, m, v per weight
+    assert H.gmh_optimizer_stat(o, b"TotalBufferSize") == 3 * (12 + 5) * 4
+    ls = HL.LossScaleC()
+    assert H.gmh_mixed_loss_scale(o, C.byref(ls)) == 0
+    assert (ls.scale, ls.growth, ls.backoff, ls.interval, ls.max_scale) == (65536.0, 2.0, 0.5, 2000, 16777216.0)
+
+    w16 = [H.gmh_mm_allocate(mm, 24), H.gmh_mm_allocate(mm, 10)]
+    g16 = [H.gmh_mm_allocate(mm, 24), H.gmh_mm_allocate(mm, 10)]
+    assert H.gmh_optimizer_step(o, HL.uarr(g16), 2, 0.0) != 0 and "weight buffer 0 is nil" in HL.err(H)
+    assert H.gmh_optimizer_set_weight_buffers(o, HL.uarr(w16[:1]), 1) != 0
+    assert H.gmh_optimizer_set_weight_buffers(o, HL.uarr(w16), 2) == 0
+    assert H.gmh_optimizer_step(o, HL.uarr(g16[:1]), 1, 0.0) != 0
+    assert HL.err(H) == "gradient buffers length (1) doesn't match weight buffers length (2)"
+    for _ in range(3):
+        assert H.gmh_optimizer_step(o, HL.uarr(g16), 2, 0.0) == 0, HL.err(H)
+    assert fake.fake_calls(HL.MIXED_STEP) == 3 and fake.fake_calls(HL.LIST_CREATE) == 1
+    assert (fake.fake_list_streams(), fake.fake_list_tensors()) == (5, 2)
+    assert [fake.fake_list_elem_bytes(s) for s in range(5)] == [2, 4, 4, 4, 2]
+    assert abs(fake.fake_last_float(0) - 0.001) < 1e-9 and abs(fake.fake_last_float(3) - 1e-8) < 1e-12
+    g16b = [g16[1], g16[0]]
+    g16b[1] = H.gmh_mm_allocate(mm, 24)
+    assert H.gmh_optimizer_step(o, HL.uarr([g16b[1], g16[1]]), 2, 0.0) == 0
+    assert fake.fake_calls(HL.LIST_CREATE) == 2 and fake.fake_calls(HL.LIST_DESTROY) == 1   # new gradient buffer: new list
+    assert H.gmh_optimizer_step_count(o) == 4
+    fake.fake_next_return(-8)
+    assert H.gmh_optimizer_step(o, HL.uarr([g16b[1], g16[1]]), 2, 0.0) != 0
+    assert "MixedAdam step failed with error code: -8" in HL.err(H)
+
+    master = np.arange(12, dtype=np.float32) / 8
+    assert H.gmh_mixed_init_master(o, 0, master.ctypes.data, 12) == 0
+    assert H.gmh_mixed_init_master(o, 0, master.ctypes.data, 11) != 0
+    assert HL.err(H) == "data size mismatch for master_0: expected 12 elements, got 11"
+    st = H.gmh_optimizer_get_state(o)
+    assert st and H.gmh_state_type(st) == b"MixedAdam"
+    names = [H.gmh_state_tensor_name(st, i).decode() for i in range(H.gmh_state_num_tensors(st))]
+    assert names == ["master_0", "master_1", "momentum_0", "momentum_1", "variance_0", "variance_1"]
+    got = np.zeros(12, np.float32)
+    H.gmh_state_tensor_data(st, 0, got.ctypes.data)
+    assert np.array_equal(got, master)
+    val = C.c_double()
+    kinds = {}
+    for key in (b"loss_scale", b"growth_factor", b"backoff_factor", b"max_loss_scale", b"growth_interval", b"good_steps",
+                b"skipped_steps", b"adam_step", b"step_count", b"learning_rate"):
+        kinds[key] = (H.gmh_state_get_param(st, key, C.byref(val)), val.value)
+    assert kinds[b"loss_scale"] == (3, 65536.0) and kinds[b"growth_interval"] == (2, 2000.0)
+    assert kinds[b"adam_step"] == (2, 4.0) and kinds[b"step_count"] == (2, 5.0) and kinds[b"good_steps"] == (2, 4.0)
+    H.gmh_state_destroy(st)
+
+    # resume into a fresh optimizer from a payload whose numbers are all float64, as after JSON
+    o2 = HL.make_optimizer(H, "MixedAdam", [], shapes, mm, dev)
+    new = H.gmh_state_new(b"MixedAdam")
+    for key, v in ((b"loss_scale", 1024.0), (b"good_steps", 77.0), (b"skipped_steps", 3.0), (b"adam_step", 40.0),
+                   (b"step_count", 43.0), (b"learning_rate", 0.5), (b"growth_interval", 100.0)):
+        H.gmh_state_set_float64(new, key, v)
+    H.gmh_state_add_tensor(new, b"master_0", b"master", master.ctypes.data, 12)
+    assert H.gmh_optimizer_load_state(o2, new) == 0, HL.err(H)
+    assert H.gmh_mixed_loss_scale(o2, C.byref(ls)) == 0
+    assert (ls.scale, ls.good_steps, ls.skipped, ls.adam_t, ls.interval, ls.growth) == (1024.0, 77, 3, 40, 100, 2.0)
+    assert H.gmh_optimizer_step_count(o2) == 43 and H.gmh_optimizer_lr(o2) == 0.5
+    got[:] = 0
+    assert H.gmh_mixed_read_master(o2, 0, got.ctypes.data, 12) == 0 and np.array_equal(got, master)
+    H.gmh_state_set_float64(new, b"beta1", 0.5)
+    assert H.gmh_optimizer_load_state(o2, new) != 0 and "beta1/beta2 of the saved state" in HL.err(H)
+    H.gmh_state_destroy(new)
+    wrong = H.gmh_state_new(b"Adam")
+    assert H.gmh_optimizer_load_state(o2, wrong) != 0 and HL.err(H) == "state type mismatch: expected MixedAdam, got Adam"
+    H.gmh_state_destroy(wrong)
+    for cfg, msg in (([0.001, 0.9, 0.999, 1e-8, 0, 0.0], "initial loss scale must be positive"),
+                     ([0.001, 0.9, 0.999, 1e-8, 0, 65536, 0.5], "growth factor must be at least 1"),
+                     ([0.001, 0.9, 0.999, 1e-8, 0, 65536, 2, 1.0], "backoff factor must be in (0, 1)"),
+                     ([0.001, 0.9, 0.999, 1e-8, 0, 65536, 2, 0.5, 0], "growth interval must be positive")):
+        assert not HL.make_optimizer(H, "MixedAdam", cfg, shapes, mm, dev) and msg in HL.err(H)
+    H.gmh_optimizer_destroy(o)
+    H.gmh_optimizer_destroy(o2)
+    assert fake.fake_calls(HL.MIXED_DESTROY) == 2
+
+
 # ---------------- schedulers ----------------
 
 def test_scheduler_tables(H):

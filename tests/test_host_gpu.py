@@ -189,3 +189,102 @@ def test_lbfgs_through_host_mirror(gm, H, oracle):
         gm.lib.deallocate_cuda_buffer(p)
     H.gmh_mm_destroy(mm)
     H.gmh_device_destroy(dev)
+
+
+def test_mixed_adam_through_host_mirror_with_checkpoint_resume(gm, H, oracle):
+    """The mixed-precision optimizer type on the real library: fp16 gradients in, fp32
+    master weights and fp16 parameters out, the loss scale growing (interval 4) and
+    backing off (one injected inf) on the device; then GetState -> a payload with
+    float64 numbers, as after JSON -> LoadState into a fresh optimizer -> the
+    continuation equals the oracle's uninterrupted run bit for bit."""
+    O, L = oracle, gm.lib
+    dev = H.gmh_device_create()
+    assert dev, HL.err(H)
+    mm = H.gmh_mm_create(dev)
+    shapes = [[33], [4097], [7, 9]]
+    sizes = [33, 4097, 63]
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.999, 1e-8, 0.01
+    cfg = [lr, b1, b2, eps, wd, 65536.0, 2.0, 0.5, 4]
+    master = [O.fill_uniform(n, -0.05, 0.05, 21, 50 + k) for k, n in enumerate(sizes)]
+    m = [np.zeros(n, np.float32) for n in sizes]
+    v = [np.zeros(n, np.float32) for n in sizes]
+    p16 = [O.f32_to_f16(w) for w in master]
+    st = O.new_loss_scale(interval=4)
+
+    def alloc16(arr):
+        p = L.allocate_cuda_buffer(dev, arr.size * 2, 1)
+        assert p, gm.last_error()
+        gm.check(L.copy_data_to_cuda_buffer(p, arr.ctypes.data, arr.size * 2), "upload")
+        return p
+
+    wp = [alloc16(a) for a in p16]
+    gp = [alloc16(np.zeros(n, np.uint16)) for n in sizes]
+
+    def make():
+        o = HL.make_optimizer(H, "MixedAdam", cfg, shapes, mm, dev)
+        assert o, HL.err(H)
+        assert H.gmh_optimizer_set_weight_buffers(o, HL.uarr(wp), 3) == 0
+        return o
+
+    rng = np.random.default_rng(5)
+
+    def step(o, k, inject):
+        scale = np.float32(st.scale)
+        g16 = [O.f32_to_f16(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3) * scale) for n in sizes]
+        if inject:
+            g16[1][4000] = 0x7c00
+        for p, g in zip(gp, g16):
+            gm.check(L.copy_data_to_cuda_buffer(p, g.ctypes.data, g.size * 2), "upload")
+        assert H.gmh_optimizer_step(o, HL.uarr(gp), 3, 0.0) == 0, HL.err(H)
+        skipped = O.mixed_adam_step(g16, master, m, v, p16, lr, b1, b2, eps, wd, st)
+        assert skipped == (1 if inject else 0)
+        ls = HL.LossScaleC()
+        assert H.gmh_mixed_loss_scale(o, C.byref(ls)) == 0, HL.err(H)
+        assert (ls.scale, ls.good_steps, ls.adam_t, ls.skipped) == (st.scale, st.good_steps, st.adam_t, st.skipped), f"step {k}"
+
+    def compare(o, what):
+        for t, n in enumerate(sizes):
+            got = np.empty(n, np.float32)
+            assert H.gmh_mixed_read_master(o, t, got.ctypes.data, n) == 0, HL.err(H)
+            assert np.array_equal(got.view(np.uint32), master[t].view(np.uint32)), f"{what}: master_{t}"
+            h = np.empty(n, np.uint16)
+            gm.check(L.gm_buffer_download(dev, wp[t], h.ctypes.data, n * 2), "download")
+            assert np.array_equal(h, p16[t]), f"{what}: fp16 parameters {t}"
+
+    opt = make()
+    for t, w in enumerate(master):
+        assert H.gmh_mixed_init_master(opt, t, w.ctypes.data, w.size) == 0, HL.err(H)
+    for k in range(1, 7):
+        step(opt, k, inject=(k == 3))
+    compare(opt, "before the checkpoint")
+    assert st.scale == 32768.0 and st.skipped == 1 and st.good_steps == 3    # halved at step 3; the 4th clean step comes after the resume
+
+    got = H.gmh_optimizer_get_state(opt)
+    assert got and H.gmh_state_num_tensors(got) == 9
+    saved = H.gmh_state_new(b"MixedAdam")
+    val = C.c_double()
+    for key in (b"learning_rate", b"epsilon", b"weight_decay", b"beta1", b"beta2", b"loss_scale", b"growth_factor",
+                b"backoff_factor", b"max_loss_scale", b"growth_interval", b"good_steps", b"skipped_steps", b"adam_step",
+                b"step_count"):
+        assert H.gmh_state_get_param(got, key, C.byref(val)) >= 0, key
+        H.gmh_state_set_float64(saved, key, val.value)
+    for i in range(9):
+        n = H.gmh_state_tensor_numel(got, i)
+        buf = np.empty(n, np.float32)
+        H.gmh_state_tensor_data(got, i, buf.ctypes.data)
+        H.gmh_state_add_tensor(saved, H.gmh_state_tensor_name(got, i), H.gmh_state_tensor_type(got, i), buf.ctypes.data, n)
+    H.gmh_state_destroy(got)
+    H.gmh_optimizer_destroy(opt)
+
+    opt2 = make()
+    assert H.gmh_optimizer_load_state(opt2, saved) == 0, HL.err(H)
+    assert H.gmh_optimizer_step_count(opt2) == 6
+    for k in range(7, 12):
+        step(opt2, k, inject=(k == 9))
+    compare(opt2, "after the resume")
+    H.gmh_state_destroy(saved)
+    H.gmh_optimizer_destroy(opt2)
+    for p in wp + gp:
+        L.deallocate_cuda_buffer(p)
+    H.gmh_mm_destroy(mm)
+    H.gmh_device_destroy(dev)
