@@ -403,6 +403,7 @@ void destroy_cuda_device(uintptr_t h) {
     for (auto& kv : d->list_cache) lists.push_back(kv.second);
     d->list_cache.clear();
     for (TensorList* l : lists) free_list(l);
+    lbfgs_release_device(d);
     if (d->partials) cudaFree(d->partials);
     if (d->ticket) cudaFree(d->ticket);
     if (d->scalars) cudaFree(d->scalars);

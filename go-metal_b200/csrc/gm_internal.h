@@ -113,6 +113,7 @@ int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items);
 int ensure_partials(Device* d, int64_t count);
 
 // ---- rule launchers (gm_rules.cu) ----
+void lbfgs_release_device(Device* d);           // frees the L-BFGS pointer tables cached for a device
 int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h);
 
 // ---- mixed precision (gm_mixed.cu) ----

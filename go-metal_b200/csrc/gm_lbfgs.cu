@@ -450,6 +450,15 @@ static int axpy_grid(Device* d, int num_chunks) {
     return (int)((num_chunks + rounds - 1) / rounds);
 }
 
+// Called when a device handle is destroyed: its pointer tables go with it.
+void lbfgs_release_device(Device* d) {
+    std::lock_guard<std::mutex> lk(g_lb_mu);
+    auto it = g_lb.find(d);
+    if (it == g_lb.end()) return;
+    for (LbfgsCtx* c : it->second) { cudaFree(c->blob); delete c; }
+    g_lb.erase(it);
+}
+
 static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in) {
     LbfgsOp op = op_in;
     if (op.kind <= 2) {
