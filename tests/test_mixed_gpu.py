@@ -245,3 +245,72 @@ def test_grad_sumsq(gm, dev, oracle):
             dev.free(p)
     finally:
         dev.free(out)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_alignments_mixed(gm, dev, oracle, seed):
+    """Seeded fuzz of the mixed-precision step: 1-10 tensors of 1-40,000 elements, each
+    of the five streams of each tensor at a random element offset (shared by the streams
+    of a tensor in 60 % of the lists, independent otherwise, which forces the
+    element-wise path); four steps with an overflow injected in one of them; state,
+    master weights, moments and fp16 parameters bit-exact, nothing written outside."""
+    O, L = oracle, gm.lib
+    rng = np.random.default_rng(500 + seed)
+    special = [1, 7, 8, 9, 2047, 2048, 2049, 8191, 8192, 8193, 16385]
+    nt = int(rng.integers(1, 11))
+    sizes = [int(rng.choice(special)) if rng.random() < 0.5 else int(rng.integers(1, 40001)) for _ in range(nt)]
+    keys, eb = "gwmvp", {"g": 2, "w": 4, "m": 4, "v": 4, "p": 2}
+    dt = {k: (np.uint16 if eb[k] == 2 else np.float32) for k in keys}
+    span = sum(sizes) + 16 * nt + 32
+    shared = rng.random() < 0.6
+    offs = {k: [0] * nt for k in keys}
+    at = 8
+    for t, n in enumerate(sizes):
+        base = int(rng.integers(0, 8))
+        for k in keys:
+            offs[k][t] = at + (base if shared else int(rng.integers(0, 8)))
+        at += n + 16
+    host = {k: np.zeros(span, dt[k]) for k in keys}
+    master = [O.fill_uniform(n, -0.05, 0.05, 31 + seed, 50 + t) for t, n in enumerate(sizes)]
+    m = [np.zeros(n, np.float32) for n in sizes]
+    v = [np.zeros(n, np.float32) for n in sizes]
+    p16 = [O.f32_to_f16(w) for w in master]
+    host["w"][:] = 3.0                                       # canary values between the tensors
+    host["p"][:] = 0x1234
+    for t, n in enumerate(sizes):
+        host["w"][offs["w"][t]:offs["w"][t] + n] = master[t]
+        host["p"][offs["p"][t]:offs["p"][t] + n] = p16[t]
+    bufs = {k: dev.to_device(host[k]) for k in keys}
+    lst = dev.tensor_list([[bufs[k] + eb[k] * offs[k][t] for t in range(nt)] for k in keys], sizes, [eb[k] for k in keys])
+    st = O.new_loss_scale(interval=2)
+    init = gm.LossScale(scale=st.scale, growth=st.growth, backoff=st.backoff, max_scale=st.max_scale,
+                        interval=st.interval, good_steps=0, adam_t=0, skipped=0, last_overflow=0)
+    mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
+    bad_step = int(rng.integers(1, 5))
+    try:
+        for step in range(1, 5):
+            scale = np.float32(st.scale)
+            g16 = [O.f32_to_f16(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3) * scale) for n in sizes]
+            if step == bad_step:
+                t = int(rng.integers(nt))
+                g16[t][int(rng.integers(sizes[t]))] = 0x7e00
+            for t, n in enumerate(sizes):
+                host["g"][offs["g"][t]:offs["g"][t] + n] = g16[t]
+            dev.upload(bufs["g"], host["g"])
+            gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed step")
+            skipped = O.mixed_adam_step(g16, master, m, v, p16, LR, B1, B2, EPS, WD, st)
+            assert skipped == (1 if step == bad_step else 0)
+            got = gm.LossScale()
+            gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(got)), "state")
+            assert same_state(got, st), f"seed {seed} step {step}"
+            for k, arrs in (("w", master), ("m", m), ("v", v), ("p", p16)):
+                for t, n in enumerate(sizes):
+                    host[k][offs[k][t]:offs[k][t] + n] = arrs[t]
+                dev_now = dev.to_host(bufs[k], span, dt[k])
+                assert np.array_equal(dev_now.view(np.uint8), host[k].view(np.uint8)), (
+                    f"seed {seed} step {step} stream {k}: sizes {sizes} offsets {offs[k]} shared={shared}")
+    finally:
+        L.gm_mixed_destroy(mx)
+        L.gm_tensor_list_destroy(lst)
+        for k in keys:
+            dev.free(bufs[k])

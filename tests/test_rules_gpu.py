@@ -375,3 +375,93 @@ def test_host_buffer_step_matches_oracle(gm, dev, oracle, sizes):
         L.gm_host_free_pinned(hw)
         for p in (dw, dg, dm, dv):
             dev.free(p)
+
+
+FUZZ_RULES = ["sgd_plain", "sgd_momentum", "adam", "nadam", "rmsprop", "rmsprop_both", "adagrad", "adadelta"]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_ragged_lists_every_rule(gm, dev, oracle, seed):
+    """Seeded fuzz through the tensor-list entry: 1-12 tensors of 1-20,000 elements
+    (sizes biased towards the chunk and vector boundaries), each stream of each tensor at
+    its own random element offset inside one arena, so aligned, peelable and
+    inconsistently aligned tensors all occur; every rule, three steps, bit-exact, and no
+    byte outside the tensors may change."""
+    O, L = oracle, gm.lib
+    rng = np.random.default_rng(1000 + seed)
+    special = [1, 2, 3, 4, 5, 7, 8, 255, 256, 257, 1023, 1024, 1025, 4095, 4096, 4097, 4099, 8191, 8192, 8193, 12289]
+    for rule in FUZZ_RULES:
+        nt = int(rng.integers(1, 13))
+        sizes = [int(rng.choice(special)) if rng.random() < 0.5 else int(rng.integers(1, 20001)) for _ in range(nt)]
+        ns = {"sgd_plain": 2, "sgd_momentum": 3, "adam": 4, "nadam": 4, "rmsprop": 3, "rmsprop_both": 5, "adagrad": 3,
+              "adadelta": 4}[rule]
+        same_alignment = rng.random() < 0.6                    # else every stream draws its own offset
+        span = sum(sizes) + 8 * nt + 16
+        host = [np.zeros(span, np.float32) for _ in range(ns)]
+        offs = [[0] * nt for _ in range(ns)]
+        at = 4
+        for t, n in enumerate(sizes):
+            base_shift = int(rng.integers(0, 4))
+            for s in range(ns):
+                offs[s][t] = at + (base_shift if same_alignment else int(rng.integers(0, 4)))
+            at += n + 8
+        host[0][:] = O.fill_uniform(span, -0.5, 0.5, 77 + seed, 1)
+        canary = [h.copy() for h in host]
+        bufs = [dev.to_device(h) for h in host]
+        lst = dev.tensor_list([[bufs[s] + 4 * offs[s][t] for t in range(nt)] for s in range(ns)], sizes)
+        wd = float(rng.choice([0.0, 0.01]))
+        hy = {"sgd_plain": gm.Hyper(lr=0.05, beta1=0.0, weight_decay=wd),
+              "sgd_momentum": gm.Hyper(lr=0.05, beta1=0.9, weight_decay=wd, nesterov=int(rng.integers(0, 2))),
+              "adam": gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=wd),
+              "nadam": gm.Hyper(lr=2e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=wd),
+              "rmsprop": gm.Hyper(lr=0.01, beta1=0.99, eps=1e-8, weight_decay=wd),
+              "rmsprop_both": gm.Hyper(lr=0.01, beta1=0.99, eps=1e-8, weight_decay=wd, momentum=0.9, centered=1),
+              "adagrad": gm.Hyper(lr=0.01, eps=1e-10, weight_decay=wd),
+              "adadelta": gm.Hyper(beta1=0.9, eps=1e-6, weight_decay=wd)}[rule]
+        rid = {"sgd_plain": gm.RULE_SGD, "sgd_momentum": gm.RULE_SGD, "adam": gm.RULE_ADAM, "nadam": gm.RULE_NADAM,
+               "rmsprop": gm.RULE_RMSPROP, "rmsprop_both": gm.RULE_RMSPROP, "adagrad": gm.RULE_ADAGRAD,
+               "adadelta": gm.RULE_ADADELTA}[rule]
+        try:
+            for step in (1, 2, 3):
+                g_full = O.fill_normal(span, 0.0, 0.01, 77 + seed, 10 + step)
+                for t, n in enumerate(sizes):
+                    host[1][offs[1][t]:offs[1][t] + n] = g_full[offs[1][t]:offs[1][t] + n]
+                dev.upload(bufs[1], host[1])
+                hy.step = step
+                gm.check(L.gm_step_async(dev.h, rid, lst, C.byref(hy)), rule)
+                dev.sync()
+                for t, n in enumerate(sizes):
+                    x = [np.ascontiguousarray(host[s][offs[s][t]:offs[s][t] + n]) for s in range(ns)]
+                    if rule == "sgd_plain":
+                        O.sgd_step(x[0], x[1], None, hy.lr, 0.0, wd, 0)
+                    elif rule == "sgd_momentum":
+                        O.sgd_step(x[0], x[1], x[2], hy.lr, 0.9, wd, hy.nesterov)
+                    elif rule == "adam":
+                        O.adam_step(x[0], x[1], x[2], x[3], hy.lr, 0.9, 0.999, 1e-8, wd, step)
+                    elif rule == "nadam":
+                        O.nadam_step(x[0], x[1], x[2], x[3], hy.lr, 0.9, 0.999, 1e-8, wd, step)
+                    elif rule == "rmsprop":
+                        O.rmsprop_step(x[0], x[1], x[2], None, None, hy.lr, 0.99, 1e-8, wd, 0.0, False)
+                    elif rule == "rmsprop_both":
+                        O.rmsprop_step(x[0], x[1], x[2], x[3], x[4], hy.lr, 0.99, 1e-8, wd, 0.9, True, True)
+                    elif rule == "adagrad":
+                        O.adagrad_step(x[0], x[1], x[2], hy.lr, 1e-10, wd)
+                    else:
+                        O.adadelta_step(x[0], x[1], x[2], x[3], 0.9, 1e-6, wd)
+                    for s in range(ns):
+                        if s != 1:
+                            host[s][offs[s][t]:offs[s][t] + n] = x[s]
+                for s in range(ns):
+                    got = dev.to_host(bufs[s], span)
+                    assert np.array_equal(got.view(np.uint32), host[s].view(np.uint32)), (
+                        f"seed {seed} {rule} step {step} stream {s}: sizes {sizes} offsets {offs[s]}")
+            # bytes between the tensors still hold what they held at the start
+            for s in range(ns):
+                mask = np.ones(span, bool)
+                for t, n in enumerate(sizes):
+                    mask[offs[s][t]:offs[s][t] + n] = False
+                assert np.array_equal(host[s][mask].view(np.uint32), canary[s][mask].view(np.uint32))
+        finally:
+            L.gm_tensor_list_destroy(lst)
+            for b in bufs:
+                dev.free(b)
