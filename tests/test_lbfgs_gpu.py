@@ -24,7 +24,7 @@ def same_bits(a, b):
 
 
 class LbfgsProblem:
-    def __init__(self, gm, dev, O, sizes, m, lo_exp, hi_exp, seed):
+    def __init__(self, gm, dev, O, sizes, m, lo_exp, hi_exp, seed, shifts=None):
         self.gm, self.dev, self.O, self.sizes, self.m = gm, dev, O, sizes, m
         self.D = [O.fill_loguniform(n, lo_exp, hi_exp, seed, 1 + k) for k, n in enumerate(sizes)]
         self.b = [O.fill_normal(n, 0.0, 1.0, seed, 100 + k) for k, n in enumerate(sizes)]
@@ -36,7 +36,17 @@ class LbfgsProblem:
         self.rho = np.zeros(m, dtype=np.float32)
         self.alpha = np.zeros(m, dtype=np.float32)
         # device side
-        alloc = lambda n: dev.to_device(np.zeros(n, dtype=np.float32))
+        # shifts: element offsets (cycled over the buffers as they are allocated) that move
+        # buffers off their 16-byte boundary, so some tensors take the element-wise path
+        self._bases = []
+        self._count = 0
+
+        def alloc(n):
+            base = dev.to_device(np.zeros(n + 8, dtype=np.float32))
+            self._bases.append(base)
+            shift = shifts[self._count % len(shifts)] if shifts else 0
+            self._count += 1
+            return base + 4 * shift
         self.dx = [alloc(n) for n in sizes]
         self.dg = [alloc(n) for n in sizes]
         self.dold = [alloc(n) for n in sizes]
@@ -48,13 +58,8 @@ class LbfgsProblem:
         self.hc = self.hi = 0
 
     def free(self):
-        for group in (self.dx, self.dg, self.dold, self.ddir, self.drho, [self.dalpha]):
-            for p in group:
-                self.dev.free(p)
-        for hist in (self.ds, self.dy):
-            for slot in hist:
-                for p in slot:
-                    self.dev.free(p)
+        for p in self._bases:
+            self.dev.free(p)
 
     def gradient(self, x):
         return [(D * xi - b).astype(np.float32) for D, xi, b in zip(self.D, x, self.b)]
@@ -155,6 +160,21 @@ def test_lbfgs_multi_tensor_short_history(gm, dev, oracle):
     P = LbfgsProblem(gm, dev, oracle, [4097, 1, 70_001, 12_288], 3, -0.2, 0.2, seed=23)
     try:
         for it in range(20):
+            P.step(3)
+            P.compare(it, full=True)
+    finally:
+        P.free()
+
+
+@pytest.mark.parametrize("shifts", [[1], [0, 0, 0, 2, 0, 1, 0]], ids=["all_off_by_one", "columns_disagree"])
+def test_lbfgs_unaligned_buffers(gm, dev, oracle, shifts):
+    """Buffers that do not start on a 16-byte boundary (every one shifted by one element,
+    or only some columns of some tensors): the passes fall back to element-wise access
+    with the same summation order, so every value stays bit-identical."""
+    gm.check(gm.lib.gm_lbfgs_set_mode(dev.h, 3), "mode")
+    P = LbfgsProblem(gm, dev, oracle, [4097, 3, 20_001, 8192], 4, -0.2, 0.2, seed=25, shifts=shifts)
+    try:
+        for it in range(9):
             P.step(3)
             P.compare(it, full=True)
     finally:
