@@ -272,6 +272,14 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     const int tile = kApplyThreads * 8;
     int chunk = 2 * tile;                               // 4096: best of a 2048..65536 sweep on B200 (fp32 lists)
     for (int s = 0; s < ns; ++s) if (l->elem_bytes[s] == 2) chunk = 4 * tile;   // fp16 streams: 8192 measured best
+    // Small lists are latency-bound, not bandwidth-bound: one pass per CTA (1,024
+    // elements) and more CTAs shorten the chain of dependent loads a CTA walks
+    // (MLP-sized list: 6 us -> 3 us per launch).
+    if (chunk == 2 * tile) {
+        const int64_t one_wave = (int64_t)d->sm_count * 5 * 1024;     // every chunk resident at once
+        if (total <= one_wave) chunk = 1024;
+        else if (total <= 2 * one_wave) chunk = 2048;
+    }
     if (d->chunk_elems > 0) chunk = (d->chunk_elems + tile - 1) / tile * tile;
 
     // head[t]: number of leading elements to peel so that every stream of the
