@@ -10,6 +10,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+
 #include <set>
 
 #include "gm_internal.h"
@@ -70,6 +72,10 @@ static Arena* as_arena(uintptr_t h) {
     return g_arenas.count(a) ? a : nullptr;
 }
 
+// Bumped by every allocation and release the library performs; a cached tensor
+// list validated under the current value needs no second look at the registry.
+static std::atomic<uint64_t> g_registry_gen{1};
+
 int64_t registered_size(uintptr_t p) {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_bufs.find(p);
@@ -94,6 +100,7 @@ static uintptr_t alloc_registered(Device* d, int64_t bytes) {
     if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc"); cudaGetLastError(); return 0; }
     std::lock_guard<std::mutex> lk(g_mu);
     g_bufs[(uintptr_t)p] = BufInfo{bytes, d->ordinal, true};
+    g_registry_gen.fetch_add(1, std::memory_order_release);
     return (uintptr_t)p;
 }
 
@@ -106,6 +113,7 @@ static void free_registered(uintptr_t p) {
         if (it == g_bufs.end() || !it->second.owned) return;   // not ours: leave it alone
         info = it->second;
         g_bufs.erase(it);
+        g_registry_gen.fetch_add(1, std::memory_order_release);
     }
     int prev = -1;
     cudaGetDevice(&prev);
@@ -213,22 +221,26 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     *err = GM_OK;
     if (ns < 1 || ns > kMaxStreams) { set_error("stream count %d outside [1,%d]", ns, kMaxStreams); *err = GM_ERR_BAD_ARG; return nullptr; }
     if (nt < 1) { set_error("tensor count %d is not positive", nt); *err = GM_ERR_BAD_ARG; return nullptr; }
-    for (int t = 0; t < nt; ++t) {
-        if (numel[t] <= 0) { set_error("tensor %d has %lld elements", t, (long long)numel[t]); *err = GM_ERR_BAD_SIZE; return nullptr; }
-        for (int s = 0; s < ns; ++s) {
-            uintptr_t p = sp[s][t];
-            if (p == 0) { set_error("stream %d tensor %d is a nil buffer", s, t); *err = GM_ERR_NIL_BUFFER; return nullptr; }
-            int eb = elem_bytes ? elem_bytes[s] : 4;
-            if (p % (uintptr_t)eb) { set_error("stream %d tensor %d address is not %d-byte aligned", s, t, eb); *err = GM_ERR_BAD_ARG; return nullptr; }
-            int64_t have = registered_size(p);
-            if (have >= 0 && have < numel[t] * eb) {
-                set_error("stream %d tensor %d: buffer holds %lld bytes, step needs %lld", s, t,
-                          (long long)have, (long long)(numel[t] * eb));
-                *err = GM_ERR_BAD_SIZE;
-                return nullptr;
+    const uint64_t gen = g_registry_gen.load(std::memory_order_acquire);
+    auto validate = [&]() -> bool {
+        for (int t = 0; t < nt; ++t) {
+            if (numel[t] <= 0) { set_error("tensor %d has %lld elements", t, (long long)numel[t]); *err = GM_ERR_BAD_SIZE; return false; }
+            for (int s = 0; s < ns; ++s) {
+                uintptr_t p = sp[s][t];
+                if (p == 0) { set_error("stream %d tensor %d is a nil buffer", s, t); *err = GM_ERR_NIL_BUFFER; return false; }
+                int eb = elem_bytes ? elem_bytes[s] : 4;
+                if (p % (uintptr_t)eb) { set_error("stream %d tensor %d address is not %d-byte aligned", s, t, eb); *err = GM_ERR_BAD_ARG; return false; }
+                int64_t have = registered_size(p);
+                if (have >= 0 && have < numel[t] * eb) {
+                    set_error("stream %d tensor %d: buffer holds %lld bytes, step needs %lld", s, t,
+                              (long long)have, (long long)(numel[t] * eb));
+                    *err = GM_ERR_BAD_SIZE;
+                    return false;
+                }
             }
         }
-    }
+        return true;
+    };
     uint64_t key = 0xcbf29ce484222325ull;
     key = fnv1a(key, &ns, sizeof(ns));
     key = fnv1a(key, &nt, sizeof(nt));
@@ -249,14 +261,25 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
                 same = memcmp(l->ptrs[s].data(), sp[s], sizeof(uintptr_t) * nt) == 0
                        && l->elem_bytes[s] == (elem_bytes ? elem_bytes[s] : 4);
             if (same) same = memcmp(l->numel.data(), numel, sizeof(int64_t) * nt) == 0;
-            if (same) return l;
+            if (same) {
+                // pointers and sizes are those of the cached list; the registry is consulted
+                // again only if something was allocated or released since it was last checked
+                if (l->validated_gen != gen) {
+                    if (!validate()) return nullptr;
+                    l->validated_gen = gen;
+                }
+                return l;
+            }
             d->list_cache.erase(it);   // hash collision: rebuild below
             free_list(l);
         }
     }
 
+    if (!validate()) return nullptr;
+
     TensorList* l = new TensorList();
     l->dev = d;
+    l->validated_gen = gen;
     l->numel.assign(numel, numel + nt);
     l->ptrs.resize(ns);
     for (int s = 0; s < ns; ++s) {
@@ -356,6 +379,10 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
             for (TensorList* o : old) free_list(o);
         }
         l->key = key;
+        auto prev = d->list_cache.find(key);
+        // another thread cached the same list meanwhile: its kernels may still read that
+        // descriptor, so it is parked until the device handle goes away
+        if (prev != d->list_cache.end()) d->parked_lists.push_back(prev->second);
         d->list_cache[key] = l;
     }
     return l;
@@ -410,6 +437,8 @@ void destroy_cuda_device(uintptr_t h) {
     std::vector<TensorList*> lists;
     for (auto& kv : d->list_cache) lists.push_back(kv.second);
     d->list_cache.clear();
+    for (TensorList* l : d->parked_lists) lists.push_back(l);
+    d->parked_lists.clear();
     for (TensorList* l : lists) free_list(l);
     lbfgs_release_device(d);
     if (d->partials) cudaFree(d->partials);
@@ -592,6 +621,7 @@ uintptr_t gm_arena_alloc(uintptr_t h, int64_t bytes) {
     uintptr_t p = a->base + (uintptr_t)a->used;
     a->used += need;
     g_bufs[p] = BufInfo{bytes, a->ordinal, false};
+    g_registry_gen.fetch_add(1, std::memory_order_release);
     return p;
 }
 
@@ -604,6 +634,7 @@ static void arena_forget_subbuffers(Arena* a) {     // g_mu held
         bool inside = !it->second.owned && it->first >= a->base && it->first < a->base + (uintptr_t)a->cap;
         if (inside) it = g_bufs.erase(it); else ++it;
     }
+    g_registry_gen.fetch_add(1, std::memory_order_release);
 }
 
 void gm_arena_reset(uintptr_t h) {

@@ -46,6 +46,7 @@ struct TensorList {
     std::vector<std::vector<uintptr_t>> ptrs;   // host copy [stream][tensor]
     uint64_t key = 0;                 // cache key (0 = not cached)
     std::vector<int> chunk_prefix;    // host copy: first chunk of each tensor, [num_tensors+1]
+    uint64_t validated_gen = 0;       // registry generation under which the buffers were last checked
     int win_begin = 0, win_count = -1; // launch window in chunks (count < 0: the whole list)
 };
 
@@ -59,6 +60,7 @@ struct Device {
     std::vector<cudaEvent_t> slice_events;
     std::mutex mu;
     std::unordered_map<uint64_t, TensorList*> list_cache;
+    std::vector<TensorList*> parked_lists;   // displaced from the cache while possibly still in use
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
