@@ -25,6 +25,22 @@ __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b);
 __device__ __forceinline__ float dvd(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ float root(float a) { return __fsqrt_rn(a); }
 
+// The IEEE division and square root take a long special-case path when an
+// operand is zero.  Parameters that a model never touches (zero gradient, zero
+// moments) would send every one of their elements down it: measured 1.6x the
+// kernel time on a list where half the elements are like that.  dvd0 and root0
+// are for the call sites where that can happen: the two shortcuts are exact
+// (+-0 / b = +-0 for every b > 0 including +inf, sqrt(+-0) = +-0) and everything
+// else goes to the intrinsic unchanged.
+__device__ __forceinline__ float dvd0(float a, float b) {
+    if (a == 0.0f && b > 0.0f) return a;
+    return __fdiv_rn(a, b);
+}
+__device__ __forceinline__ float root0(float a) {
+    if (a == 0.0f) return a;
+    return __fsqrt_rn(a);
+}
+
 // Streaming accesses: every byte is touched once per step, so lines are marked
 // evict-first on the way in and on the way out.
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
@@ -51,9 +67,9 @@ struct AdamRule {
         const float w = x[0], g = x[1];
         const float m_new = add(mul(x[2], p.beta1), mul(g, p.omb1));
         const float v_new = add(mul(x[3], p.beta2), mul(mul(g, g), p.omb2));
-        const float m_hat = dvd(m_new, p.bc1);
-        const float v_hat = dvd(v_new, p.bc2);
-        float upd = dvd(m_hat, add(root(v_hat), p.eps));
+        const float m_hat = dvd0(m_new, p.bc1);
+        const float v_hat = dvd0(v_new, p.bc2);
+        float upd = dvd0(m_hat, add(root0(v_hat), p.eps));
         if (p.use_wd) upd = add(upd, mul(w, p.wd));
         x[0] = sub(w, mul(upd, p.lr));
         x[2] = m_new;

@@ -20,11 +20,11 @@ struct NadamRule {
         const float w = x[0], g = x[1];
         const float m_new = add(mul(x[2], p.beta1), mul(g, p.omb1));
         const float v_new = add(mul(x[3], p.beta2), mul(mul(g, g), p.omb2));
-        const float v_hat = dvd(v_new, p.bc2);
-        const float m_hat = dvd(m_new, p.bc1);
-        const float g_hat = dvd(g, p.bc1);
+        const float v_hat = dvd0(v_new, p.bc2);
+        const float m_hat = dvd0(m_new, p.bc1);
+        const float g_hat = dvd0(g, p.bc1);
         const float m_bar = add(mul(m_hat, p.mu_next), mul(g_hat, p.om_mu));
-        float upd = dvd(m_bar, add(root(v_hat), p.eps));
+        float upd = dvd0(m_bar, add(root0(v_hat), p.eps));
         if (p.use_wd) upd = add(upd, mul(w, p.wd));
         x[0] = sub(w, mul(upd, p.lr));
         x[2] = m_new;
@@ -87,7 +87,7 @@ struct RmsPropRule {
         } else {
             denom = root(add(sq_new, p.eps));
         }
-        float upd = dvd(g, denom);
+        float upd = dvd0(g, denom);
         if (MOM) {
             const float b_new = add(mul(x[MOM_S < NS ? MOM_S : 0], p.momentum), upd);
             x[MOM_S < NS ? MOM_S : 0] = b_new;
@@ -109,7 +109,7 @@ struct AdaGradRule {
         float gf = x[1];
         if (p.use_wd) gf = add(x[1], mul(w, p.wd));
         const float acc = add(x[2], mul(gf, gf));
-        const float adj = dvd(p.lr, add(root(acc), p.eps));
+        const float adj = dvd(p.lr, add(root0(acc), p.eps));
         x[0] = sub(w, mul(adj, gf));
         x[2] = acc;
     }
