@@ -301,7 +301,8 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     if (chunk == 2 * tile) {
         const int64_t one_wave = (int64_t)d->sm_count * 5 * 1024;     // every chunk resident at once
         if (total <= one_wave) chunk = 1024;
-        else if (total <= 2 * one_wave) chunk = 2048;
+        else if (total <= (1LL << 27)) chunk = 2048;                  // measured: 1-3 % ahead of 4,096 from 2^24 to 2^27 elements,
+                                                                      // level at 2^28, 1.5 % behind at 2^30
     }
     if (d->chunk_elems > 0) chunk = (d->chunk_elems + tile - 1) / tile * tile;
 
