@@ -218,6 +218,29 @@ def case_small(dev, reps, small):
                 dev.free(p)
 
 
+def case_sizes(dev, reps, small):
+    """fp32 Adam on 16 equal tensors from 2^21 to 2^28 elements in all (2^24 at most with --small)."""
+    rng = np.random.default_rng(1)
+    block = 1 << 22
+    fill = {"w": rng.uniform(-0.05, 0.05, block).astype(np.float32), "g": (rng.standard_normal(block) * 0.01).astype(np.float32),
+            "m": (rng.standard_normal(block) * 0.001).astype(np.float32), "v": rng.uniform(1e-6, 1e-4, block).astype(np.float32)}
+    for lg in range(21, (24 if small else 28) + 1):
+        n, nt = 1 << lg, 16
+        per = n // nt
+        bufs = {k: dev.alloc(4 * n) for k in "wgmv"}
+        for k in "wgmv":
+            for lo in range(0, n, block):
+                gm.check(L.gm_buffer_upload(dev.h, bufs[k] + 4 * lo, fill[k].ctypes.data, 4 * min(block, n - lo)), "upload")
+        lst = dev.tensor_list([[bufs[k] + 4 * per * t for t in range(nt)] for k in "wgmv"], [per] * nt)
+        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
+        ms = timed(dev, lambda: gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy)), "adam"), reps)
+        emit(kernel="mta_apply_kernel<adam>", elements=n, us=ms * 1e3, gbs=28 * n / ms / 1e6,
+             chunks=L.gm_tensor_list_num_chunks(lst))
+        L.gm_tensor_list_destroy(lst)
+        for k in "wgmv":
+            dev.free(bufs[k])
+
+
 def _zeros(dev, k):
     p = dev.alloc(4 * k)
     gm.check(L.gm_buffer_zero(dev.h, p, 4 * k), "zero")
@@ -226,13 +249,13 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small", "sizes"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
-        cases = {"rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
+        cases = {"sizes": case_sizes, "rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
                  "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16),
                  "mixed_norm": lambda d, r, sm: case_mixed(d, r, sm, norm=True)}
         cases[args.case](dev, args.reps, args.small)
