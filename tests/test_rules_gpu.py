@@ -306,6 +306,18 @@ def test_error_codes(gm, dev):
     assert L.execute_rmsprop_step_cuda(dev.h, one, one, one, None, None, 1, sizes, 0.01, 0.99, 1e-8, 0.0, 0.0, True, 1) == -6
     assert L.allocate_cuda_buffer(dev.h, 0, 1) == 0
     assert L.allocate_cuda_buffer(0, 64, 1) == 0
+    # empty inputs: no tensors, a zero-byte tensor, an empty tensor list
+    assert L.execute_adam_step_cuda(dev.h, one, one, one, one, 0, sizes, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -10
+    assert L.execute_adam_step_cuda(dev.h, one, one, one, one, 1, gm.iarray([0]), 1e-3, 0.9, 0.999, 1e-8, 0.0, 1) == -9
+    assert L.execute_sgd_step_cuda(dev.h, one, one, None, 0, sizes, 0.01, 0.0, 0.0, 0, 1) == -10
+    with pytest.raises(gm.GmError):
+        dev.tensor_list([[], []], [])
+    # Adam's step count starts at 1 (bias correction 1 - beta^0 would divide by zero)
+    lst = dev.tensor_list([[p], [p], [p], [p]], [16])
+    hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=0)
+    assert L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy)) == -10
+    assert L.gm_step_async(dev.h, 17, lst, C.byref(hy)) == -10
+    L.gm_tensor_list_destroy(lst)
     L.deallocate_cuda_buffer(p)
 
 
