@@ -143,6 +143,7 @@ static Device* make_device(int ordinal) {
     if (const char* e2 = getenv("GOMETAL_GRID_WAVES")) d->grid_waves = atoi(e2);
     if (const char* e3 = getenv("GOMETAL_LBFGS_WAVES")) d->lbfgs_waves = atoi(e3);
     if (const char* e4 = getenv("GOMETAL_LBFGS_KEEP_DIR")) d->lbfgs_keep_dir = atoi(e4);
+    if (const char* e9 = getenv("GOMETAL_LBFGS_OVERLAP")) d->lbfgs_overlap = atoi(e9);
     if (const char* e5 = getenv("GOMETAL_MIXED_KEEP_G")) d->mixed_keep_g = atoi(e5);
     if (const char* e6 = getenv("GOMETAL_MIXED_OVERLAP")) d->mixed_overlap = atoi(e6);
     if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);

@@ -64,7 +64,12 @@ struct Device {
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
-    int mixed_overlap = 1;              // update grid launched with programmatic stream serialization (GOMETAL_MIXED_OVERLAP)
+    int mixed_overlap = 2;              // update grid launched with programmatic stream serialization: 2 = it may start when the
+                                        // check grid's CTAs reach their end (measured best), 1 = from their start, 0 = off
+                                        // (GOMETAL_MIXED_OVERLAP)
+    int lbfgs_overlap = 2;              // L-BFGS passes launched with programmatic stream serialization: 2 = the next pass may
+                                        // start when a pass's CTAs reach their end (measured best), 1 = from their start, 0 = off
+                                        // (GOMETAL_LBFGS_OVERLAP)
     int lbfgs_keep_dir = 1;             // L-BFGS direction lines marked evict_last in L2 (GOMETAL_LBFGS_KEEP_DIR=0 turns it off)
     int lbfgs_waves = 1;                // resident-CTA waves of the pipelined L-BFGS pass (GOMETAL_LBFGS_WAVES)
     int grid_waves = 0;                 // 0: one CTA per chunk; >0: waves of resident CTAs (GOMETAL_GRID_WAVES)

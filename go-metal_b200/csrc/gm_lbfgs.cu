@@ -69,6 +69,7 @@ struct LbfgsOp {
     int col_s_new, col_y_prev, col_s_prev, have_pair, corrected;
     int descent;              // kind 0: dir = +g instead of -g
     int keep_dir;             // kinds 0..2: the direction's lines get the evict_last L2 policy
+    int early_trigger;        // kinds 0..2: dependents may launch from the start of this grid (else from its end)
     float step;
 };
 
@@ -139,6 +140,8 @@ lbfgs_pass_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ par
     const int T = tb.T;
 
     // kinds 3 (final update) and 4 (plain dot); kinds 0..2 run in lbfgs_axpy_dot_kernel
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // no effect after an ordinary launch
     const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot) && (op.kind != 3 || op.have_pair);
 
     {
@@ -261,6 +264,23 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
     const int T = tb.T;
     const int kind = op.kind;
 
+    // Launched with programmatic stream serialization (every pass of a step but the
+    // first), this grid may become resident while the previous pass drains.  Only the
+    // pointer table, which no pass writes, is touched before the wait; the scalars,
+    // the direction and the chunk sums are the previous pass's to finish first.
+    if (op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
+    if (blockIdx.x < tb.num_chunks) {
+        const int t0 = find_tensor(tb.chunk_prefix, T, blockIdx.x);
+        const float* warm = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)COL_DIR * T + t0));
+        if (op.col_dot >= 0) warm = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)op.col_dot * T + t0));
+        // the history column this pass dots with is read-only during the step: start pulling
+        // this CTA's first chunk of it towards L2
+        const long long e0 = (long long)(blockIdx.x - __ldg(tb.chunk_prefix + t0)) * kDotChunk + tid * 16LL;
+        if (op.col_dot >= 0 && __ldg(tb.aligned + t0) != 0 && e0 + 16 <= __ldg(tb.numel + t0))
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(warm + e0));
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     const bool skip_axpy = kind != 0 && rho_skips(op.rho_axpy);
     const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot);
     const float coef = kind != 0 ? *op.coef : 0.0f;
@@ -352,6 +372,7 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
             cur = nxt;
         }
     }
+    if (!op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
     finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
 }
 
@@ -459,14 +480,24 @@ void lbfgs_release_device(Device* d) {
     g_lb.erase(it);
 }
 
-static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in) {
+static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in, const bool overlap = true) {
     LbfgsOp op = op_in;
+    // Every pass after the first of a step is launched so that it may start while its
+    // predecessor drains; each waits for that predecessor before touching its data.
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(kDotThreads); cfg.dynamicSmemBytes = 0; cfg.stream = d->stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (overlap && d->lbfgs_overlap) { cfg.attrs = &attr; cfg.numAttrs = 1; }
     if (op.kind <= 2) {
         op.keep_dir = d->lbfgs_keep_dir;
-        lbfgs_axpy_dot_kernel<<<axpy_grid(d, c->tb.num_chunks), kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+        op.early_trigger = d->lbfgs_overlap == 1;
+        cfg.gridDim = dim3(axpy_grid(d, c->tb.num_chunks));
+        cudaLaunchKernelEx(&cfg, lbfgs_axpy_dot_kernel, c->tb, op, d->partials, d->ticket);
     } else {
-        int grid = launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks);
-        lbfgs_pass_kernel<<<grid, kDotThreads, 0, d->stream>>>(c->tb, op, d->partials, d->ticket);
+        cfg.gridDim = dim3(launch_grid(d, (const void*)lbfgs_pass_kernel, kDotThreads, c->tb.num_chunks));
+        cudaLaunchKernelEx(&cfg, lbfgs_pass_kernel, c->tb, op, d->partials, d->ticket);
     }
     d->launches++;
 }
@@ -513,7 +544,7 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
         const int idx = slot(hc - 1);
         op.col_dot = col_s(idx); op.rho_dot = rho_of(idx); op.epilogue = 1; op.out = alpha + (hc - 1);
     }
-    launch_pass(d, c, op);
+    launch_pass(d, c, op, false);
 
     // first loop, newest to oldest: q -= alpha_j * y_j, fused with the next dot
     for (int j = hc - 1; j >= 0; --j) {

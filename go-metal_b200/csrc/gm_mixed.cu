@@ -103,11 +103,13 @@ template <bool NORM>
 __global__ void __launch_bounds__(kApplyThreads, NORM ? 6 : 8)
 mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
                    const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g) {
-    // Lets an update kernel launched with programmatic stream serialization become
-    // resident while this grid drains; it still waits for this grid to finish
-    // before it reads the published scalars.  Without that launch attribute: no effect.
-    asm volatile("griddepcontrol.launch_dependents;");
-    const unsigned long long pol = l2_policy(keep_g != 0);      // the update kernel reads the gradients again
+    // flags bit 0: the gradients get the evict_last L2 policy (the update kernel reads them
+    // again); bit 1: an update kernel launched with programmatic stream serialization may
+    // become resident from the start of this grid, else from the point where its CTAs have
+    // finished their chunks.  Either way it waits for this grid to complete before it reads
+    // the published scalars; without that launch attribute the trigger has no effect.
+    if (keep_g & 2) asm volatile("griddepcontrol.launch_dependents;");
+    const unsigned long long pol = l2_policy((keep_g & 1) != 0);
     constexpr int NT = kApplyThreads;
     constexpr int U = 4;                                     // 16-byte loads in flight per thread
     const int tid = threadIdx.x;
@@ -185,6 +187,7 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
         c = cn;
         cur = nxt;
     }
+    if (!(keep_g & 2)) asm volatile("griddepcontrol.launch_dependents;");
     // warp vote, then one atomic for the whole CTA (and only when needed)
     if (NORM) {
         __shared__ float warp_ss[NT / 32];
@@ -470,10 +473,10 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
     if (m->want_norm)
         mixed_check_kernel<true><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                          m->table_len, prep, d->mixed_keep_g);
+                                                                          m->table_len, prep, (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0));
     else
         mixed_check_kernel<false><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                           m->table_len, prep, d->mixed_keep_g);
+                                                                           m->table_len, prep, (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0));
     d->launches++;
     if (hook) {
         int rc = hook(ctx, m->d_flag);

@@ -143,7 +143,7 @@ def case_mixed(dev, reps, small, scale_up=1, norm=False):
 
 
 def case_lbfgs(dev, reps, small):
-    n = 10_000_000 // (4 if small else 1)
+    n = int(os.environ.get("GM_REPORT_LBFGS_ELEMENTS", 10_000_000 // (4 if small else 1)))
     m = 10
     z = lambda k: dev.to_device(np.zeros(k, np.float32)) if k < 4096 else _zeros(dev, k)
     x, g, old, d = (z(n) for _ in range(4))
@@ -173,7 +173,7 @@ def case_lbfgs(dev, reps, small):
         xs = dev.to_host(x, n)
     ms = float(np.median(walls))
     bpe = 44 + 32 * m
-    emit(kernel="lbfgs_pass_kernel x 22 launches (one synchronous step)", elements=n, history=m, ms=ms,
+    emit(kernel="lbfgs_axpy_dot_kernel x 21 + lbfgs_pass_kernel (one synchronous step)", elements=n, history=m, ms=ms,
          bytes_per_element=bpe, gbs=bpe * n / ms / 1e6, note="host wall clock around the synchronous drop-in entry")
 
 
