@@ -175,6 +175,14 @@ func (m *MixedAdam) State() (LossScale, error) {
 		int32(c.good_steps), int32(c.adam_t), int32(c.skipped), int32(c.last_overflow)}, nil
 }
 
+// SetState waits for the stream and overwrites the loss-scale state (checkpoint restore).
+func (m *MixedAdam) SetState(s LossScale) error {
+	c := C.gm_loss_scale_t{scale: C.float(s.Scale), growth: C.float(s.Growth), backoff: C.float(s.Backoff),
+		max_scale: C.float(s.MaxScale), interval: C.int32_t(s.Interval), good_steps: C.int32_t(s.GoodSteps),
+		adam_t: C.int32_t(s.AdamT), skipped: C.int32_t(s.Skipped), last_overflow: C.int32_t(s.LastOverflow)}
+	return stepError("mixed state", C.gm_mixed_set_state(handle(m.device), m.h, &c))
+}
+
 // EnableGradNorm makes every following step also compute the sum of squares of the
 // unscaled gradients inside the overflow-check pass; GradSumSq waits for the stream
 // and returns the last step's value (inf or NaN on an overflow step).
