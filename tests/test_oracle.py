@@ -98,11 +98,21 @@ def test_host_scalars(oracle):
 
 # ---------------------------------------------------------------- numpy cross-check
 
+@pytest.mark.filterwarnings("ignore::RuntimeWarning")
+@pytest.mark.parametrize("special", [False, True], ids=["dense", "zeros_and_denormals"])
 @pytest.mark.parametrize("wd", [0.0, 0.01])
-def test_rules_match_numpy_restatement(oracle, wd):
+def test_rules_match_numpy_restatement(oracle, wd, special):
+    """special: a third of the gradient entries are +0 or -0 (their state stays zero: the
+    untouched-parameter case the kernels shortcut), and weights and gradients carry
+    denormals, 1e-30 and 1e30, so the two restatements are compared where rounding and
+    the sign of zero matter most."""
     O = oracle
     n = 10_007
     w0 = O.fill_uniform(n, -0.5, 0.5, 3, 1)
+    if special:
+        w0[::11] = 0.0
+        w0[5::97] = np.float32(1e-42)
+        w0[7::101] = np.float32(-1e30)
     z = lambda: np.zeros(n, f32)
     state = {
         "adam": [w0.copy(), z(), z()], "nadam": [w0.copy(), z(), z()], "sgd": [w0.copy(), z()],
@@ -112,6 +122,12 @@ def test_rules_match_numpy_restatement(oracle, wd):
     ref = {k: [a.copy() for a in v] for k, v in state.items()}
     for t in range(1, 8):
         g = O.scale_subset(O.fill_normal(n, 0, 0.01, 3, 10 + t), 10, 100.0, 3, 40 + t)
+        if special:
+            g[::3] = 0.0
+            g[::6] = -0.0
+            g[1::91] = np.float32(1e-42)
+            g[2::89] = np.float32(1e-30)
+            g[4::83] = np.float32(1e18)
         bc1, bc2, _, _ = O.adam_scalars(0.9, 0.999, t)
         s = state
         O.adam_step(s["adam"][0], g, s["adam"][1], s["adam"][2], 1e-3, 0.9, 0.999, 1e-8, wd, t)

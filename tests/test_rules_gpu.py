@@ -484,7 +484,8 @@ def test_untouched_parameters_stay_exact(gm, dev, oracle, rule):
     """Parameters a model never touches: gradient exactly zero (+0 and -0) and all state
     zero for 60 % of the elements, scattered and in whole 4,096-element runs.  The
     kernels take exact shortcuts for 0/b and sqrt(0) there; results, including the sign
-    of every zero, must still equal the oracle's for three steps."""
+    of every zero, must still equal the oracle's for three steps.  A few denormal, tiny
+    and huge values ride along so the division's and square root's own slow paths run too."""
     O, L = oracle, gm.lib
     n = 3 * 4096 + 77
     rng = np.random.default_rng(42)
@@ -495,6 +496,7 @@ def test_untouched_parameters_stay_exact(gm, dev, oracle, rule):
     host = [np.zeros(n, np.float32) for _ in range(ns)]
     host[0][:] = O.fill_uniform(n, -0.5, 0.5, 5, 1)
     host[0][::97] = 0.0                                      # some parameters are zero themselves
+    host[0][7::101] = np.float32(-1e30)
     bufs = [dev.to_device(h) for h in host]
     lst = dev.tensor_list([[b] for b in bufs], [n])
     hy = {"sgd_plain": gm.Hyper(lr=0.05, beta1=0.0), "sgd_momentum": gm.Hyper(lr=0.05, beta1=0.9, nesterov=1),
@@ -510,6 +512,9 @@ def test_untouched_parameters_stay_exact(gm, dev, oracle, rule):
             g = O.fill_normal(n, 0.0, 0.01, 5, 10 + step)
             g[dead] = 0.0
             g[dead & (np.arange(n) % 3 == 0)] = -0.0
+            g[1::91] = np.float32(1e-42)                     # denormal, tiny and huge gradients: the
+            g[2::89] = np.float32(1e-30)                     # intrinsics' own special-case paths
+            g[4::83] = np.float32(1e18)
             host[1][:] = g
             dev.upload(bufs[1], host[1])
             hy.step = step
