@@ -291,6 +291,11 @@ def test_random_alignments_mixed(gm, dev, oracle, seed):
         for step in range(1, 5):
             scale = np.float32(st.scale)
             g16 = [O.f32_to_f16(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3) * scale) for n in sizes]
+            for a in g16:                                    # signed zeros, the smallest denormal half, the largest half
+                a[::7] = 0x0000
+                a[::13] = 0x8000
+                a[3::17] = 0x0001
+                a[5::19] = 0x7bff
             if step == bad_step:
                 t = int(rng.integers(nt))
                 g16[t][int(rng.integers(sizes[t]))] = 0x7e00
