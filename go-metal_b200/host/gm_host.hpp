@@ -125,6 +125,15 @@ struct OptimizerState {
     std::vector<OptimizerTensor> StateData;
 };
 
+namespace checkpoints {
+// The optimizer part of a checkpoint as JSON text, field names of
+// checkpoints/checkpoint.go:74-86.  Decode returns what a Go reader would pass to
+// LoadState: every parameter number as Float64, tensors as float32 with the saved bits.
+// Both return "" or an error text.
+std::string EncodeOptimizerState(const OptimizerState& state, std::string* out);
+std::string DecodeOptimizerState(const std::string& text, OptimizerState* out);
+}  // namespace checkpoints
+
 namespace optimizer {
 
 // optimizer/interface.go:56-84, optimizer/state_helpers.go:52-74, adam.go (calculateTensorSize)

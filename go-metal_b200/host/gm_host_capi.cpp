@@ -91,6 +91,19 @@ GMH_API void gmh_state_tensor_data(void* s, int i, float* out) {
     memcpy(out, d.data(), d.size() * sizeof(float));
 }
 
+// JSON text of a state (thread-local buffer, valid until the next call) and back.
+GMH_API const char* gmh_state_to_json(void* s) {
+    std::string e = checkpoints::EncodeOptimizerState(*static_cast<OptimizerState*>(s), &g_str);
+    if (!e.empty()) { g_err = e; return nullptr; }
+    return g_str.c_str();
+}
+GMH_API void* gmh_state_from_json(const char* text) {
+    auto* s = new OptimizerState();
+    std::string e = checkpoints::DecodeOptimizerState(text ? text : "", s);
+    if (!e.empty()) { g_err = e; delete s; return nullptr; }
+    return s;
+}
+
 // ---- optimizers ----
 // cfg layout per type (missing trailing values keep the reference defaults; pass ncfg = 0 for Default*Config()):
 //   SGD      lr, momentum, weight_decay, nesterov

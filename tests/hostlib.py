@@ -49,6 +49,7 @@ def load_host():
         "gmh_extract_float32_param": (f, [vp, s, f]), "gmh_extract_bool_param": (i, [vp, s, i]),
         "gmh_extract_uint64_param": (C.c_uint64, [vp, s, C.c_uint64]), "gmh_validate_state_type": (i, [s, vp]),
         "gmh_pow": (C.c_float, [C.c_float, C.c_float]),
+        "gmh_state_to_json": (s, [vp]), "gmh_state_from_json": (vp, [s]),
         "gmh_state_add_tensor": (None, [vp, s, s, vp, i]), "gmh_state_num_tensors": (i, [vp]),
         "gmh_state_tensor_name": (s, [vp, i]), "gmh_state_tensor_type": (s, [vp, i]), "gmh_state_tensor_numel": (i, [vp, i]),
         "gmh_state_tensor_shape0": (i, [vp, i]), "gmh_state_tensor_data": (None, [vp, i, vp]),

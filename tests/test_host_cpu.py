@@ -412,6 +412,61 @@ def test_mixed_adam_host_logic(env):
     assert fake.fake_calls(HL.MIXED_DESTROY) == 2
 
 
+def test_checkpoint_json_round_trip(env):
+    """checkpoints/checkpoint.go:74-86: field names of the payload; after a JSON round trip
+    every parameter number is a float64 (what Go's decoder hands to LoadState) and every
+    tensor value has the bits it was saved with -- denormals, -0 and extremes included."""
+    import json
+    H, fake, mm, dev = env
+    shapes = [[5], [2, 2]]
+    o = HL.make_optimizer(H, "Adam", [], shapes, mm, dev)
+    data = np.array([1.0, -0.0, 1e-42, 3.4028235e38, 0.1], np.float32)
+    src = H.gmh_state_new(b"Adam")
+    H.gmh_state_set_uint64(src, b"step_count", 12345678901)
+    H.gmh_state_set_bool(src, b"nesterov", 1)
+    H.gmh_state_set_float64(src, b"learning_rate", 0.001)
+    H.gmh_state_add_tensor(src, b"momentum_0", b"momentum", data.ctypes.data, 5)
+    H.gmh_state_add_tensor(src, b"variance_1", b"variance", (data[:4] * np.float32(0.5)).ctypes.data, 4)
+    text = H.gmh_state_to_json(src)
+    assert text, HL.err(H)
+    doc = json.loads(text.decode())
+    assert set(doc) == {"type", "parameters", "state_data"} and doc["type"] == "Adam"
+    assert doc["parameters"] == {"learning_rate": 0.001, "nesterov": True, "step_count": 12345678901}
+    assert [sorted(t) for t in doc["state_data"]] == [["data", "name", "shape", "state_type"]] * 2
+    assert doc["state_data"][0]["shape"] == [5] and doc["state_data"][0]["state_type"] == "momentum"
+    back = H.gmh_state_from_json(text)
+    assert back, HL.err(H)
+    val = C.c_double()
+    assert H.gmh_state_get_param(back, b"step_count", C.byref(val)) == 0 and val.value == 12345678901.0   # float64 now
+    assert H.gmh_state_get_param(back, b"nesterov", C.byref(val)) == 1 and val.value == 1.0
+    assert H.gmh_state_get_param(back, b"learning_rate", C.byref(val)) == 0 and val.value == 0.001
+    got = np.zeros(5, np.float32)
+    H.gmh_state_tensor_data(back, 0, got.ctypes.data)
+    assert np.array_equal(got.view(np.uint32), data.view(np.uint32))
+    assert H.gmh_state_tensor_name(back, 1) == b"variance_1" and H.gmh_state_tensor_shape0(back, 1) == 4
+    # the decoded payload loads: step_count arrives as float64, tensors land in the buffers
+    assert H.gmh_optimizer_load_state(o, back) == 0, HL.err(H)
+    assert H.gmh_optimizer_step_count(o) == 12345678901
+    # what a Go writer produces loads too: other key order, whitespace, an unknown field, null slices
+    go_text = (b'{ "state_data": [ {"state_type": "variance", "data": [0.25, 1e-3], "shape": [2], "name": "variance_0", "x": [1, {"y": null}]} ],'
+               b' "extra": "ignored", "parameters": {"beta1": 0.9, "step_count": 7, "note": "text"}, "type": "Adam" }')
+    g = H.gmh_state_from_json(go_text)
+    assert g, HL.err(H)
+    assert H.gmh_state_type(g) == b"Adam" and H.gmh_state_num_tensors(g) == 1 and H.gmh_state_tensor_numel(g, 0) == 2
+    assert H.gmh_state_get_param(g, b"note", C.byref(val)) == -1
+    empty = H.gmh_state_from_json(b'{"type":"SGD","parameters":{},"state_data":null}')
+    assert empty and H.gmh_state_num_tensors(empty) == 0
+    for bad in (b"", b"{", b'{"type":"Adam"} x', b'{"type":5}', b'{"state_data":[{"data":[1,}]}'):
+        assert not H.gmh_state_from_json(bad) and "invalid checkpoint JSON" in HL.err(H)
+    # json.Marshal refuses NaN and infinities; so does the encoder
+    nan = H.gmh_state_new(b"Adam")
+    H.gmh_state_add_tensor(nan, b"momentum_0", b"momentum", np.array([np.nan], np.float32).ctypes.data, 1)
+    assert not H.gmh_state_to_json(nan) and "unsupported value" in HL.err(H)
+    for st in (src, back, g, empty, nan):
+        H.gmh_state_destroy(st)
+    H.gmh_optimizer_destroy(o)
+
+
 # ---------------- schedulers ----------------
 
 def test_scheduler_tables(H):
