@@ -25,6 +25,21 @@ def test_plan_arithmetic():
     for r in range(8):
         covered += list(ZP.make_plan(256, 10, 8, r).owned)
     assert covered == list(range(256))
+    # sharded checkpoint bookkeeping
+    p1 = ZP.make_plan(4, 3, 2, 1)
+    shard = {"type": "Adam", "parameters": {"beta1": 0.9}, "state_data": [
+        {"name": "momentum_0", "shape": [3], "data": [1, 2, 3], "state_type": "momentum"},
+        {"name": "variance_1", "shape": [3], "data": [4, 5, 6], "state_type": "variance"}]}
+    g = ZP.shard_state_to_global(shard, p1)
+    assert [t["name"] for t in g["state_data"]] == ["momentum_2", "variance_3"]
+    assert ZP.global_state_to_shard(g, p1) == shard
+    assert ZP.global_state_to_shard(g, ZP.make_plan(4, 3, 2, 0))["state_data"] == []
+    with pytest.raises(ValueError, match="invalid buffer index"):
+        ZP.shard_state_to_global({"type": "Adam", "parameters": {}, "state_data": [{"name": "momentum", "data": []}]}, p1)
+    with pytest.raises(ValueError, match="more than one shard"):
+        ZP.merge_shard_states([g, g])
+    with pytest.raises(ValueError, match="disagree"):
+        ZP.merge_shard_states([g, dict(g, parameters={"beta1": 0.8}, state_data=[])])
     with pytest.raises(ValueError):
         ZP.make_plan(10, 4, 4, 0)               # uneven split
     with pytest.raises(ValueError):
@@ -71,6 +86,19 @@ for step in range(1, STEPS + 1):
         O.adam_step(ws, grads[t], ms, vs, 1e-3, 0.9, 0.999, 1e-8, 0.0, step)
         full[a:a + E], fm[a:a + E], fv[a:a + E] = ws, ms, vs
     assert np.array_equal(w.view(np.uint32), full.view(np.uint32)), f"rank {rank} step {step}: arena differs"
+# sharded checkpoint: every rank's payload (local tensor numbers) -> one global payload on
+# every rank -> cut back per rank; it must equal the single-process payload and round-trip
+def payload(mm, vv, count):
+    data = [{"name": f"momentum_{i}", "shape": [E], "data": mm[i * E:(i + 1) * E].tolist(), "state_type": "momentum"} for i in range(count)]
+    data += [{"name": f"variance_{i}", "shape": [E], "data": vv[i * E:(i + 1) * E].tolist(), "state_type": "variance"} for i in range(count)]
+    return {"type": "Adam", "parameters": {"learning_rate": 1e-3, "beta1": 0.9, "step_count": STEPS}, "state_data": data}
+mine = ZP.shard_state_to_global(payload(m, v, plan.tensors_per_rank), plan)
+gathered = [None] * world
+dist.all_gather_object(gathered, mine)
+merged = ZP.merge_shard_states(gathered[::-1])                 # order of arrival must not matter
+assert merged == payload(fm, fv, T), f"rank {rank}: merged checkpoint differs from the single-process one"
+back = ZP.global_state_to_shard(merged, plan)
+assert back == payload(m, v, plan.tensors_per_rank), f"rank {rank}: shard cut from the checkpoint differs"
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
