@@ -146,6 +146,7 @@ static Device* make_device(int ordinal) {
     if (const char* e9 = getenv("GOMETAL_LBFGS_OVERLAP")) d->lbfgs_overlap = atoi(e9);
     if (const char* e5 = getenv("GOMETAL_MIXED_KEEP_G")) d->mixed_keep_g = atoi(e5);
     if (const char* e6 = getenv("GOMETAL_MIXED_OVERLAP")) d->mixed_overlap = atoi(e6);
+    if (const char* e8 = getenv("GOMETAL_MIXED_VARIANT")) d->mixed_variant = atoi(e8);
     if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);
     if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);
     // A blocking stream on purpose: the synchronous copies of the drop-in ABI

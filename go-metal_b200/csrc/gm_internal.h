@@ -64,6 +64,7 @@ struct Device {
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
+    int mixed_variant = 0;              // 1: the 4-elements-per-thread update kernel instead of the 8-element one (GOMETAL_MIXED_VARIANT)
     int mixed_overlap = 2;              // update grid launched with programmatic stream serialization: 2 = it may start when the
                                         // check grid's CTAs reach their end (measured best), 1 = from their start, 0 = off
                                         // (GOMETAL_MIXED_OVERLAP)
