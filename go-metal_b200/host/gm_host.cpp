@@ -60,6 +60,9 @@ std::string Backend::load(const std::string& path) {
     resolve(h, "gm_tensor_list_create", &b.list_create, &optional);
     resolve(h, "gm_tensor_list_destroy", &b.list_destroy, &optional);
     resolve(h, "gm_device_synchronize", &b.device_synchronize, &optional);
+    resolve(h, "gm_arena_create", &b.arena_create, &optional);
+    resolve(h, "gm_arena_alloc", &b.arena_alloc, &optional);
+    resolve(h, "gm_arena_destroy", &b.arena_destroy, &optional);
     *this = b;
     return "";
 }
@@ -86,8 +89,21 @@ int calculateMaxPoolSize(int bufferSize) {
 
 MemoryManager::~MemoryManager() {
     Backend& b = backend();
+    if (arena_) { if (b.arena_destroy) b.arena_destroy(arena_); return; }      // the buffers go with the arena
     if (!b.deallocate) return;
     for (auto& kv : pools_) for (uintptr_t p : kv.second.free) b.deallocate(p);
+}
+
+std::string MemoryManager::UseArena(int64_t bytes) {
+    Backend& b = backend();
+    std::lock_guard<std::mutex> lk(mu_);
+    if (arena_) return "this memory manager already has an arena";
+    if (!sizes_.empty() || !pools_.empty()) return "the arena must be chosen before the first allocation";
+    if (bytes <= 0) return "arena size must be positive";
+    if (!b.has_arena()) return "the loaded backend has no arena entries";
+    arena_ = b.arena_create(device_, bytes);
+    if (!arena_) return std::string("failed to create the arena: ") + (b.last_error ? b.last_error() : "");
+    return "";
 }
 
 uintptr_t MemoryManager::AllocateBuffer(int size) {
@@ -103,9 +119,14 @@ uintptr_t MemoryManager::AllocateBuffer(int size) {
         buf = pool.free.back();
         pool.free.pop_back();
     } else {
-        if (pool.allocated >= pool.maxSize) return 0;          // "buffer pool at capacity"
-        buf = b.allocate(device_, tier, 1 /* GPU */);
-        if (!buf) return 0;
+        if (arena_) {
+            buf = b.arena_alloc(arena_, tier);                 // 0 when the arena is full
+            if (!buf) return 0;
+        } else {
+            if (pool.allocated >= pool.maxSize) return 0;      // "buffer pool at capacity"
+            buf = b.allocate(device_, tier, 1 /* GPU */);
+            if (!buf) return 0;
+        }
         pool.allocated++;
     }
     sizes_[buf] = tier;
@@ -119,11 +140,11 @@ void MemoryManager::ReleaseBuffer(uintptr_t buffer) {
     auto it = sizes_.find(buffer);
     // manager.go:305-313 falls back to a 4 MB guess for an untracked buffer and
     // prints a warning; an untracked pointer is simply handed back to the device here.
-    if (it == sizes_.end()) { if (b.deallocate) b.deallocate(buffer); return; }
+    if (it == sizes_.end()) { if (!arena_ && b.deallocate) b.deallocate(buffer); return; }
     const int tier = it->second;
     sizes_.erase(it);
     Pool& pool = pools_[tier];
-    if ((int)pool.free.size() < pool.maxSize) {
+    if (arena_ || (int)pool.free.size() < pool.maxSize) {     // arena memory can only be reused, not returned
         pool.free.push_back(buffer);
     } else {
         if (b.deallocate) b.deallocate(buffer);

@@ -56,6 +56,11 @@ struct Backend {
     uintptr_t (*list_create)(uintptr_t, int, int, const uintptr_t* const*, const int64_t*, const int*) = nullptr;
     void (*list_destroy)(uintptr_t) = nullptr;
     int (*device_synchronize)(uintptr_t) = nullptr;
+    // Flat arenas (optional as well)
+    uintptr_t (*arena_create)(uintptr_t, int64_t) = nullptr;
+    uintptr_t (*arena_alloc)(uintptr_t, int64_t) = nullptr;
+    void (*arena_destroy)(uintptr_t) = nullptr;
+    bool has_arena() const { return arena_create && arena_alloc && arena_destroy; }
     bool has_mixed() const {
         return mixed_create && mixed_destroy && mixed_step && mixed_get_state && mixed_set_state && list_create &&
                list_destroy && device_synchronize;
@@ -90,6 +95,13 @@ public:
     std::map<int, PoolStats> Stats();
     uintptr_t device() const { return device_; }
     int trackedSize(uintptr_t buffer);    // -1 when unknown
+    // Switches this manager to one flat, 256-byte-aligned arena of `bytes`: every later
+    // buffer is carved from it (still rounded to its tier, still reused through the tier's
+    // free list) and the per-tier caps of manager.go:210-224 no longer apply, only the
+    // arena's size does.  The reference's caps cannot hold a large model (20 buffers of
+    // 16 MB); this is the pool the large configurations use.  Call it before the first
+    // allocation; returns "" or an error text.
+    std::string UseArena(int64_t bytes);
 
 private:
     struct Pool { int size = 0, maxSize = 0, allocated = 0; std::vector<uintptr_t> free; };
@@ -97,6 +109,7 @@ private:
     uintptr_t device_;
     std::map<int, Pool> pools_;
     std::map<uintptr_t, int> sizes_;
+    uintptr_t arena_ = 0;
 };
 
 }  // namespace memory

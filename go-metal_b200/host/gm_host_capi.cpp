@@ -32,6 +32,7 @@ GMH_API void gmh_device_destroy(uintptr_t d) { if (backend().destroy_device) bac
 
 // ---- memory manager ----
 GMH_API void* gmh_mm_create(uintptr_t device) { return new memory::MemoryManager(device); }
+GMH_API int gmh_mm_use_arena(void* mm, int64_t bytes) { return fail(static_cast<memory::MemoryManager*>(mm)->UseArena(bytes)); }
 GMH_API void gmh_mm_destroy(void* mm) { delete static_cast<memory::MemoryManager*>(mm); }
 GMH_API uintptr_t gmh_mm_allocate(void* mm, int size) { return static_cast<memory::MemoryManager*>(mm)->AllocateBuffer(size); }
 GMH_API void gmh_mm_release(void* mm, uintptr_t p) { static_cast<memory::MemoryManager*>(mm)->ReleaseBuffer(p); }

@@ -96,3 +96,29 @@ uintptr_t gm_tensor_list_create(uintptr_t dev, int ns, int nt, const uintptr_t* 
 }
 void gm_tensor_list_destroy(uintptr_t l) { if (l) { g_calls[LIST_DESTROY]++; free((void*)l); } }
 int gm_device_synchronize(uintptr_t dev) { (void)dev; return 0; }
+
+/* ---- arenas: one malloc'd block, 256-byte granules ---- */
+typedef struct { char* base; int64_t cap, used; } fake_arena_t;
+static int g_arenas_live;
+int fake_arenas_live(void) { return g_arenas_live; }
+uintptr_t gm_arena_create(uintptr_t dev, int64_t bytes) {
+    if (!dev || bytes <= 0) return 0;
+    fake_arena_t* a = (fake_arena_t*)calloc(1, sizeof *a);
+    a->base = (char*)aligned_alloc(256, (size_t)((bytes + 255) / 256 * 256));
+    a->cap = bytes;
+    g_arenas_live++;
+    return (uintptr_t)a;
+}
+uintptr_t gm_arena_alloc(uintptr_t h, int64_t bytes) {
+    fake_arena_t* a = (fake_arena_t*)h;
+    int64_t need = (bytes + 255) / 256 * 256;
+    if (!a || bytes <= 0 || a->used + need > a->cap) return 0;
+    uintptr_t p = (uintptr_t)(a->base + a->used);
+    a->used += need;
+    return p;
+}
+void gm_arena_destroy(uintptr_t h) {
+    fake_arena_t* a = (fake_arena_t*)h;
+    if (!a) return;
+    free(a->base); free(a); g_arenas_live--;
+}

@@ -39,7 +39,7 @@ def load_host():
     ip = C.POINTER(C.c_int)
     sig = {
         "gmh_last_error": (s, []), "gmh_init": (i, [s]), "gmh_device_create": (u, []), "gmh_device_destroy": (None, [u]),
-        "gmh_mm_create": (vp, [u]), "gmh_mm_destroy": (None, [vp]), "gmh_mm_allocate": (u, [vp, i]),
+        "gmh_mm_create": (vp, [u]), "gmh_mm_destroy": (None, [vp]), "gmh_mm_use_arena": (i, [vp, C.c_int64]), "gmh_mm_allocate": (u, [vp, i]),
         "gmh_mm_release": (None, [vp, u]), "gmh_mm_tracked_size": (i, [vp, u]), "gmh_find_pool_size": (i, [i]),
         "gmh_calculate_max_pool_size": (i, [i]), "gmh_mm_stats": (i, [vp, i, ip, ip, ip]),
         "gmh_extract_buffer_index": (i, [s]), "gmh_calculate_tensor_size": (i, [ip, i]),

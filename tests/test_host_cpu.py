@@ -109,6 +109,40 @@ def test_memory_manager_reuses_and_caps(env):
     H.gmh_mm_release(mm, 0)                                          # nil is ignored
 
 
+def test_memory_manager_on_a_flat_arena(H, fake):
+    """The north-star pool: one flat 256-byte-aligned arena instead of per-tier device
+    allocations.  The reference's tier caps (100 buffers of 1 KB) no longer bind, only the
+    arena's size; released buffers are reused; nothing is allocated from or returned to the
+    device one by one; the arena goes when the manager goes."""
+    fake.fake_reset()
+    dev = H.gmh_device_create()
+    plain = H.gmh_mm_create(dev)
+    held = [H.gmh_mm_allocate(plain, 1000) for _ in range(101)]
+    assert all(held[:100]) and held[100] == 0                         # manager.go:210-224: the 1 KB tier holds 100
+    for p in held[:100]:
+        H.gmh_mm_release(plain, p)
+    assert H.gmh_mm_use_arena(plain, 1 << 20) != 0 and "before the first allocation" in HL.err(H)
+    H.gmh_mm_destroy(plain)
+
+    fake.fake_reset()
+    mm = H.gmh_mm_create(dev)
+    assert H.gmh_mm_use_arena(mm, 0) != 0
+    assert H.gmh_mm_use_arena(mm, 160 * 1024) == 0, HL.err(H)
+    assert H.gmh_mm_use_arena(mm, 160 * 1024) != 0 and "already has an arena" in HL.err(H)
+    assert fake.fake_arenas_live() == 1
+    bufs = [H.gmh_mm_allocate(mm, 1000) for _ in range(150)]
+    assert all(bufs) and fake.fake_allocs() == 0                      # carved from the arena, no device allocation
+    assert all(p % 256 == 0 for p in bufs) and bufs[1] - bufs[0] == 1024 and H.gmh_mm_tracked_size(mm, bufs[5]) == 1024
+    more = [H.gmh_mm_allocate(mm, 1024) for _ in range(11)]
+    assert all(more[:10]) and more[10] == 0                           # 160 KB hold exactly 160 buffers of 1 KB
+    H.gmh_mm_release(mm, bufs[7])
+    assert H.gmh_mm_allocate(mm, 900) == bufs[7] and fake.fake_frees() == 0     # reused from the tier's free list
+    o = HL.make_optimizer(H, "Adam", [], [[8]], mm, dev)
+    assert not o and "failed to allocate" in HL.err(H)                # arena full: the constructor fails cleanly
+    H.gmh_mm_destroy(mm)
+    assert fake.fake_arenas_live() == 0 and fake.fake_frees() == 0
+
+
 # ---------------- constructors ----------------
 
 SHAPES = [[784, 128], [128], [128, 10], [10]]

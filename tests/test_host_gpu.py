@@ -284,3 +284,46 @@ def test_mixed_adam_through_host_mirror_with_checkpoint_resume(gm, H, oracle):
         L.deallocate_cuda_buffer(p)
     H.gmh_mm_destroy(mm)
     H.gmh_device_destroy(dev)
+
+
+def test_adam_with_state_in_a_flat_arena(gm, H, oracle):
+    """The memory manager on one flat arena of the real library: the optimizer's moment
+    buffers are carved from it (256-byte aligned, back to back), more of them than the
+    reference's tier cap allows, and the steps still equal the oracle's."""
+    global gm_dev
+    O = oracle
+    dev = H.gmh_device_create()
+    gm_dev = dev
+    mm = H.gmh_mm_create(dev)
+    assert H.gmh_mm_use_arena(mm, 8 << 20) == 0, HL.err(H)
+    nt = 130                                                   # 260 state buffers of the 1 KB tier: over its cap of 100
+    shapes = [[200]] * nt
+    sizes = [200] * nt
+    w_cpu = [O.fill_uniform(200, -0.3, 0.3, 9, t) for t in range(nt)]
+    m_cpu = [np.zeros(200, np.float32) for _ in range(nt)]
+    v_cpu = [np.zeros(200, np.float32) for _ in range(nt)]
+    wp = put(gm, w_cpu)
+    gp = put(gm, [np.zeros(200, np.float32) for _ in range(nt)])
+    opt = HL.make_optimizer(H, "Adam", [], shapes, mm, dev)
+    assert opt, HL.err(H)
+    assert H.gmh_optimizer_set_weight_buffers(opt, HL.uarr(wp), nt) == 0
+    for k in range(1, 4):
+        grads = [O.fill_normal(200, 0.0, 0.01, 9, 1000 * k + t) for t in range(nt)]
+        for p, g in zip(gp, grads):
+            gm.check(gm.lib.copy_float32_array_to_cuda_buffer(p, g.ctypes.data, g.size), "upload")
+        assert H.gmh_optimizer_step(opt, HL.uarr(gp), nt, 0.0) == 0, HL.err(H)
+        for t in range(nt):
+            O.adam_step(w_cpu[t], grads[t], m_cpu[t], v_cpu[t], 1e-3, 0.9, 0.999, 1e-8, 0.0, k)
+    for a, b in zip(get(gm, wp, sizes), w_cpu):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    st = H.gmh_optimizer_get_state(opt)
+    assert st and H.gmh_state_num_tensors(st) == 2 * nt
+    buf = np.empty(200, np.float32)
+    H.gmh_state_tensor_data(st, nt + 3, buf.ctypes.data)            # variance_3
+    assert np.array_equal(buf.view(np.uint32), v_cpu[3].view(np.uint32))
+    H.gmh_state_destroy(st)
+    H.gmh_optimizer_destroy(opt)
+    for p in wp + gp:
+        gm.lib.deallocate_cuda_buffer(p)
+    H.gmh_mm_destroy(mm)
+    H.gmh_device_destroy(dev)
