@@ -126,6 +126,8 @@ def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | 
     g = O.fill_normal(n, 0.0, 0.01, SEED, 2)
     m = np.zeros(n, dtype=np.float32)
     v = np.zeros(n, dtype=np.float32)
+    m.fill(0.0)                       # np.zeros maps pages lazily: touch them so that no timed step pays the page faults
+    v.fill(0.0)
     step = 0
     for _ in range(warmup):
         step += 1
