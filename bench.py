@@ -248,7 +248,16 @@ def run_gpu(args):
         exchange = args.exchange
         if exchange in ("push", "dma"):
             mine = (C.c_ubyte * 64)()
-            gm.check(L.gm_zero1_ipc_handle(zero1, w_arena.data_ptr(), mine), "ipc handle")
+            rc = L.gm_zero1_ipc_handle(zero1, w_arena.data_ptr(), mine)
+            # torch may have carved the arena out of a larger segment, which cannot be exported to
+            # the peers; every rank then takes the NCCL all-gather instead
+            ok = torch.tensor([1 if rc == 0 else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                exchange = "nccl"
+                if rank == 0:
+                    print(f"peer mapping unavailable ({gm.last_error()}); using the NCCL all-gather", file=sys.stderr)
+        if exchange in ("push", "dma"):
             mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
             all_t = [torch.empty_like(mine_t) for _ in range(world)]
             dist.all_gather(all_t, mine_t)

@@ -263,12 +263,35 @@ int gm_zero1_adam_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t
     return gm_zero1_allgather_async(h, arena_base, count, 4);
 }
 
+// cudaIpcGetMemHandle describes a whole device allocation, and the peer that opens it
+// gets the allocation's first byte back, whatever address inside it was exported.  The
+// peers store to "their mapping + the same offset", so the arena has to start where its
+// allocation starts; the driver's address-range query (loaded at run time, like NCCL)
+// tells.  Returns 1 when arena_base is the base, 0 when it is not, -1 when unknown.
+static int is_allocation_base(uintptr_t arena_base) {
+    typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+    static range_fn fn = []() -> range_fn {
+        void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+        return h ? (range_fn)dlsym(h, "cuMemGetAddressRange_v2") : nullptr;
+    }();
+    if (!fn) return -1;
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (fn(&base, &size, (unsigned long long)arena_base) != 0) return -1;
+    return base == (unsigned long long)arena_base ? 1 : 0;
+}
+
 // ---- peer mapping for the push path ----
 int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 64 bytes */) {
     Zero1* z = as_zero1(h);
     if (!z) return GM_ERR_BAD_ARG;
     if (!arena_base || !out_handle) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
     DeviceGuard g(z->dev);
+    if (is_allocation_base(arena_base) == 0) {
+        set_error("the parameter arena must start at the first byte of its device allocation: "
+                  "an IPC handle maps the whole allocation and the peers would store at the wrong offset");
+        return GM_ERR_BAD_ARG;
+    }
     cudaIpcMemHandle_t mh;
     GM_CUDA_CHECK(cudaIpcGetMemHandle(&mh, (void*)arena_base));
     static_assert(sizeof(mh) == 64, "cudaIpcMemHandle_t is 64 bytes");

@@ -299,7 +299,9 @@ int gm_zero1_world(uintptr_t zero1);
  * pointers (plain stores over NVLink).  Setup: each rank exports its arena
  * with gm_zero1_ipc_handle (64 bytes), the caller exchanges the handles by
  * any host channel, and gm_zero1_open_peers maps them (rank order).  The
- * step ends with a one-word all-reduce that acts as the cross-rank barrier. */
+ * step ends with a one-word all-reduce that acts as the cross-rank barrier.
+ * arena_base must be the first byte of its device allocation (an IPC handle
+ * maps whole allocations); anything else is refused with -10. */
 #define GM_IPC_HANDLE_BYTES 64
 int gm_zero1_ipc_handle(uintptr_t zero1, uintptr_t arena_base, void* out_handle);
 int gm_zero1_open_peers(uintptr_t zero1, const void* handles);

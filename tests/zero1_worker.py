@@ -56,6 +56,9 @@ def main():
         lst = dev.tensor_list([w_ptrs, loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
         if exchange in ("push", "dma"):
             mine = (C.c_ubyte * 64)()
+            # an address inside the allocation cannot be exported: the peers would map the
+            # allocation's first byte and store at the wrong offset
+            assert L.gm_zero1_ipc_handle(z, arena + 256, mine) == -10, "interior pointer must be refused"
             gm.check(L.gm_zero1_ipc_handle(z, arena, mine), "ipc handle")
             mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
             all_t = [torch.empty_like(mine_t) for _ in range(world)]
