@@ -85,6 +85,7 @@ struct Zero1 {
     uintptr_t peer_base[kMaxPeers] = {0};
     bool peer_opened[kMaxPeers] = {false};
     uintptr_t local_base = 0;
+    size_t local_bytes = 0;            // size of the exported allocation (0 = unknown)
     int* barrier_word = nullptr;       // device int used by the closing all-reduce
     // copy-engine path: one stream per peer, one event per slice, one "done" event per peer
     cudaStream_t copy_stream[kMaxPeers] = {nullptr};
@@ -267,8 +268,9 @@ int gm_zero1_adam_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t
 // gets the allocation's first byte back, whatever address inside it was exported.  The
 // peers store to "their mapping + the same offset", so the arena has to start where its
 // allocation starts; the driver's address-range query (loaded at run time, like NCCL)
-// tells.  Returns 1 when arena_base is the base, 0 when it is not, -1 when unknown.
-static int is_allocation_base(uintptr_t arena_base) {
+// tells.  Returns 1 when arena_base is the base (and the allocation's size), 0 when it
+// is not, -1 when unknown.
+static int is_allocation_base(uintptr_t arena_base, size_t* alloc_bytes) {
     typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
     static range_fn fn = []() -> range_fn {
         void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
@@ -278,6 +280,7 @@ static int is_allocation_base(uintptr_t arena_base) {
     unsigned long long base = 0;
     size_t size = 0;
     if (fn(&base, &size, (unsigned long long)arena_base) != 0) return -1;
+    *alloc_bytes = size;
     return base == (unsigned long long)arena_base ? 1 : 0;
 }
 
@@ -287,7 +290,9 @@ int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 6
     if (!z) return GM_ERR_BAD_ARG;
     if (!arena_base || !out_handle) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
     DeviceGuard g(z->dev);
-    if (is_allocation_base(arena_base) == 0) {
+    size_t alloc_bytes = 0;
+    const int at_base = is_allocation_base(arena_base, &alloc_bytes);
+    if (at_base == 0) {
         set_error("the parameter arena must start at the first byte of its device allocation: "
                   "an IPC handle maps the whole allocation and the peers would store at the wrong offset");
         return GM_ERR_BAD_ARG;
@@ -297,6 +302,8 @@ int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 6
     static_assert(sizeof(mh) == 64, "cudaIpcMemHandle_t is 64 bytes");
     memcpy(out_handle, &mh, sizeof(mh));
     z->local_base = arena_base;
+    z->local_bytes = at_base == 1 ? alloc_bytes : 0;          // 0: size unknown, no range check
+    if (z->local_bytes == 0 && registered_size(arena_base) > 0) z->local_bytes = (size_t)registered_size(arena_base);
     return GM_OK;
 }
 
@@ -324,6 +331,22 @@ int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, ra
     return GM_OK;
 }
 
+// Every parameter tensor of the shard must lie inside the exported arena: its address
+// minus the arena base is added to each peer's mapping, and a tensor from elsewhere would
+// turn into a store to an address no peer mapped.
+static int check_inside_arena(const Zero1* z, const TensorList* l) {
+    if (!z->local_base) { set_error("call gm_zero1_ipc_handle and gm_zero1_open_peers first"); return GM_ERR_BAD_ARG; }
+    for (size_t t = 0; t < l->numel.size(); ++t) {
+        const uintptr_t p = l->ptrs[0][t];
+        const uintptr_t end = p + (uintptr_t)l->numel[t] * 4;
+        if (p < z->local_base || (z->local_bytes && end > z->local_base + z->local_bytes)) {
+            set_error("parameter tensor %zu lies outside the arena exported to the peers", t);
+            return GM_ERR_BAD_ARG;
+        }
+    }
+    return GM_OK;
+}
+
 int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper) {
     Zero1* z = as_zero1(h);
     if (!z) return GM_ERR_BAD_ARG;
@@ -331,6 +354,10 @@ int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hy
     if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
     if (l->dl.num_streams != 4) { set_error("Adam shard list needs w,g,m,v"); return GM_ERR_BAD_ARG; }
     if (hyper->step < 1) { set_error("Adam step count %d must be >= 1", hyper->step); return GM_ERR_BAD_ARG; }
+    {
+        const int rc = check_inside_arena(z, l);
+        if (rc != GM_OK) return rc;
+    }
     Device* d = z->dev;
     PeerDst peers{};
     peers.count = 0;
@@ -394,6 +421,10 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
     }
     for (int r = 0; r < z->world; ++r) {
         if (r != z->rank && !z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
+    }
+    {
+        const int rc = check_inside_arena(z, l);
+        if (rc != GM_OK) return rc;
     }
     DeviceGuard g(d);
     for (int r = 0; r < z->world; ++r) {

@@ -66,6 +66,14 @@ def main():
             blob = bytes(b for tt in all_t for b in tt.cpu().tolist())
             gm.check(L.gm_zero1_open_peers(z, (C.c_ubyte * len(blob))(*blob)), "open peers")
             dist.barrier()
+            # a shard list whose parameters are not in the exported arena must be refused, not run
+            stray = dev.alloc(4 * plan.shard_elems)
+            bad = dev.tensor_list([loc(stray), loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
+            hy0 = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=1)
+            assert L.gm_zero1_adam_push_step_async(z, bad, C.byref(hy0)) == -10, "tensor outside the arena must be refused"
+            assert L.gm_zero1_adam_dma_step_async(z, bad, C.byref(hy0), 2) == -10
+            L.gm_tensor_list_destroy(bad)
+            dev.free(stray)
         for step in range(1, STEPS + 1):
             grads = [O.fill_normal(E, 0.0, 0.01, 91, 1000 * step + k) for k in range(T)]
             shard_g = np.concatenate([grads[k] for k in plan.owned])
