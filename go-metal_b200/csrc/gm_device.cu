@@ -82,6 +82,17 @@ int64_t registered_size(uintptr_t p) {
     return it == g_bufs.end() ? -1 : it->second.bytes;
 }
 
+uint64_t registry_generation() { return g_registry_gen.load(std::memory_order_acquire); }
+
+bool buffer_holds(uintptr_t p, int64_t need, const char* what) {
+    const int64_t have = registered_size(p);
+    if (have >= 0 && have < need) {
+        set_error("%s: buffer holds %lld bytes, the call needs %lld", what, (long long)have, (long long)need);
+        return false;
+    }
+    return true;
+}
+
 int registered_ordinal(uintptr_t p) {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_bufs.find(p);
@@ -676,6 +687,10 @@ int convert_tensor_type_cuda(uintptr_t src, uintptr_t dst, int* shape, int nd, i
         n *= shape[i];
     }
     const int F32 = 0, F16 = 2;
+    if ((src_t == F32 || src_t == F16) && (dst_t == F32 || dst_t == F16)) {
+        if (!buffer_holds(src, n * (src_t == F32 ? 4 : 2), "conversion source")) return GM_ERR_BAD_SIZE;
+        if (!buffer_holds(dst, n * (dst_t == F32 ? 4 : 2), "conversion destination")) return GM_ERR_BAD_SIZE;
+    }
     DeviceGuard g(d);
     int blocks = (int)((n + 255) / 256);
     int cap = d->sm_count * 16;

@@ -130,6 +130,12 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
 
 // ---- buffer registry (gm_device.cu) ----
 int64_t registered_size(uintptr_t p);   // -1 if unknown
+// false (with the error text set) when p is a buffer this library allocated and it holds
+// fewer than `need` bytes; buffers from elsewhere cannot be checked and pass
+bool buffer_holds(uintptr_t p, int64_t need, const char* what);
+// changes whenever the library allocates or releases a buffer: a cached validation made under the
+// current value is still good
+uint64_t registry_generation();
 int registered_ordinal(uintptr_t p);    // -1 if unknown
 
 }  // namespace gm

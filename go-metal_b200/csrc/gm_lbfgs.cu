@@ -382,6 +382,7 @@ struct LbfgsCtx {
     LbfgsTable tb{};
     std::vector<uintptr_t> key;      // every pointer + size, for exact comparison
     int history = 0;
+    uint64_t validated_gen = 0;      // registry generation under which the buffer sizes were last checked
 };
 
 static std::mutex g_lb_mu;
@@ -528,6 +529,19 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
     LbfgsCtx* c = nullptr;
     int rc = get_ctx(d, T, m, cols4, s_flat, y_flat, numel.data(), &c);
     if (rc != GM_OK) return rc;
+    // Buffers this library allocated are checked against their sizes, once per table and again
+    // only after something was allocated or released.
+    const uint64_t gen = registry_generation();
+    if (c->validated_gen != gen) {
+        for (int t = 0; t < T; ++t)
+            for (uintptr_t p : {w[t], g[t], old_g[t], dir[t]})
+                if (!buffer_holds(p, buffer_sizes[t], "L-BFGS vector")) return GM_ERR_BAD_SIZE;
+        for (int k = 0; k < m * T; ++k)
+            if (!buffer_holds(s_flat[k], buffer_sizes[k % T], "L-BFGS history") ||
+                !buffer_holds(y_flat[k], buffer_sizes[k % T], "L-BFGS history")) return GM_ERR_BAD_SIZE;
+        if (!buffer_holds(alpha_buf, 4LL * m, "L-BFGS alpha")) return GM_ERR_BAD_SIZE;
+        c->validated_gen = gen;
+    }
 
     DeviceGuard guard(d);
     float* alpha = (float*)alpha_buf;

@@ -243,6 +243,7 @@ int gm_zero1_allgather_async(uintptr_t h, uintptr_t arena_base, int64_t count, i
     if (!z) return GM_ERR_BAD_ARG;
     if (!arena_base) { set_error("arena is nil"); return GM_ERR_NIL_BUFFER; }
     if (count <= 0 || (elem_bytes != 2 && elem_bytes != 4)) { set_error("bad count/element size"); return GM_ERR_BAD_SIZE; }
+    if (!buffer_holds(arena_base, (int64_t)z->world * count * elem_bytes, "all-gather arena")) return GM_ERR_BAD_SIZE;
     if (z->world == 1) return GM_OK;
     DeviceGuard g(z->dev);
     const char* send = (const char*)arena_base + (size_t)z->rank * count * elem_bytes;
@@ -502,6 +503,7 @@ int gm_zero1_reduce_scatter_async(uintptr_t h, uintptr_t grad_arena_base, int64_
     if (!z) return GM_ERR_BAD_ARG;
     if (!grad_arena_base) { set_error("arena is nil"); return GM_ERR_NIL_BUFFER; }
     if (count <= 0 || (elem_bytes != 2 && elem_bytes != 4)) { set_error("bad count/element size"); return GM_ERR_BAD_SIZE; }
+    if (!buffer_holds(grad_arena_base, (int64_t)z->world * count * elem_bytes, "reduce-scatter arena")) return GM_ERR_BAD_SIZE;
     if (z->world == 1) return GM_OK;
     if (!nccl().ReduceScatter) { set_error("ncclReduceScatter is not available"); return GM_ERR_UNSUPPORTED; }
     DeviceGuard g(z->dev);

@@ -210,6 +210,31 @@ def test_canonical_dot(gm, dev, oracle):
         dev.free(pb)
 
 
+def test_lbfgs_refuses_short_buffers(gm, dev):
+    """A buffer the library allocated that is shorter than buffer_sizes says is refused
+    before any kernel runs (a vector, a history slot, alpha)."""
+    L = gm.lib
+    n, m = 5000, 2
+    big = lambda: dev.alloc(4 * n)
+    x, g, old, d = big(), big(), big(), big()
+    S, Y = [big() for _ in range(m)], [big() for _ in range(m)]
+    RHO = [dev.alloc(4) for _ in range(m)]
+    alpha, short = dev.alloc(4 * m), dev.alloc(4 * 100)
+    step = C.c_float()
+
+    def call(xx=x, ss=None, aa=alpha):
+        return L.execute_lbfgs_step_cuda(dev.h, gm.uarray([xx]), gm.uarray([g]), gm.uarray([old]), gm.uarray([d]),
+                                         gm.uarray(ss or S), gm.uarray(Y), gm.uarray(RHO), aa, 1, gm.iarray([4 * n]), m, 0, 0,
+                                         1.0, 1e-4, 0.9, 20, 0.0, 0.0, C.byref(step))
+    assert call() == 0, gm.last_error()
+    assert call(xx=short) == -9 and "L-BFGS vector" in gm.last_error()
+    assert call(ss=[S[0], short]) == -9 and "L-BFGS history" in gm.last_error()
+    assert call(aa=dev.alloc(4)) == -9 and "L-BFGS alpha" in gm.last_error()
+    assert call() == 0
+    for p in [x, g, old, d, alpha, short] + S + Y + RHO:
+        dev.free(p)
+
+
 def test_lbfgs_argument_errors(gm, dev):
     L = gm.lib
     p = dev.alloc(64)

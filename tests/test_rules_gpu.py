@@ -338,6 +338,10 @@ def test_convert_roundtrip(gm, dev, oracle):
     gm.check(gm.lib.convert_tensor_type_cuda(dst, back, shape, 1, 2, 0, dev.h), "f16->f32")
     assert np.array_equal(dev.to_host(back, n).view(np.uint32), O.f16_to_f32(h).view(np.uint32))
     assert gm.lib.convert_tensor_type_cuda(src, dst, shape, 1, 0, 1, dev.h) == -11
+    tiny = dev.alloc(64)                                      # a destination that cannot hold the result is refused
+    assert gm.lib.convert_tensor_type_cuda(src, tiny, shape, 1, 0, 2, dev.h) == -9
+    assert gm.lib.convert_tensor_type_cuda(tiny, back, shape, 1, 2, 0, dev.h) == -9
+    dev.free(tiny)
     for p in (src, dst, back):
         dev.free(p)
 
