@@ -648,6 +648,7 @@ int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, 
     if (!d) return GM_ERR_NIL_DEVICE;
     if (!a || !b || !out) { set_error("nil argument"); return GM_ERR_NIL_BUFFER; }
     if (n <= 0) { set_error("length %lld is not positive", (long long)n); return GM_ERR_BAD_SIZE; }
+    if (!buffer_holds(a, 4 * n, "dot operand") || !buffer_holds(b, 4 * n, "dot operand")) return GM_ERR_BAD_SIZE;
     // A one-tensor table with the two operands in columns 0 and 1.
     const int64_t nc = (n + kDotChunk - 1) / kDotChunk;
     if (nc > 0x7fffffff) { set_error("vector too long"); return GM_ERR_BAD_SIZE; }
