@@ -352,7 +352,14 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
             const long long e = (b + chunk < n) ? b + chunk : n;
             if (k == 0 && tid < h) scalar_at(tid);
 
-            if (WIDE) {
+            // The 256-bit accesses need the fp32 streams on a 32-byte boundary.  The alignment peel
+            // guarantees 16 bytes; 32 follow whenever the streams of a tensor share one element
+            // offset (the fp16 streams then force a multiple of 8 elements), which is the usual
+            // packing.  A tensor whose streams sit at different offsets can miss it and takes the
+            // 4-element path below.
+            const bool wide_ok = WIDE && (((reinterpret_cast<uintptr_t>(w + b) | reinterpret_cast<uintptr_t>(m + b) |
+                                            reinterpret_cast<uintptr_t>(v + b)) & 31) == 0);
+            if (wide_ok) {
                 // 8 consecutive elements per thread per pass: one 16-byte access on the fp16
                 // streams, one 32-byte access on each fp32 stream, all loads before the arithmetic
                 const int nv8 = (int)((e - b) >> 3);

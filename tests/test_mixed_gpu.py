@@ -319,3 +319,55 @@ def test_random_alignments_mixed(gm, dev, oracle, seed):
         L.gm_tensor_list_destroy(lst)
         for k in keys:
             dev.free(bufs[k])
+
+
+def test_fp32_streams_on_16_but_not_32_byte_boundaries(gm, dev, oracle):
+    """fp16 streams on a 16-byte boundary and fp32 streams 16 bytes past a 32-byte one:
+    every stream is vector-aligned with no peel, yet the 256-bit accesses of the update
+    kernel would be misaligned, so those tensors must take its 128-bit path.  One tensor
+    in the usual packing (all streams at one element offset) rides along."""
+    O, L = oracle, gm.lib
+    sizes = [20_000, 8192 + 24, 3000]
+    keys, eb = "gwmvp", {"g": 2, "w": 4, "m": 4, "v": 4, "p": 2}
+    dt = {k: (np.uint16 if eb[k] == 2 else np.float32) for k in keys}
+    span = sum(sizes) + 64 * len(sizes) + 64
+    offs = {k: [] for k in keys}
+    at = 16
+    for t, n in enumerate(sizes):
+        for k in keys:
+            skew = 4 if (eb[k] == 4 and t < 2) else 0          # fp32 streams of tensors 0 and 1: +16 bytes
+            offs[k].append(at + skew)
+        at += (n + 63) // 16 * 16 + 16
+    master = [O.fill_uniform(n, -0.05, 0.05, 71, 50 + t) for t, n in enumerate(sizes)]
+    m = [np.zeros(n, np.float32) for n in sizes]
+    v = [np.zeros(n, np.float32) for n in sizes]
+    p16 = [O.f32_to_f16(w) for w in master]
+    host = {k: np.zeros(span, dt[k]) for k in keys}
+    for t, n in enumerate(sizes):
+        host["w"][offs["w"][t]:offs["w"][t] + n] = master[t]
+        host["p"][offs["p"][t]:offs["p"][t] + n] = p16[t]
+    bufs = {k: dev.to_device(host[k]) for k in keys}
+    for t in range(2):
+        assert (bufs["g"] + 2 * offs["g"][t]) % 16 == 0 and (bufs["w"] + 4 * offs["w"][t]) % 32 == 16
+    lst = dev.tensor_list([[bufs[k] + eb[k] * offs[k][t] for t in range(len(sizes))] for k in keys], sizes, [eb[k] for k in keys])
+    st = O.new_loss_scale(interval=2000)
+    mx = L.gm_mixed_create(dev.h, None, B1, B2, 0)
+    rng = np.random.default_rng(3)
+    try:
+        for step in range(1, 4):
+            g16 = [O.f32_to_f16(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3) * np.float32(st.scale)) for n in sizes]
+            for t, n in enumerate(sizes):
+                host["g"][offs["g"][t]:offs["g"][t] + n] = g16[t]
+            dev.upload(bufs["g"], host["g"])
+            gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed step")
+            assert O.mixed_adam_step(g16, master, m, v, p16, LR, B1, B2, EPS, WD, st) == 0
+            for k, arrs in (("w", master), ("m", m), ("v", v), ("p", p16)):
+                for t, n in enumerate(sizes):
+                    host[k][offs[k][t]:offs[k][t] + n] = arrs[t]
+                got = dev.to_host(bufs[k], span, dt[k])
+                assert np.array_equal(got.view(np.uint8), host[k].view(np.uint8)), f"step {step} stream {k}"
+    finally:
+        L.gm_mixed_destroy(mx)
+        L.gm_tensor_list_destroy(lst)
+        for k in keys:
+            dev.free(bufs[k])
