@@ -241,6 +241,25 @@ def case_sizes(dev, reps, small):
             dev.free(bufs[k])
 
 
+def case_convert(dev, reps, small):
+    """Standalone fp32 <-> fp16 conversion (the drop-in convert_tensor_type entry, synchronous), 6 B/element."""
+    n = 25_165_824 // (4 if small else 1)
+    src = dev.to_device((np.random.default_rng(4).standard_normal(n) * 3).astype(np.float32))
+    half, back = dev.alloc(2 * n), dev.alloc(4 * n)
+    shape = gm.iarray([n])
+    for name, a, b, st, dt_ in (("f32->f16", src, half, 0, 2), ("f16->f32", half, back, 2, 0)):
+        walls = []
+        for _ in range(max(reps, 5)):
+            dev.sync()
+            t0 = time.perf_counter()
+            gm.check(L.convert_tensor_type_cuda(a, b, shape, 1, st, dt_, dev.h), "convert")
+            walls.append((time.perf_counter() - t0) * 1e3)
+        ms = float(np.median(walls))
+        emit(kernel="convert " + name, elements=n, ms=ms, gbs=6 * n / ms / 1e6, note="host wall clock around the synchronous entry")
+    for p in (src, half, back):
+        dev.free(p)
+
+
 def _zeros(dev, k):
     p = dev.alloc(4 * k)
     gm.check(L.gm_buffer_zero(dev.h, p, 4 * k), "zero")
@@ -249,13 +268,13 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small", "sizes"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small", "sizes", "convert"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
-        cases = {"sizes": case_sizes, "rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
+        cases = {"sizes": case_sizes, "convert": case_convert, "rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
                  "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16),
                  "mixed_norm": lambda d, r, sm: case_mixed(d, r, sm, norm=True)}
         cases[args.case](dev, args.reps, args.small)

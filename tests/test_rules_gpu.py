@@ -338,6 +338,19 @@ def test_convert_roundtrip(gm, dev, oracle):
     gm.check(gm.lib.convert_tensor_type_cuda(dst, back, shape, 1, 2, 0, dev.h), "f16->f32")
     assert np.array_equal(dev.to_host(back, n).view(np.uint32), O.f16_to_f32(h).view(np.uint32))
     assert gm.lib.convert_tensor_type_cuda(src, dst, shape, 1, 0, 1, dev.h) == -11
+    # buffers off the 16-byte boundary take the element-wise kernels; same results
+    src1 = dev.to_device(np.concatenate([[np.float32(0)], x]))
+    dst1 = dev.alloc((n + 8) * 2)
+    back1 = dev.alloc((n + 8) * 4)
+    gm.check(gm.lib.convert_tensor_type_cuda(src1 + 4, dst1 + 2, shape, 1, 0, 2, dev.h), "f32->f16 unaligned")
+    assert np.array_equal(dev.to_host(dst1, n + 1, np.uint16)[1:], O.f32_to_f16(x))
+    gm.check(gm.lib.convert_tensor_type_cuda(dst1 + 2, back1 + 4, shape, 1, 2, 0, dev.h), "f16->f32 unaligned")
+    assert np.array_equal(dev.to_host(back1, n + 1)[1:].view(np.uint32), O.f16_to_f32(h).view(np.uint32))
+    for n_small in (1, 7, 8, 9, 4096):                          # vector passes and the ragged tail
+        gm.check(gm.lib.convert_tensor_type_cuda(src, dst, gm.iarray([n_small]), 1, 0, 2, dev.h), "small")
+        assert np.array_equal(dev.to_host(dst, n_small, np.uint16), O.f32_to_f16(x[:n_small]))
+    for p in (src1, dst1, back1):
+        dev.free(p)
     tiny = dev.alloc(64)                                      # a destination that cannot hold the result is refused
     assert gm.lib.convert_tensor_type_cuda(src, tiny, shape, 1, 0, 2, dev.h) == -9
     assert gm.lib.convert_tensor_type_cuda(tiny, back, shape, 1, 2, 0, dev.h) == -9
