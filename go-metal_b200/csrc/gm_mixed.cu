@@ -458,21 +458,40 @@ sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
         const int2 rec = __ldg(L.chunk_rec + c);
         const int t = rec.x, k = rec.y;
         const long long n = __ldg(L.numel + t);
-        const long long b = (long long)k * chunk + (k > 0 && __ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
-        long long e = (long long)(k + 1) * chunk + (__ldg(L.head + t) > 0 ? __ldg(L.head + t) : 0);
+        const int h = __ldg(L.head + t);
+        const long long hh = h > 0 ? h : 0;
+        const long long b = (long long)k * chunk + (k > 0 ? hh : 0);     // chunk 0 also takes the h elements before the boundary
+        long long e = (long long)(k + 1) * chunk + hh;
         if (e > n) e = n;
+        constexpr int V = HALF ? 8 : 4;                                  // elements per 16-byte access
+        // [b, a0) before the 16-byte boundary, [a0, a0 + nvec*V) in 16-byte accesses, the rest one by one
+        const long long a0 = h < 0 ? e : (k == 0 ? (hh < e ? hh : e) : b);
+        const long long nvec = h < 0 ? 0 : (e - a0) / V;
+        const long long tail = a0 + nvec * V;
         if (HALF) {
             const unsigned short* g = reinterpret_cast<const unsigned short*>(__ldg(L.ptrs + t));
-            for (long long i = b + tid; i < e; i += NT) {
-                const float x = half_bits_to_float(g[i]) * inv_scale;
-                acc = fmaf(x, x, acc);
+            for (long long i = b + tid; i < a0; i += NT) acc = sumsq1(g[i], inv_scale, acc);
+            const uint4* q = reinterpret_cast<const uint4*>(g + a0);
+            for (long long i = tid; i < nvec; i += 2 * NT) {
+                const uint4 v0 = __ldcs(q + i);
+                const uint4 v1 = i + NT < nvec ? __ldcs(q + i + NT) : make_uint4(0u, 0u, 0u, 0u);
+                acc = sumsq8(v1, inv_scale, sumsq8(v0, inv_scale, acc));
             }
+            for (long long i = tail + tid; i < e; i += NT) acc = sumsq1(g[i], inv_scale, acc);
         } else {
             const float* g = reinterpret_cast<const float*>(__ldg(L.ptrs + t));
-            for (long long i = b + tid; i < e; i += NT) {
-                const float x = g[i] * inv_scale;
-                acc = fmaf(x, x, acc);
+            auto one = [&](long long i) { const float x = g[i] * inv_scale; acc = fmaf(x, x, acc); };
+            for (long long i = b + tid; i < a0; i += NT) one(i);
+            const float4* q = reinterpret_cast<const float4*>(g + a0);
+            for (long long i = tid; i < nvec; i += 2 * NT) {
+                const float4 v0 = __ldcs(q + i);
+                const float4 v1 = i + NT < nvec ? __ldcs(q + i + NT) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float x[8] = {v0.x * inv_scale, v0.y * inv_scale, v0.z * inv_scale, v0.w * inv_scale,
+                                    v1.x * inv_scale, v1.y * inv_scale, v1.z * inv_scale, v1.w * inv_scale};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc = fmaf(x[j], x[j], acc);
             }
+            for (long long i = tail + tid; i < e; i += NT) one(i);
         }
     }
 #pragma unroll

@@ -260,6 +260,24 @@ def case_convert(dev, reps, small):
         dev.free(p)
 
 
+def case_sumsq(dev, reps, small):
+    """Stand-alone gradient sum of squares: 2^28 fp32 elements (4 B each) and 2^28 fp16 elements (2 B each)."""
+    n, nt = (1 << 28) // (16 if small else 1), 16
+    per = n // nt
+    out = dev.alloc(256)
+    for eb, name in ((4, "fp32"), (2, "fp16")):
+        buf = dev.alloc(eb * n)
+        fill(dev, buf, n * eb // 4, 0.01, 7)                     # any finite bit pattern will do for a timing
+        if eb == 2:
+            gm.check(L.gm_buffer_zero(dev.h, buf, eb * n), "zero")   # halves: zeros (an fp32 pattern may read as inf/NaN halves)
+        lst = dev.tensor_list([[buf + eb * per * t for t in range(nt)]], [per] * nt, [eb])
+        ms = timed(dev, lambda: gm.check(L.gm_grad_sumsq_async(dev.h, lst, eb, 1.0, out), "sumsq"), reps)
+        emit(kernel=f"sumsq_kernel<{name}>", elements=n, ms=ms, gbs=eb * n / ms / 1e6)
+        L.gm_tensor_list_destroy(lst)
+        dev.free(buf)
+    dev.free(out)
+
+
 def _zeros(dev, k):
     p = dev.alloc(4 * k)
     gm.check(L.gm_buffer_zero(dev.h, p, 4 * k), "zero")
@@ -268,13 +286,13 @@ def _zeros(dev, k):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small", "sizes", "convert"], required=True)
+    ap.add_argument("--case", choices=["rules", "mixed", "mixed_norm", "mixed_x16", "lbfgs", "small", "sizes", "convert", "sumsq"], required=True)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--small", action="store_true")
     args = ap.parse_args()
     dev = gm.Device(0)
     try:
-        cases = {"sizes": case_sizes, "convert": case_convert, "rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
+        cases = {"sizes": case_sizes, "convert": case_convert, "sumsq": case_sumsq, "rules": case_rules, "mixed": case_mixed, "lbfgs": case_lbfgs, "small": case_small,
                  "mixed_x16": lambda d, r, sm: case_mixed(d, r, sm, scale_up=16),
                  "mixed_norm": lambda d, r, sm: case_mixed(d, r, sm, norm=True)}
         cases[args.case](dev, args.reps, args.small)
