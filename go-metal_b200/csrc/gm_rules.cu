@@ -263,7 +263,7 @@ int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper
 // and the download of slice s-1 overlap the update of slice s and both PCIe
 // directions are busy at once.  host_grads / host_params hold the tensors back
 // to back in list order; the device gradient (stream 1) and parameter (stream
-// 0) tensors must be contiguous too.  Synchronous: host_params is complete on return.
+// 0) tensors may be one flat run or separate allocations.  Synchronous: host_params is complete on return.
 int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, const void* host_grads,
                  void* host_params, int num_slices) {
     Device* d = as_device(device_ptr);
@@ -274,14 +274,13 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
     if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
     if (l->dl.num_streams < 2) { set_error("list needs at least the parameter and gradient streams"); return GM_ERR_BAD_ARG; }
     const int T = l->dl.num_tensors;
-    for (int t = 0; t + 1 < T; ++t) {
-        for (int s = 0; s < 2; ++s) {
-            if (l->ptrs[s][t] + (uintptr_t)l->numel[t] * 4 != l->ptrs[s][t + 1]) {
-                set_error("stream %d tensors %d and %d are not contiguous on the device", s, t, t + 1);
-                return GM_ERR_BAD_ARG;
-            }
-        }
-    }
+    if (l->elem_bytes[0] != 4 || l->elem_bytes[1] != 4) { set_error("the host-buffer step needs fp32 parameters and gradients"); return GM_ERR_BAD_ARG; }
+    // Tensors that lie back to back on the device (a flat arena) move with one copy per slice
+    // and direction; separately allocated tensors move one by one.
+    bool packed = true;
+    for (int t = 0; t + 1 < T && packed; ++t)
+        for (int s = 0; s < 2; ++s)
+            if (l->ptrs[s][t] + (uintptr_t)l->numel[t] * 4 != l->ptrs[s][t + 1]) packed = false;
     if (num_slices < 1) num_slices = 1;
     if (num_slices > T) num_slices = T;
     DeviceGuard guard(d);
@@ -301,7 +300,16 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
         size_t bytes = 0;
         for (int t = t0; t < t1; ++t) bytes += (size_t)l->numel[t] * 4;
         cudaEvent_t in = d->slice_events[2 * s], done = d->slice_events[2 * s + 1];
-        GM_CUDA_CHECK(cudaMemcpyAsync((void*)l->ptrs[1][t0], (const char*)host_grads + host_off, bytes, cudaMemcpyHostToDevice, d->h2d_stream));
+        if (packed) {
+            GM_CUDA_CHECK(cudaMemcpyAsync((void*)l->ptrs[1][t0], (const char*)host_grads + host_off, bytes, cudaMemcpyHostToDevice, d->h2d_stream));
+        } else {
+            size_t off = host_off;
+            for (int t = t0; t < t1; ++t) {
+                const size_t tb = (size_t)l->numel[t] * 4;
+                GM_CUDA_CHECK(cudaMemcpyAsync((void*)l->ptrs[1][t], (const char*)host_grads + off, tb, cudaMemcpyHostToDevice, d->h2d_stream));
+                off += tb;
+            }
+        }
         GM_CUDA_CHECK(cudaEventRecord(in, d->h2d_stream));
         GM_CUDA_CHECK(cudaStreamWaitEvent(d->stream, in, 0));
         l->win_begin = l->chunk_prefix[t0];
@@ -311,7 +319,16 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
         if (rc != GM_OK) break;
         GM_CUDA_CHECK(cudaEventRecord(done, d->stream));
         GM_CUDA_CHECK(cudaStreamWaitEvent(d->d2h_stream, done, 0));
-        GM_CUDA_CHECK(cudaMemcpyAsync((char*)host_params + host_off, (const void*)l->ptrs[0][t0], bytes, cudaMemcpyDeviceToHost, d->d2h_stream));
+        if (packed) {
+            GM_CUDA_CHECK(cudaMemcpyAsync((char*)host_params + host_off, (const void*)l->ptrs[0][t0], bytes, cudaMemcpyDeviceToHost, d->d2h_stream));
+        } else {
+            size_t off = host_off;
+            for (int t = t0; t < t1; ++t) {
+                const size_t tb = (size_t)l->numel[t] * 4;
+                GM_CUDA_CHECK(cudaMemcpyAsync((char*)host_params + off, (const void*)l->ptrs[0][t], tb, cudaMemcpyDeviceToHost, d->d2h_stream));
+                off += tb;
+            }
+        }
         host_off += bytes;
     }
     cudaError_t e1 = cudaStreamSynchronize(d->h2d_stream);

@@ -204,8 +204,8 @@ func (m *MixedAdam) Destroy() { C.gm_mixed_destroy(m.h); m.h = 0 }
 
 // StepHost runs one step with the gradients in (pinned) host memory and the new
 // parameters returned to host memory; upload, update and download are pipelined
-// over `slices` groups of tensors.  The list's parameter and gradient tensors must
-// lie back to back on the device.
+// over `slices` groups of tensors.  Parameter and gradient tensors that lie back to back
+// on the device move with one copy per slice, separately allocated ones one by one.
 func StepHost(device unsafe.Pointer, rule Rule, list *TensorList, hyper Hyper, hostGrads, hostParams unsafe.Pointer, slices int) error {
 	ch := hyper.c()
 	return stepError("host-buffer step", C.gm_step_host(handle(device), C.int(rule), list.h, &ch, hostGrads, hostParams, C.int(slices)))

@@ -222,8 +222,9 @@ int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper
  * memory: gradients are uploaded, the rule is applied and the new parameters
  * are downloaded slice by slice on three streams, so both PCIe directions and
  * the SMs are busy at once.  host_grads / host_params hold the tensors back to
- * back in list order; stream 0 (parameters) and stream 1 (gradients) of the
- * list must be contiguous on the device.  Synchronous. */
+ * back in list order; on the device stream 0 (parameters) and stream 1
+ * (gradients) may be one flat run (one copy per slice and direction) or
+ * separately allocated tensors (one copy each).  fp32 only.  Synchronous. */
 int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
                  const void* host_grads, void* host_params, int num_slices);
 

@@ -393,11 +393,20 @@ def test_host_buffer_step_matches_oracle(gm, dev, oracle, sizes):
             assert np.array_equal(hw_arr.view(np.uint32), w.view(np.uint32)), f"step {step}: downloaded parameters"
             assert np.array_equal(dev.to_host(dw, n).view(np.uint32), w.view(np.uint32)), f"step {step}: device parameters"
         assert np.array_equal(dev.to_host(dv, n).view(np.uint32), v.view(np.uint32))
-        # non-contiguous device tensors are refused
-        bad = dev.tensor_list([[dw, dw + 4 * 6000], [dg, dg + 4 * 6000], [dm, dm + 4 * 6000], [dv, dv + 4 * 6000]], [5000, 100])
-        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=1)
-        assert L.gm_step_host(dev.h, gm.RULE_ADAM, bad, C.byref(hy), hg, hw, 2) == -10
-        L.gm_tensor_list_destroy(bad)
+        # tensors that do not lie back to back on the device (here: a gap after the first) move one by one
+        gap = dev.tensor_list([[dw, dw + 4 * 6000], [dg, dg + 4 * 6000], [dm, dm + 4 * 6000], [dv, dv + 4 * 6000]], [5000, 100])
+        before = {k: dev.to_host(p, n) for k, p in (("w", dw), ("m", dm), ("v", dv))}
+        g2 = O.fill_normal(5100, 0.0, 0.01, 61, 99)
+        hg_arr[:5100] = g2
+        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=5)
+        gm.check(L.gm_step_host(dev.h, gm.RULE_ADAM, gap, C.byref(hy), hg, hw, 2), "gm_step_host on separate tensors")
+        for lo, cnt, src in ((0, 5000, 0), (6000, 100, 5000)):
+            ws, ms, vs = (np.ascontiguousarray(before[k][lo:lo + cnt]) for k in "wmv")
+            O.adam_step(ws, np.ascontiguousarray(g2[src:src + cnt]), ms, vs, 1e-3, 0.9, 0.999, 1e-8, 0.0, 5)
+            assert np.array_equal(hw_arr[src:src + cnt].view(np.uint32), ws.view(np.uint32)), "downloaded parameters (separate tensors)"
+            assert np.array_equal(dev.to_host(dw, n)[lo:lo + cnt].view(np.uint32), ws.view(np.uint32))
+        assert np.array_equal(dev.to_host(dw, n)[5000:6000].view(np.uint32), before["w"][5000:6000].view(np.uint32)), "the gap was written"
+        L.gm_tensor_list_destroy(gap)
     finally:
         L.gm_tensor_list_destroy(lst)
         L.gm_host_free_pinned(hg)
