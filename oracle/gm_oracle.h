@@ -24,6 +24,13 @@
 extern "C" {
 #endif
 
+/* ---- threads ----
+ * Elementwise loops and per-chunk partial sums are independent per element or
+ * chunk; running them on several threads (pthreads) changes no result bit.  The
+ * default is 1.  Used by the full-size parity cases only. */
+void gmo_set_threads(int threads);
+int gmo_get_threads(void);
+
 /* ---- elementwise rules (one flat tensor per call; in place) ---- */
 
 /* cgo_bridge/bridge_optimizer.m:360-641 */
@@ -63,6 +70,8 @@ uint16_t gmo_f32_to_f16(float x);   /* round-to-nearest-even */
 float gmo_f16_to_f32(uint16_t h);   /* exact */
 void gmo_convert_f32_to_f16(const float* src, uint16_t* dst, size_t n);
 void gmo_convert_f16_to_f32(const uint16_t* src, float* dst, size_t n);
+/* dst[i] = half(src[i] * factor), the product rounded to binary32 first. */
+void gmo_scale_to_f16(const float* src, float factor, uint16_t* dst, size_t n);
 
 /* ---- mixed-precision Adam with dynamic loss scaling ----
  * Policy: training/model_trainer.go:258-270 (defaults 65536, x2, x0.5, 2000)
@@ -92,6 +101,26 @@ int gmo_mixed_adam_step(int num_tensors, const size_t* numel,
                         float lr, float beta1, float beta2, float eps, float wd,
                         gmo_loss_scale_t* st);
 
+/* Global-norm clipping (no code in the reference; docs/guides/optimizers.md:568-569
+ * names the concept).  coef = min(1, max_norm / (sqrt(sumsq) + 1e-6)) in binary32;
+ * a NaN coefficient becomes 1.  Clipped steps multiply every gradient by coef
+ * (one rounding) before the rule. */
+float gmo_clip_coef(float sumsq, float max_norm);
+/* Sum of squares of a list of fp32 tensors in the canonical dot order. */
+float gmo_sumsq_canonical(int num_tensors, const size_t* numel, const float* const* g);
+/* Sum of (half*inv_scale)^2 in the order of the CUDA overflow-check pass, which
+ * follows the memory layout: head[t] = elements of tensor t before the first
+ * address where all its streams are 16-byte aligned (-1 none), chunk = elements
+ * per chunk of the list (8192 by default).  See the definition for the order. */
+float gmo_sumsq_f16_layout(int num_tensors, const size_t* numel, const uint16_t* const* g16,
+                           const int* head, size_t chunk, float inv_scale);
+int gmo_mixed_adam_step_clipped(int num_tensors, const size_t* numel,
+                                const uint16_t* const* g16, float* const* master,
+                                float* const* m, float* const* v, uint16_t* const* p16,
+                                float lr, float beta1, float beta2, float eps, float wd,
+                                float max_norm, const int* head, size_t chunk,
+                                float* sumsq, float* coef, gmo_loss_scale_t* st);
+
 /* ---- reductions ---- */
 /* Dot product in the canonical fixed order used by the CUDA kernels:
  * 4096-element chunks; inside a chunk lane t of 256 walks elements
@@ -120,7 +149,9 @@ double gmo_sumsq_f16(const uint16_t* g, size_t n, float inv_scale);
  * reference starts from q = -g and negates again at the end, :1026-1038 and
  * :1204-1213, which moves along +H*g).  0 = the reference's statement order,
  * 3 = a working L-BFGS.
- * order 0 = canonical dot order, 1 = sequential (reference) order. */
+ * order 0 = canonical dot order, 1 = sequential (reference) order: one fp32
+ * accumulator per tensor for the loop dots (:1073-1109) and one accumulator
+ * carried across the tensors for s.y (:1272-1297). */
 int gmo_lbfgs_step(int num_tensors, const size_t* numel,
                    float* const* w, const float* const* g, float* const* old_g,
                    float* const* dir, float* const* s, float* const* y,

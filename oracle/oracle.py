@@ -83,6 +83,19 @@ def lib():
     L.gmo_lbfgs_step.argtypes = [i, C.POINTER(z), pp, pp, pp, pp, pp, pp, _f32p, _f32p,
                                  i, i, i, f, i, i, C.POINTER(f)]
     L.gmo_lbfgs_step.restype = i
+    L.gmo_set_threads.argtypes = [i]
+    L.gmo_get_threads.restype = i
+    L.gmo_scale_to_f16.argtypes = [_f32p, f, _u16p, z]
+    L.gmo_clip_coef.argtypes = [f, f]
+    L.gmo_clip_coef.restype = f
+    L.gmo_sumsq_canonical.argtypes = [i, C.POINTER(z), pp]
+    L.gmo_sumsq_canonical.restype = f
+    L.gmo_sumsq_f16_layout.argtypes = [i, C.POINTER(z), pp, C.POINTER(i), z, f]
+    L.gmo_sumsq_f16_layout.restype = f
+    L.gmo_mixed_adam_step_clipped.argtypes = [i, C.POINTER(z), pp, pp, pp, pp, pp, f, f, f, f, f,
+                                              f, C.POINTER(i), z, C.POINTER(f), C.POINTER(f),
+                                              C.POINTER(LossScale)]
+    L.gmo_mixed_adam_step_clipped.restype = i
     L.gmo_hash64.argtypes = [C.c_uint64] * 3
     L.gmo_hash64.restype = C.c_uint64
     L.gmo_fill_uniform.argtypes = [_f32p, z, f, f, C.c_uint64, C.c_uint64]
@@ -102,6 +115,15 @@ def _ptr_array(arrays):
 
 def _opt(a):
     return None if a is None else a.ctypes.data
+
+
+def set_threads(n: int) -> None:
+    """Threads for the independent elementwise loops (bit-identical results; default 1)."""
+    lib().gmo_set_threads(int(n))
+
+
+def all_cores() -> int:
+    return max(1, min(64, os.cpu_count() or 1))
 
 
 # ---- elementwise rules (flat float32 arrays, updated in place) ----
@@ -160,6 +182,14 @@ def f16_to_f32(h):
     return out
 
 
+def scale_to_f16(x, factor):
+    """half(x * factor), the product rounded to float32 first."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().gmo_scale_to_f16(x.reshape(-1), float(factor), out.reshape(-1), x.size)
+    return out
+
+
 # ---- mixed precision ----
 
 def new_loss_scale(**kw):
@@ -176,6 +206,35 @@ def mixed_adam_step(g16, master, m, v, p16, lr, beta1, beta2, eps, wd, state):
     return lib().gmo_mixed_adam_step(n, numel, _ptr_array(g16), _ptr_array(master), _ptr_array(m),
                                      _ptr_array(v), _ptr_array(p16), lr, beta1, beta2, eps, wd,
                                      C.byref(state))
+
+
+def mixed_adam_step_clipped(g16, master, m, v, p16, lr, beta1, beta2, eps, wd, max_norm, head, chunk, state):
+    """Returns (skipped, sumsq, coef); head = per-tensor element offsets of the device layout."""
+    n = len(g16)
+    numel = (C.c_size_t * n)(*[a.size for a in master])
+    heads = (C.c_int * n)(*[int(h) for h in head])
+    ss, cf = C.c_float(), C.c_float()
+    skipped = lib().gmo_mixed_adam_step_clipped(n, numel, _ptr_array(g16), _ptr_array(master), _ptr_array(m),
+                                                _ptr_array(v), _ptr_array(p16), lr, beta1, beta2, eps, wd,
+                                                max_norm, heads, chunk, C.byref(ss), C.byref(cf), C.byref(state))
+    return skipped, np.float32(ss.value), np.float32(cf.value)
+
+
+def clip_coef(sumsq, max_norm):
+    return np.float32(lib().gmo_clip_coef(float(sumsq), float(max_norm)))
+
+
+def sumsq_canonical(tensors):
+    n = len(tensors)
+    numel = (C.c_size_t * n)(*[a.size for a in tensors])
+    return np.float32(lib().gmo_sumsq_canonical(n, numel, _ptr_array(tensors)))
+
+
+def sumsq_f16_layout(g16, head, chunk, inv_scale):
+    n = len(g16)
+    numel = (C.c_size_t * n)(*[a.size for a in g16])
+    heads = (C.c_int * n)(*[int(h) for h in head])
+    return np.float32(lib().gmo_sumsq_f16_layout(n, numel, _ptr_array(g16), heads, chunk, float(inv_scale)))
 
 
 # ---- reductions ----

@@ -138,3 +138,47 @@ def _reduce_partials_to_lanes(partials):
 
 def _reduce_lanes(lane):
     return _tree(lane.reshape(1, 256))[0]
+
+
+def sumsq_f16_layout(g16_list, heads, chunk, inv_scale):
+    """Sum of (half * inv_scale)^2 in the order of the CUDA overflow-check pass, written
+    with numpy array operations (see gmo_sumsq_f16_layout for the order in words)."""
+    inv = f32(inv_scale)
+    partials = []
+    for g16, hd in zip(g16_list, heads):
+        n = g16.size
+        sq_all = (g16.view(np.float16).astype(f32) * inv).astype(f32)
+        sq_all = (sq_all * sq_all).astype(f32)
+        h = min(max(hd, 0), n)
+        body = n - h
+        nchunks = (body + chunk - 1) // chunk if body > 0 else 1
+        for k in range(nchunks):
+            b = min(h + k * chunk, n)
+            e = min(b + chunk, n)
+            lane = np.zeros(256, f32)
+            if hd < 0:
+                seg = sq_all[b:e]
+                rounds = (seg.size + 255) // 256
+                for r in range(rounds):
+                    part = seg[r * 256:(r + 1) * 256]
+                    lane[:part.size] = lane[:part.size] + part
+            else:
+                nvec = (e - b) >> 3
+                vecs = sq_all[b:b + 8 * nvec].reshape(nvec, 8)
+                rounds = (nvec + 255) // 256
+                for r in range(rounds):
+                    part = vecs[r * 256:(r + 1) * 256]
+                    for j in range(8):
+                        lane[:part.shape[0]] = lane[:part.shape[0]] + part[:, j]
+                if k == 0 and h > 0:
+                    lane[:h] = lane[:h] + sq_all[:h]
+                tail = sq_all[b + 8 * nvec:e]
+                lane[:tail.size] = lane[:tail.size] + tail
+            partials.append(_tree(lane.reshape(1, 256))[0])
+    return _reduce_lanes(_reduce_partials_to_lanes(np.array(partials, f32)))
+
+
+def clip_coef(sumsq, max_norm):
+    norm = np.sqrt(f32(sumsq)).astype(f32)
+    coef = f32(max_norm) / f32(norm + f32(1e-6))
+    return f32(coef) if coef < 1.0 else f32(1.0)

@@ -281,6 +281,120 @@ def test_lbfgs_orders_agree_within_rounding(oracle):
         assert np.allclose(xa, xs, rtol=1e-3, atol=1e-4)
 
 
+def test_sequential_order_carries_one_accumulator_across_tensors_for_sy(oracle):
+    """bridge_optimizer.m:1272-1297 adds every s*y product of every tensor into one
+    fp32 accumulator, unlike the loop dots (:1073-1109) that sum per tensor first."""
+    O = oracle
+    sizes = [301, 77, 1025]
+    rng = np.random.default_rng(4)
+    mk = lambda: [rng.standard_normal(n).astype(f32) for n in sizes]
+    z = lambda: [np.zeros(n, f32) for n in sizes]
+    x, old, d = z(), mk(), z()
+    g = mk()
+    s, y = [mk(), mk()], [z(), z()]
+    rho, alpha = np.zeros(2, f32), np.zeros(2, f32)
+    s_prev = [a.copy() for a in s[0]]
+    old_before = [a.copy() for a in old]
+    rc, _ = O.lbfgs_step(x, g, old, d, s, y, rho, alpha, 2, 1, 1, 1.0, 1, 1)
+    assert rc == 0
+    acc = f32(0.0)
+    for t in range(len(sizes)):
+        yt = (g[t] - old_before[t]).astype(f32)
+        for k in range(sizes[t]):
+            acc = f32(acc + f32(s_prev[t][k] * yt[k]))
+    assert bits(rho[0]) == bits(f32(1.0) / acc)
+
+
+def test_threads_change_no_bit(oracle):
+    """The pthread split of the independent loops must give the results of one thread."""
+    O = oracle
+    n = 300_007
+    def run():
+        a = O.fill_normal(n, 0, 1, 9, 1)
+        u = O.fill_uniform(n, -1, 1, 9, 2)
+        d = O.fill_loguniform(n, -1, 1, 9, 3)
+        h = O.f32_to_f16(a)
+        back = O.f16_to_f32(h)
+        sc = O.scale_to_f16(a, 3.0)
+        dot = O.dot_canonical(a, u)
+        st = O.new_loss_scale()
+        w, m, v = u.copy(), np.zeros(n, f32), np.zeros(n, f32)
+        p = O.f32_to_f16(w)
+        O.mixed_adam_step([h], [w], [m], [v], [p], 1e-3, 0.9, 0.999, 1e-8, 0.01, st)
+        _, _, hist = lbfgs_run(O, 200_000, 3, 4, mode=3)
+        ss = O.sumsq_f16_layout([h], [3], 8192, 0.5)
+        return [a, u, d, h, back, sc, np.array([dot, ss]), w, m, v, p, hist[-1][0]]
+    one = run()
+    O.set_threads(5)
+    try:
+        many = run()
+    finally:
+        O.set_threads(1)
+    for x, y in zip(one, many):
+        assert np.array_equal(x.view(np.uint8), y.view(np.uint8))
+    assert np.array_equal(one[5], O.f32_to_f16((one[0] * f32(3.0)).astype(f32)))
+
+
+@pytest.mark.parametrize("sizes,heads", [([5], [0]), ([70_001, 9, 8192 * 2 + 3], [3, 7, 0]), ([4099, 33], [-1, 1]),
+                                         ([2], [7])])
+def test_layout_sumsq_matches_numpy_restatement(oracle, sizes, heads):
+    O = oracle
+    g16 = [O.f32_to_f16(O.fill_normal(n, 0, 30.0, 12, k)) for k, n in enumerate(sizes)]
+    inv = 1.0 / 64.0
+    got = O.sumsq_f16_layout(g16, heads, 8192, inv)
+    assert bits(got) == bits(R.sumsq_f16_layout(g16, heads, 8192, inv))
+    exact = sum(O.sumsq_f16(g, inv) for g in g16)
+    assert abs(float(got) - exact) <= 1e-5 * exact
+    # a smaller chunk is another (equally valid) order: same value within rounding
+    assert abs(float(O.sumsq_f16_layout(g16, heads, 2048, inv)) - exact) <= 1e-5 * exact
+
+
+def test_canonical_sumsq_is_the_list_dot_of_g_with_itself(oracle):
+    O = oracle
+    g = [O.fill_normal(n, 0, 1, 13, k) for k, n in enumerate([4097, 3, 70_001])]
+    got = O.sumsq_canonical(g)
+    parts = np.concatenate([np.array([R.dot_canonical(a[c * 4096:(c + 1) * 4096], a[c * 4096:(c + 1) * 4096])
+                                      for c in range((a.size + 4095) // 4096)], f32) for a in g])
+    assert bits(got) == bits(R._reduce_lanes(R._reduce_partials_to_lanes(parts)))
+
+
+def test_clip_coefficient(oracle):
+    O = oracle
+    assert O.clip_coef(4.0, 1.0) == f32(1.0) / f32(f32(2.0) + f32(1e-6))
+    assert O.clip_coef(0.25, 1.0) == 1.0                       # norm below the limit: untouched
+    assert O.clip_coef(0.0, 1.0) == 1.0
+    assert O.clip_coef(np.inf, 1.0) == 0.0
+    assert O.clip_coef(np.nan, 1.0) == 1.0
+    for ss, mx in ((3.7, 0.5), (1e-12, 1e-7), (1e30, 2.0)):
+        assert bits(O.clip_coef(ss, mx)) == bits(R.clip_coef(ss, mx))
+
+
+def test_clipped_mixed_step_is_the_plain_step_on_clipped_gradients(oracle):
+    O = oracle
+    sizes, heads = [1000, 4099], [1, 5]
+    rng = np.random.default_rng(8)
+    g16 = [O.f32_to_f16(rng.standard_normal(n).astype(f32) * f32(65536 * 1e-2)) for n in sizes]
+    mk = lambda: ([O.fill_uniform(n, -1, 1, 3, k) for k, n in enumerate(sizes)], [np.zeros(n, f32) for n in sizes],
+                  [np.zeros(n, f32) for n in sizes], [np.zeros(n, np.uint16) for n in sizes])
+    w, m, v, p = mk()
+    st = O.new_loss_scale()
+    skipped, ss, coef = O.mixed_adam_step_clipped(g16, w, m, v, p, 1e-3, 0.9, 0.999, 1e-8, 0.0, 0.25, heads, 8192, st)
+    assert skipped == 0 and 0 < coef < 1 and bits(coef) == bits(O.clip_coef(ss, 0.25))
+    assert bits(ss) == bits(O.sumsq_f16_layout(g16, heads, 8192, 1.0 / 65536.0))
+    # the same update by hand: unscale, clip, fp32 Adam
+    w2, m2, v2, _ = mk()
+    for t in range(2):
+        g = (O.f16_to_f32(g16[t]) * f32(1.0 / 65536.0)).astype(f32)
+        g = (g * coef).astype(f32)
+        O.adam_step(w2[t], g, m2[t], v2[t], 1e-3, 0.9, 0.999, 1e-8, 0.0, 1)
+        assert same(w[t], w2[t]) and same(m[t], m2[t]) and same(v[t], v2[t])
+        assert np.array_equal(p[t], O.f32_to_f16(w[t]))
+    # an overflow step: not finite sum, skipped
+    g16[1][7] = 0x7c00
+    skipped, ss, coef = O.mixed_adam_step_clipped(g16, w, m, v, p, 1e-3, 0.9, 0.999, 1e-8, 0.0, 0.25, heads, 8192, st)
+    assert skipped == 1 and not np.isfinite(ss) and st.scale == 32768.0
+
+
 # ---------------------------------------------------------------- generators, fixtures
 
 def test_generators_are_deterministic_and_shaped(oracle):
