@@ -3,20 +3,23 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (all N): fp32 Adam (lr 1e-3, betas 0.9/0.999, eps 1e-8, no decay) on
-1,073,741,824 parameters in 256 flat tensors of 4,194,304, He-uniform weights
-and N(0, 0.01^2) gradients generated on the device from a fixed seed.  One
-step = one pass of the update over all parameters.  At N > 1 the optimizer
-state and the gradients are sharded ZeRO-1 style (rank r owns tensors
-[r*256/N, (r+1)*256/N)) and every step ends with the exchange of the updated
-fp32 parameters over NVLink, so the total work is fixed (strong scaling).
+Headline workload (all N): fp32 Adam (lr 1e-3, betas 0.9/0.999, eps 1e-8, no decay)
+on 1,073,741,824 parameters in 256 flat tensors of 4,194,304, He-uniform weights
+and N(0, 0.01^2) gradients generated on the device from a fixed seed.  One step =
+one pass of the update over all parameters.  At N > 1 the optimizer state and the
+gradients are sharded ZeRO-1 style (rank r owns tensors [r*256/N, (r+1)*256/N))
+and every step ends with the exchange of the updated fp32 parameters over
+NVLink, so the total work is fixed (strong scaling).
 
 `value` is timed with CUDA events on the stream the kernels are launched on,
-inputs resident in HBM, max over ranks.  `e2e` times the host-buffer entry
-(gm_step_host): every step copies that step's gradients from pinned host
-memory to the device and the updated parameters back to pinned host memory
-inside the timed region, pipelined slice by slice; the same step through the
-synchronous drop-in entry with plain copies is reported beside it.
+inputs resident in HBM, max over ranks.  After the timed region (and outside it)
+every rank compares a strided sample of its whole parameter arena with the CPU
+oracle replayed over the same steps: `parity_check`.  `e2e` times the host-buffer
+entry: every step copies that step's gradients from pinned host memory to the
+device and the updated parameters back inside the timed region, pipelined slice
+by slice.  At N = 1 a `workloads` block adds the other configurations, device
+timed: mixed-precision Adam (25.2 M parameters, 48 ragged tensors), L-BFGS
+(n = 10^7, history 10) and the other fp32 rules on 2^28 parameters.
 
 `--impl reference` times the CPU restatement of the reference's Adam rule
 (the oracle; the reference itself needs Apple Metal) on the host cores.
@@ -44,9 +47,12 @@ BYTES_PER_PARAM = 28            # read w,g,m,v (16) + write w,m,v (12)
 SEED = 0x5EED601D
 LR, B1, B2, EPS, WD = 1e-3, 0.9, 0.999, 1e-8, 0.0
 WORKLOAD = "fp32 Adam, 2^30 params in 256 flat tensors of 4 Mi (config 4), ZeRO-1 over N GPUs"
-# dram__bytes_read.sum + dram__bytes_write.sum of one mta_apply_kernel<AdamRule> launch,
-# measured on a 16-tensor launch and scaled by the tensor count (traffic is proportional to it).
-TRAFFIC_BYTES_PER_LAUNCH = 16 * (1.07389e9 + 0.75180e9)   # ncu, 16-tensor case: 1.074 GB read + 0.752 GB written, x16
+# Both arms print exactly this object as `config`.
+CONFIG = {"workload": WORKLOAD, "rule": "adam", "lr": LR, "beta1": B1, "beta2": B2, "eps": EPS, "weight_decay": WD,
+          "params": 256 * TENSOR_ELEMS, "tensors": 256, "seed": SEED}
+CPU_SAMPLE = 1 << 26            # parameters per CPU step (1/16 of the workload)
+NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
+NVLINK_MEASURED_GBS = 770.0     # peer copy measured on this pool, per direction
 
 
 def measured_peak_gbs():
@@ -56,6 +62,16 @@ def measured_peak_gbs():
             return float(json.load(fh)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def ncu_traffic_record():
+    """DRAM bytes of one launch of the headline kernel from the committed ncu capture."""
+    path = os.path.join(ROOT, "profiles", "adam_fp32_traffic.json")
+    try:
+        with open(path) as fh:
+            return json.load(fh)
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -122,8 +138,10 @@ def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | 
     cores = os.cpu_count() or 1
     n = sample_elems
     lim = float(np.sqrt(6.0 / 4096.0))
+    O.set_threads(cores)
     w = O.fill_uniform(n, -lim, lim, SEED, 1)
     g = O.fill_normal(n, 0.0, 0.01, SEED, 2)
+    O.set_threads(1)
     m = np.zeros(n, dtype=np.float32)
     v = np.zeros(n, dtype=np.float32)
     m.fill(0.0)                       # np.zeros maps pages lazily: touch them so that no timed step pays the page faults
@@ -142,6 +160,11 @@ def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | 
             break
     dt = time.perf_counter() - t0
     return n * done / dt / 1e9, cores, done, dt / done
+
+
+def cpu_sample_text(done: int) -> str:
+    return (f"{done} Adam steps over a {CPU_SAMPLE}-parameter slice (1/16 of the workload; same rule, same "
+            "hyper-parameters), pthread split over all host cores")
 
 
 def go_transcription_rate(sample_elems: int):
@@ -163,17 +186,14 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    sample = 1 << 26
-    rate, cores, done, per_step = cpu_adam_rate(args.steps, args.warmup, sample, None)
+    rate, cores, done, per_step = cpu_adam_rate(args.steps, args.warmup, CPU_SAMPLE, None)
     line = {
         "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
         "steps": done, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": f"{sample} of {TOTAL} params per step"},
-        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{done} Adam steps over a {sample}-parameter slice (same rule, same "
-                                   "hyper-parameters), pthread split over all host cores",
-                         "go_transcription": go_transcription_rate(sample)},
+        "config": dict(CONFIG),
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(done),
+                         "go_transcription": go_transcription_rate(CPU_SAMPLE)},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference's Adam rule (oracle); the reference itself needs Apple Metal",
     }
@@ -182,9 +202,186 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------
+# GPU arm: the other configurations, device timed (N = 1)
+# ---------------------------------------------------------------------------
+def _event_timed(gm, dev, fn, reps, warm=3):
+    L = gm.lib
+    for _ in range(warm):
+        fn()
+    dev.sync()
+    ms = C.c_float()
+    gm.check(L.gm_timer_start(dev.h), "timer")
+    for _ in range(reps):
+        fn()
+    gm.check(L.gm_timer_stop(dev.h, C.byref(ms)), "timer")
+    return ms.value / reps
+
+
+def _entry(name, params, ms, algorithmic_bpp, dram_bpp, dram_basis, peak, **extra):
+    gbs_dram = dram_bpp * params / ms / 1e6
+    d = {"name": name, "params": params, "ms": ms, "gparams_s": params / ms / 1e6,
+         "algorithmic_bytes": algorithmic_bpp * params, "dram_bytes": dram_bpp * params, "dram_basis": dram_basis,
+         "dram_gbs": gbs_dram, "frac": gbs_dram / peak}
+    d.update(extra)
+    return d
+
+
+def workload_mixed(gm, dev, torch, peak, reps):
+    """Mixed-precision Adam on 25,165,824 parameters in 48 ragged tensors packed back to back."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from workloads import ragged_sizes
+    L = gm.lib
+    sizes = ragged_sizes(48, 25_165_824, 4096, 4_194_304)
+    n = sum(sizes)
+    total = n + 32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 30)
+    g16 = (torch.empty(total, dtype=torch.float32, device="cuda").normal_(0.0, 1e-3 * 65536.0, generator=gen)).to(torch.float16)
+    w = torch.empty(total, dtype=torch.float32, device="cuda").uniform_(-0.05, 0.05, generator=gen)
+    m = torch.zeros(total, dtype=torch.float32, device="cuda")
+    v = torch.zeros(total, dtype=torch.float32, device="cuda")
+    p16 = w.to(torch.float16)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64) + 1     # tensor starts off the 16-byte boundary
+    eb = [2, 4, 4, 4, 2]
+    ptrs = [[a.data_ptr() + e * int(o) for o in offs] for a, e in zip((g16, w, m, v, p16), eb)]
+    lst = dev.tensor_list(ptrs, sizes, eb)
+    init = gm.LossScale(scale=65536.0, growth=2.0, backoff=0.5, max_scale=16777216.0, interval=1 << 30,
+                        good_steps=0, adam_t=0, skipped=0, last_overflow=0)    # the scale stays at 65536 while timing
+    mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
+    if not mx:
+        raise SystemExit("mixed state: " + gm.last_error())
+    torch.cuda.synchronize()
+    ms = _event_timed(gm, dev, lambda: gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed"), reps)
+    st = gm.LossScale()
+    gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(st)), "state")
+    L.gm_mixed_destroy(mx)
+    L.gm_tensor_list_destroy(lst)
+    del g16, w, m, v, p16
+    return _entry("mixed-precision Adam, 25,165,824 params in 48 ragged tensors (config 3)", n, ms, 30, 28,
+                  "28 B/param: fp16 gradients once (the update re-reads them from L2), master/m/v read and "
+                  "written, fp16 parameters written; ncu measured 705 MB per step = 28.0 B/param", peak,
+                  kernels="mixed_check_kernel + mixed_update_kernel", steps_timed=reps, clean_steps=int(st.adam_t),
+                  skipped_steps=int(st.skipped))
+
+
+def workload_lbfgs(gm, dev, torch, peak, reps):
+    """L-BFGS, n = 10,000,000, history 10: one iteration once the history is full."""
+    import numpy as np
+    L = gm.lib
+    n, m = 10_000_000, 10
+    z = lambda k: torch.zeros(k, dtype=torch.float32, device="cuda")
+    x, g, old, d = (z(n) for _ in range(4))
+    S, Y = [z(n) for _ in range(m)], [z(n) for _ in range(m)]
+    RHO, ALPHA = [z(64) for _ in range(m)], z(64)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 50)
+    D = torch.pow(10.0, torch.empty(n, dtype=torch.float32, device="cuda").uniform_(-0.3, 0.3, generator=gen))
+    b = torch.empty(n, dtype=torch.float32, device="cuda").normal_(0.0, 1.0, generator=gen)
+    P = lambda ts: gm.uarray([t.data_ptr() for t in ts])
+    hc = hi = 0
+    times = []
+    ms = C.c_float()
+    step = C.c_float()
+    for it in range(m + reps):
+        torch.mul(D, x, out=g)                                 # gradient of the quadratic, outside the timed part
+        g.sub_(b)
+        torch.cuda.synchronize()
+        gm.check(L.gm_timer_start(dev.h), "timer")
+        rc = L.execute_lbfgs_step_cuda(dev.h, P([x]), P([g]), P([old]), P([d]), P(S), P(Y), P(RHO), ALPHA.data_ptr(), 1,
+                                       gm.iarray([4 * n]), m, hc, hi, 1.0, 1e-4, 0.9, 20, 0.0, 0.0, C.byref(step))
+        gm.check(rc, "lbfgs")
+        gm.check(L.gm_timer_stop(dev.h, C.byref(ms)), "timer")
+        if hc == m:
+            times.append(ms.value)
+        hi, hc = (hi + 1) % m, min(hc + 1, m)
+    accepted = int(sum(1 for r in RHO if float(r[0]) != 0.0))
+    med = float(np.median(times))
+    del x, g, old, d, S, Y, RHO, ALPHA, D, b
+    # bytes that must cross DRAM with the direction vector kept on chip: g 4; each of the 2h loop passes reads
+    # two history vectors (8h + 8h); the final pass reads x, g, old_g, s_prev and writes x, old_g, s, y (32)
+    must = 4 + 16 * m + 32
+    return _entry("L-BFGS iteration, n = 10,000,000, history 10 full (config 5; working mode)", n, med, 44 + 32 * m, must,
+                  f"{must} B/element: what has to cross DRAM if the direction vector never left the chip "
+                  "(history vectors do not fit L2, so each is read once per loop); the kernels' own ncu "
+                  "DRAM traffic is 215 B/element", peak,
+                  kernels=f"{2 * m + 1} x lbfgs_axpy_dot_kernel + lbfgs_pass_kernel", iterations_timed=len(times),
+                  pairs_accepted=accepted, timing="CUDA events around the synchronous drop-in entry, median")
+
+
+def workload_rules(gm, dev, torch, peak, reps):
+    L = gm.lib
+    n, nt = 1 << 28, 64
+    per = n // nt
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 20)
+    bufs = {k: torch.zeros(n, dtype=torch.float32, device="cuda") for k in ("w", "g", "s1", "s2")}
+    bufs["g"].normal_(0.0, 0.01, generator=gen)
+    ptrs = {k: [a.data_ptr() + 4 * per * t for t in range(nt)] for k, a in bufs.items()}
+    rules = [
+        ("NAdam", gm.RULE_NADAM, ["w", "g", "s1", "s2"], 28, dict(lr=2e-3, beta1=0.9, beta2=0.999, eps=1e-8)),
+        ("AdaDelta", gm.RULE_ADADELTA, ["w", "g", "s1", "s2"], 28, dict(beta1=0.9, eps=1e-6)),
+        ("SGD with momentum", gm.RULE_SGD, ["w", "g", "s1"], 20, dict(lr=0.01, beta1=0.9)),
+        ("RMSProp", gm.RULE_RMSPROP, ["w", "g", "s1"], 20, dict(lr=0.01, beta1=0.99, eps=1e-8)),
+        ("AdaGrad", gm.RULE_ADAGRAD, ["w", "g", "s1"], 20, dict(lr=0.01, eps=1e-10)),
+    ]
+    out = []
+    for name, rule, streams, bpp, hp in rules:
+        bufs["w"].uniform_(-0.05, 0.05, generator=gen)         # one rule's state is not a valid state of the next
+        bufs["s1"].zero_()
+        bufs["s2"].zero_()
+        torch.cuda.synchronize()
+        lst = dev.tensor_list([ptrs[k] for k in streams], [per] * nt)
+        hy = gm.Hyper(step=1, **hp)
+        state = {"t": 0}
+
+        def one():
+            state["t"] += 1
+            hy.step = state["t"]
+            gm.check(L.gm_step_async(dev.h, rule, lst, C.byref(hy)), name)
+
+        ms = _event_timed(gm, dev, one, reps)
+        out.append(_entry(f"{name}, fp32, 2^28 params in 64 tensors", n, ms, bpp, bpp,
+                          "every stream is read once and every written stream written once", peak,
+                          kernels="mta_apply_kernel", steps_timed=reps))
+        L.gm_tensor_list_destroy(lst)
+    del bufs
+    return out
+
+
+def run_only(args):
+    """Profiler captures: one of the other configurations alone, a few repetitions, one JSON line."""
+    import torch
+    import gometal_cuda as gm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the optimizer step has no CPU path")
+    torch.cuda.set_device(0)
+    dev = gm.Device(0)
+    peak, _ = measured_peak_gbs()
+    fn = {"mixed": workload_mixed, "lbfgs": workload_lbfgs, "rules": workload_rules}[args.only]
+    out = fn(gm, dev, torch, peak, max(args.steps, 1))
+    dev.close()
+    print(json.dumps({"only": args.only, "result": out}))
+    return 0
+
+
+def run_workloads(gm, dev, torch, reps):
+    peak, peak_kind = measured_peak_gbs()
+    entries = [workload_mixed(gm, dev, torch, peak, max(reps, 20))]
+    torch.cuda.empty_cache()
+    entries.append(workload_lbfgs(gm, dev, torch, peak, max(reps // 2, 8)))
+    torch.cuda.empty_cache()
+    entries.extend(workload_rules(gm, dev, torch, peak, max(reps // 2, 10)))
+    torch.cuda.empty_cache()
+    return {"peak_gbs": peak, "peak_source": f"of {peak_kind}", "timing": "CUDA events on the launching stream, after warm-up; "
+            "every list is larger than the 126 MB L2", "entries": entries}
+
+
+# ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu(args):
+    import numpy as np
     import torch
     import gometal_cuda as gm
     L = gm.lib
@@ -233,6 +430,14 @@ def run_gpu(args):
     numel = [TENSOR_ELEMS] * per_rank_tensors
     lists = [dev.tensor_list([w_ptrs, gp, m_ptrs, v_ptrs], numel) for gp in g_ptrs]
 
+    # --- the sample the parity check follows: a stride over the whole arena plus both ends of every shard ---
+    edge = np.concatenate([np.arange(0, 64), np.arange(shard_elems - 64, shard_elems)])
+    idx_np = np.unique(np.concatenate([np.arange(0, TOTAL, 4099)] + [edge + r * shard_elems for r in range(world)])).astype(np.int64)
+    idx = torch.from_numpy(idx_np).cuda()
+    w0_sample = w_arena[idx].cpu().numpy()              # before any step
+    owner = idx_np // shard_elems
+    mine = torch.from_numpy(idx_np[owner == rank] - rank * shard_elems).cuda()
+
     zero1 = 0
     exchange = "none"
     if world > 1:
@@ -247,8 +452,8 @@ def run_gpu(args):
             raise SystemExit("ZeRO-1 group creation failed: " + gm.last_error())
         exchange = args.exchange
         if exchange in ("push", "dma"):
-            mine = (C.c_ubyte * 64)()
-            rc = L.gm_zero1_ipc_handle(zero1, w_arena.data_ptr(), mine)
+            mine_h = (C.c_ubyte * 64)()
+            rc = L.gm_zero1_ipc_handle(zero1, w_arena.data_ptr(), mine_h)
             # torch may have carved the arena out of a larger segment, which cannot be exported to
             # the peers; every rank then takes the NCCL all-gather instead
             ok = torch.tensor([1 if rc == 0 else 0], device="cuda")
@@ -258,7 +463,7 @@ def run_gpu(args):
                 if rank == 0:
                     print(f"peer mapping unavailable ({gm.last_error()}); using the NCCL all-gather", file=sys.stderr)
         if exchange in ("push", "dma"):
-            mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
+            mine_t = torch.tensor(list(bytes(mine_h)), dtype=torch.uint8, device="cuda")
             all_t = [torch.empty_like(mine_t) for _ in range(world)]
             dist.all_gather(all_t, mine_t)
             blob = bytes(b for tt in all_t for b in tt.cpu().tolist())
@@ -294,7 +499,8 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         one_step()
     barrier()
 
@@ -314,7 +520,36 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
     value = TOTAL / (ms_per_step * 1e-3) / 1e9
 
-    # update-only timing at N > 1 (the part the HBM roofline applies to)
+    # --- parity: the sampled elements of the WHOLE arena on every rank against the oracle, outside the timed region ---
+    parity = None
+    if not args.no_parity_check:
+        from oracle import oracle as O
+        steps_done = step_no[0]
+        g_samples = []
+        for gset in grads:                                      # every rank contributes the samples it owns (exact: int32 sum with zeros)
+            buf = torch.zeros(idx.numel(), dtype=torch.int32, device="cuda")
+            buf[torch.from_numpy(np.nonzero(owner == rank)[0]).cuda()] = gset[mine].view(torch.int32)
+            if dist is not None:
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM)
+            g_samples.append(buf.view(torch.float32).cpu().numpy())
+        ws, ms_o, vs_o = w0_sample.copy(), np.zeros_like(w0_sample), np.zeros_like(w0_sample)
+        for s in range(1, steps_done + 1):
+            O.adam_step(ws, g_samples[s % 2], ms_o, vs_o, LR, B1, B2, EPS, WD, s)
+        got_w = w_arena[idx].cpu().numpy()
+        sel = owner == rank
+        ok_w = bool(np.array_equal(got_w.view(np.uint32), ws.view(np.uint32)))
+        ok_m = bool(np.array_equal(m_arena[mine].cpu().numpy().view(np.uint32), ms_o[sel].view(np.uint32)))
+        ok_v = bool(np.array_equal(v_arena[mine].cpu().numpy().view(np.uint32), vs_o[sel].view(np.uint32)))
+        flag = torch.tensor([1 if (ok_w and ok_m and ok_v) else 0], device="cuda")
+        if dist is not None:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = {"ranks": world, "sampled": int(idx.numel()), "steps_replayed": steps_done, "ok": bool(int(flag.item()) == 1),
+                  "what": "bit equality of the sampled parameters of the whole arena on every rank (and of the "
+                          "owner's m and v) with the CPU oracle replayed over the same steps"}
+        if not parity["ok"] and rank == 0:
+            print("PARITY CHECK FAILED", file=sys.stderr)
+
+    # --- update-only timing at N > 1 (the part the HBM roofline applies to) ---
     update_ms = ms_per_step
     if world > 1:
         gm.check(L.gm_timer_start(dev.h), "timer")
@@ -328,112 +563,167 @@ def run_gpu(args):
 
     peak, peak_kind = measured_peak_gbs()
     achieved = BYTES_PER_PARAM * shard_elems / (update_ms * 1e-3) / 1e9
+    rec = ncu_traffic_record()
+    traffic = None
+    if rec is not None:
+        traffic = rec["dram_bytes_per_param"] * shard_elems
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH * shard_elems / (256 * TENSOR_ELEMS), "peak_source": f"of {peak_kind}",
+                "traffic": traffic, "traffic_source": (rec or {}).get("source"), "peak_source": f"of {peak_kind}",
                 "kernel": "mta_apply_kernel<AdamRule>", "algorithmic_bytes_per_launch": BYTES_PER_PARAM * shard_elems,
                 "kernel_ms": update_ms, "frac_of_8TBs_nominal": achieved / 8000.0}
 
-    # --- end to end: host buffers through the drop-in entry ---
-    if args.skip_e2e:
-        return _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks,
-                       launches, roofline, None, exchange, shard_elems)
-    e2e_steps = min(args.steps, 3)
-    host_g = torch.empty(shard_elems, dtype=torch.float32).pin_memory()
-    host_g.copy_(grads[0].cpu())
-    host_w = torch.empty(shard_elems, dtype=torch.float32).pin_memory()
-    sizes = gm.iarray([4 * TENSOR_ELEMS] * per_rank_tensors)
-    arr = {k: gm.uarray(p) for k, p in (("w", w_ptrs), ("g", g_ptrs[0]), ("m", m_ptrs), ("v", v_ptrs))}
-    shard_bytes = 4 * shard_elems
-    w_shard_ptr = w_arena.data_ptr() + 4 * first * TENSOR_ELEMS
+    scaling_detail = None
+    if world > 1:
+        # the same update on the whole workload on one GPU, measured here so that the efficiency of the update
+        # phase needs no number from another run
+        full_ms = None
+        if not args.no_full_update:
+            gf = torch.empty(TOTAL, dtype=torch.float32, device="cuda").normal_(0.0, 0.01, generator=gen)
+            mf = torch.zeros(TOTAL, dtype=torch.float32, device="cuda")
+            vf = torch.zeros(TOTAL, dtype=torch.float32, device="cuda")
+            wf = torch.empty(TOTAL, dtype=torch.float32, device="cuda").uniform_(-lim, lim, generator=gen)
+            ptr_all = lambda a: [a.data_ptr() + 4 * t * TENSOR_ELEMS for t in range(NUM_TENSORS)]
+            lf = dev.tensor_list([ptr_all(wf), ptr_all(gf), ptr_all(mf), ptr_all(vf)], [TENSOR_ELEMS] * NUM_TENSORS)
+            hf = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=0)
+            cnt = [0]
 
-    def e2e_step_dropin():
-        # upload, synchronous drop-in entry, download: nothing overlaps
-        step_no[0] += 1
-        gm.check(L.gm_buffer_upload_async(dev.h, grads[0].data_ptr(), host_g.data_ptr(), shard_bytes), "h2d")
-        rc = L.execute_adam_step_cuda(dev.h, arr["w"], arr["g"], arr["m"], arr["v"], per_rank_tensors, sizes,
-                                      LR, B1, B2, EPS, WD, step_no[0])
-        gm.check(rc, "execute_adam_step_cuda")
-        if world > 1:
-            gm.check(L.gm_zero1_allgather_async(zero1, w_arena.data_ptr(), shard_elems, 4), "all-gather")
-        gm.check(L.gm_buffer_download_async(dev.h, w_shard_ptr, host_w.data_ptr(), shard_bytes), "d2h")
-        dev.sync()
+            def full_step():
+                cnt[0] += 1
+                hf.step = cnt[0]
+                gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lf, C.byref(hf)), "adam step")
 
-    def e2e_step_host():
-        # the host-buffer entry: upload, update and download pipelined slice by slice
-        step_no[0] += 1
-        hyper.step = step_no[0]
-        gm.check(L.gm_step_host(dev.h, gm.RULE_ADAM, lists[0], C.byref(hyper), host_g.data_ptr(), host_w.data_ptr(),
-                                args.host_slices), "gm_step_host")
-        if world > 1:
-            gm.check(L.gm_zero1_allgather_async(zero1, w_arena.data_ptr(), shard_elems, 4), "all-gather")
+            full_ms = max_over_ranks(_event_timed(gm, dev, full_step, 5))
+            L.gm_tensor_list_destroy(lf)
+            del gf, mf, vf, wf
+            torch.cuda.empty_cache()
+            barrier()
+        bytes_in = 4 * (TOTAL - shard_elems)
+        gbs_in = bytes_in / (ms_per_step * 1e-3) / 1e9
+        scaling_detail = {
+            "exchange": exchange,
+            "update_only_ms_per_step": update_ms,
+            "one_gpu_update_ms_measured_here": full_ms,
+            "update_phase_efficiency": (full_ms / (world * update_ms)) if full_ms else None,
+            "exchange_bytes_in_per_gpu": bytes_in,
+            "exchange_gbs_in_per_gpu": gbs_in,
+            "exchange_frac_of_900_nominal": gbs_in / NVLINK_NOMINAL_GBS,
+            "exchange_frac_of_770_measured_peer_copy": gbs_in / NVLINK_MEASURED_GBS,
+            "exchange_floor_ms_at_770": bytes_in / NVLINK_MEASURED_GBS / 1e6,
+            "bound": "NVLink ingress: every GPU must receive 4*(N-1)/N bytes per parameter",
+        }
+
+    # --- end to end: host buffers through the host-buffer entries ---
+    e2e = None
+    if not args.skip_e2e:
+        e2e_steps = max(10, min(args.steps, 20))
+        host_g = torch.empty(shard_elems, dtype=torch.float32).pin_memory()
+        host_g.copy_(grads[0].cpu())
+        host_w = torch.empty(shard_elems, dtype=torch.float32).pin_memory()
+        sizes = gm.iarray([4 * TENSOR_ELEMS] * per_rank_tensors)
+        arr = {k: gm.uarray(p) for k, p in (("w", w_ptrs), ("g", g_ptrs[0]), ("m", m_ptrs), ("v", v_ptrs))}
+        shard_bytes = 4 * shard_elems
+        w_shard_ptr = w_arena.data_ptr() + 4 * first * TENSOR_ELEMS
+        use_push_host = world > 1 and exchange == "push"
+
+        def e2e_step_dropin():
+            # upload, synchronous drop-in entry, download: nothing overlaps
+            step_no[0] += 1
+            gm.check(L.gm_buffer_upload_async(dev.h, grads[0].data_ptr(), host_g.data_ptr(), shard_bytes), "h2d")
+            rc = L.execute_adam_step_cuda(dev.h, arr["w"], arr["g"], arr["m"], arr["v"], per_rank_tensors, sizes,
+                                          LR, B1, B2, EPS, WD, step_no[0])
+            gm.check(rc, "execute_adam_step_cuda")
+            if world > 1:
+                gm.check(L.gm_zero1_allgather_async(zero1, w_arena.data_ptr(), shard_elems, 4), "all-gather")
+            gm.check(L.gm_buffer_download_async(dev.h, w_shard_ptr, host_w.data_ptr(), shard_bytes), "d2h")
             dev.sync()
 
-    def time_e2e(fn):
-        fn()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
+        def e2e_step_host():
+            # the host-buffer entry: upload, update (and exchange) and download pipelined slice by slice
+            step_no[0] += 1
+            hyper.step = step_no[0]
+            if use_push_host:
+                gm.check(L.gm_zero1_adam_push_step_host(zero1, lists[0], C.byref(hyper), host_g.data_ptr(), host_w.data_ptr(),
+                                                        args.host_slices), "gm_zero1_adam_push_step_host")
+                return
+            gm.check(L.gm_step_host(dev.h, gm.RULE_ADAM, lists[0], C.byref(hyper), host_g.data_ptr(), host_w.data_ptr(),
+                                    args.host_slices), "gm_step_host")
+            if world > 1:
+                gm.check(L.gm_zero1_allgather_async(zero1, w_arena.data_ptr(), shard_elems, 4), "all-gather")
+                dev.sync()
+
+        def time_e2e(fn, steps):
             fn()
-        dt = max_over_ranks(time.perf_counter() - t0)
-        barrier()
-        return dt
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                fn()
+            dt = max_over_ranks(time.perf_counter() - t0)
+            barrier()
+            return dt / steps
 
-    # the floor of any host-buffer step: the same two copies, both directions at once, no kernel
-    up, down = torch.cuda.Stream(), torch.cuda.Stream()
-    g_dev = grads[0][:shard_elems]
-    w_dev = w_arena[first * TENSOR_ELEMS: first * TENSOR_ELEMS + shard_elems]
-    scratch_w = torch.empty_like(host_w).pin_memory()
+        # the floor of any host-buffer step: the same two copies, both directions at once, no kernel
+        up, down = torch.cuda.Stream(), torch.cuda.Stream()
+        g_dev = grads[0][:shard_elems]
+        w_dev = w_arena[first * TENSOR_ELEMS: first * TENSOR_ELEMS + shard_elems]
+        scratch_w = torch.empty_like(host_w).pin_memory()
 
-    def copies_only():
-        with torch.cuda.stream(up):
-            g_dev.copy_(host_g, non_blocking=True)
-        with torch.cuda.stream(down):
-            scratch_w.copy_(w_dev, non_blocking=True)
-        torch.cuda.synchronize()
+        def copies_only():
+            with torch.cuda.stream(up):
+                g_dev.copy_(host_g, non_blocking=True)
+            with torch.cuda.stream(down):
+                scratch_w.copy_(w_dev, non_blocking=True)
+            torch.cuda.synchronize()
 
-    dropin_s = time_e2e(e2e_step_dropin)
-    e2e_s = time_e2e(e2e_step_host)
-    copy_s = time_e2e(copies_only)
-    del scratch_w
-    e2e = {"value": TOTAL * e2e_steps / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": shard_bytes,
-           "d2h_bytes_per_step": shard_bytes, "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
-           "api": f"gm_step_host (pinned host gradients in, updated parameters out, {args.host_slices} pipelined slices)",
-           "copy_floor": {"ms_per_step": copy_s / e2e_steps * 1e3,
-                          "note": "the step's two host<->device copies alone, concurrent, no kernel"},
-           "unpipelined": {"value": TOTAL * e2e_steps / dropin_s / 1e9, "ms_per_step": dropin_s / e2e_steps * 1e3,
-                           "api": "upload + execute_adam_step_cuda (synchronous drop-in entry) + download"}}
+        dropin_s = time_e2e(e2e_step_dropin, 3)
+        e2e_s = time_e2e(e2e_step_host, e2e_steps)
+        copy_s = time_e2e(copies_only, 5)
+        del scratch_w
+        api = ("gm_zero1_adam_push_step_host" if use_push_host else "gm_step_host" + (" + NCCL all-gather" if world > 1 else ""))
+        e2e = {"value": TOTAL / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": shard_bytes,
+               "d2h_bytes_per_step": shard_bytes, "steps": e2e_steps, "ms_per_step": e2e_s * 1e3,
+               "api": f"{api} (pinned host gradients in, updated parameters out, {args.host_slices} pipelined slices)",
+               "copy_floor": {"ms_per_step": copy_s * 1e3,
+                              "note": "the step's two host<->device copies alone, concurrent, no kernel; at N > 1 all "
+                                      "ranks share the box's host<->device bandwidth, which is what bounds this leg"},
+               "unpipelined": {"value": TOTAL / dropin_s / 1e9, "ms_per_step": dropin_s * 1e3, "steps": 3,
+                               "api": "upload + execute_adam_step_cuda (synchronous drop-in entry) + download"}}
 
-    return _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks,
-                   launches, roofline, e2e, exchange, shard_elems)
+    for lst in lists:
+        L.gm_tensor_list_destroy(lst)
+    lists = []
+    del grads, m_arena, v_arena, w_arena
+    torch.cuda.empty_cache()
 
+    workloads = None
+    if world == 1 and not args.no_workloads and NUM_TENSORS == 256:
+        workloads = run_workloads(gm, dev, torch, args.steps)
 
-def _finish(args, gm, L, dev, dist, lists, zero1, rank, world, value, ms_per_step, update_ms, clocks, launches,
-            roofline, e2e, exchange, shard_elems):
     line = None
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            rate, cores, done, per = cpu_adam_rate(50, 1, 1 << 26, 12.0)
-            cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"{done} Adam steps over a {1 << 26}-parameter slice of the workload, "
-                             "pthread split over all host cores"}
+            rate, cores, done, per = cpu_adam_rate(50, 1, CPU_SAMPLE, 12.0)
+            cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(done)}
+        cfg = dict(CONFIG)
+        if NUM_TENSORS != 256:
+            cfg["workload"] = f"REDUCED for profiling: {NUM_TENSORS} tensors"
+            cfg["params"], cfg["tensors"] = TOTAL, NUM_TENSORS
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD if NUM_TENSORS == 256 else f"REDUCED for profiling: {NUM_TENSORS} tensors",
-                       "params": TOTAL, "tensors": NUM_TENSORS,
-                       "parallelism": f"zero1x{world}", "exchange": exchange,
-                       "l2": "inputs (>= 2 GiB per rank) far exceed the 126 MB L2; no flush needed",
-                       "hbm_gbs_algorithmic": BYTES_PER_PARAM * TOTAL / (ms_per_step * 1e-3) / 1e9},
+            "config": cfg,
+            "details": {"parallelism": f"zero1x{world}", "exchange": exchange,
+                        "l2": "inputs (>= 2 GiB per rank) far exceed the 126 MB L2; no flush needed",
+                        "hbm_gbs_algorithmic": BYTES_PER_PARAM * TOTAL / (ms_per_step * 1e-3) / 1e9},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-            "cpu_baseline": cpu,
+            "parity_check": parity, "cpu_baseline": cpu,
         }
-        if world > 1:
+        if scaling_detail is not None:
+            line["zero1"] = scaling_detail
             line["update_only_ms_per_step"] = update_ms
-            line["exchange_bytes_in_per_gpu"] = 4 * (TOTAL - shard_elems)
-    for lst in lists:
-        L.gm_tensor_list_destroy(lst)
+        if workloads is not None:
+            line["workloads"] = workloads
     if zero1:
         L.gm_zero1_destroy(zero1)
     dev.close()
@@ -455,12 +745,19 @@ def main():
     ap.add_argument("--slices", type=int, default=8, help="slices of the shard for --exchange dma")
     ap.add_argument("--host-slices", type=int, default=64, help="pipeline depth of the host-buffer step (e2e)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="leave out the block of other configurations (N = 1)")
+    ap.add_argument("--no-parity-check", action="store_true")
+    ap.add_argument("--no-full-update", action="store_true", help="N > 1: skip the one-GPU update timing behind update_phase_efficiency")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,
                     help="profiling runs only: fewer 4 Mi tensors than the 256 of the workload")
+    ap.add_argument("--only", choices=["mixed", "lbfgs", "rules"],
+                    help="profiling runs only: time one of the other configurations alone for --steps repetitions")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.only:
+        return run_only(args)
     return run_gpu(args)
 
 

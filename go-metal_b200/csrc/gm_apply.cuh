@@ -198,7 +198,7 @@ mta_apply_kernel(const DevList L, const typename Rule::P prm) {
 }
 
 template <class Rule>
-int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm) {
+int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm, Window win = Window()) {
     if (l->dl.num_streams != Rule::NS) {
         set_error("tensor list has %d streams, rule needs %d", l->dl.num_streams, Rule::NS);
         return GM_ERR_BAD_ARG;
@@ -207,12 +207,11 @@ int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm) {
         if (l->elem_bytes[s] != 4) { set_error("stream %d is not fp32", s); return GM_ERR_BAD_ARG; }
     }
     auto kernel = mta_apply_kernel<Rule>;
-    DevList dl = l->dl;
-    if (l->win_count >= 0) {                     // a slice of the list: chunks [win_begin, win_begin + win_count)
-        if (l->win_begin < 0 || l->win_begin + l->win_count > dl.num_chunks) { set_error("launch window outside the list"); return GM_ERR_BAD_ARG; }
-        if (l->win_count == 0) return GM_OK;
-        dl.chunk_rec += l->win_begin;
-        dl.num_chunks = l->win_count;
+    DevList dl;
+    {
+        const int rc = apply_window(l, win, &dl);
+        if (rc != GM_OK) return rc;
+        if (dl.num_chunks == 0) return GM_OK;
     }
     int grid = launch_grid(d, (const void*)kernel, kApplyThreads, dl.num_chunks);
     kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, prm);

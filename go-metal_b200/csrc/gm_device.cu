@@ -11,6 +11,8 @@
 #include <string.h>
 
 #include <atomic>
+#include <chrono>
+#include <thread>
 
 #include <set>
 
@@ -385,12 +387,15 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     }
     if (cache) {
         std::lock_guard<std::mutex> lk(d->mu);
-        if (d->list_cache.size() >= 64) {       // bounded: drop everything, rebuild on demand
-            std::vector<TensorList*> old;
-            for (auto& kv : d->list_cache) old.push_back(kv.second);
-            d->list_cache.clear();
+        if (d->list_cache.size() >= 64) {
+            // Bounded: forget everything, rebuild on demand.  The forgotten lists are parked, not
+            // freed: a caller may still hold one between its lookup and its launch.  What the
+            // eviction before this one parked is freed now, once the stream has drained.
             cudaStreamSynchronize(d->stream);
-            for (TensorList* o : old) free_list(o);
+            for (TensorList* o : d->retired_lists) free_list(o);
+            d->retired_lists.clear();
+            for (auto& kv : d->list_cache) d->retired_lists.push_back(kv.second);
+            d->list_cache.clear();
         }
         l->key = key;
         auto prev = d->list_cache.find(key);
@@ -495,6 +500,8 @@ void destroy_cuda_device(uintptr_t h) {
     d->list_cache.clear();
     for (TensorList* l : d->parked_lists) lists.push_back(l);
     d->parked_lists.clear();
+    for (TensorList* l : d->retired_lists) lists.push_back(l);
+    d->retired_lists.clear();
     for (TensorList* l : lists) free_list(l);
     lbfgs_release_device(d);
     if (d->partials) cudaFree(d->partials);
@@ -527,6 +534,28 @@ int gm_device_synchronize(uintptr_t h) {
     DeviceGuard g(d);
     GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
     return GM_OK;
+}
+
+// Waits for the device's stream, but no longer than timeout_ms: polls the stream instead
+// of blocking in the driver, so a step that never completes (a peer that never entered
+// its collective) gives the caller GM_ERR_TIMEOUT and the choice of what to do next.
+int gm_device_synchronize_timeout(uintptr_t h, int timeout_ms) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (timeout_ms < 0) { set_error("timeout %d ms is negative", timeout_ms); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    unsigned spins = 0;
+    for (;;) {
+        const cudaError_t e = cudaStreamQuery(d->stream);
+        if (e == cudaSuccess) return GM_OK;
+        if (e != cudaErrorNotReady) return cuda_fail(e, "cudaStreamQuery");
+        if (std::chrono::steady_clock::now() >= deadline) {
+            set_error("the device stream did not drain within %d ms", timeout_ms);
+            return GM_ERR_TIMEOUT;
+        }
+        if (++spins > 200) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
 }
 
 int gm_timer_start(uintptr_t h) {

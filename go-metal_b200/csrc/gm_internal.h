@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <functional>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -47,8 +48,12 @@ struct TensorList {
     uint64_t key = 0;                 // cache key (0 = not cached)
     std::vector<int> chunk_prefix;    // host copy: first chunk of each tensor, [num_tensors+1]
     uint64_t validated_gen = 0;       // registry generation under which the buffers were last checked
-    int win_begin = 0, win_count = -1; // launch window in chunks (count < 0: the whole list)
 };
+
+// A launch may cover only chunks [begin, begin + count) of a list (a slice of whole
+// tensors in the pipelined entries); count < 0 means the whole list.  Passed by value:
+// the list itself is never modified by a launch.
+struct Window { int begin = 0; int count = -1; };
 
 struct Device {
     int magic = kMagicDevice;
@@ -61,6 +66,7 @@ struct Device {
     std::mutex mu;
     std::unordered_map<uint64_t, TensorList*> list_cache;
     std::vector<TensorList*> parked_lists;   // displaced from the cache while possibly still in use
+    std::vector<TensorList*> retired_lists;  // the cache's content at its last eviction; freed at the next one
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
@@ -122,7 +128,13 @@ int ensure_partials(Device* d, int64_t count);
 
 // ---- rule launchers (gm_rules.cu) ----
 void lbfgs_release_device(Device* d);           // frees the L-BFGS pointer tables cached for a device
-int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h);
+int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win = Window());
+// Applies a window to a list's descriptor; GM_ERR_BAD_ARG when it lies outside the list.
+int apply_window(const TensorList* l, Window win, DevList* out);
+
+// Host-buffer pipeline shared by gm_step_host and the sharded host step (gm_rules.cu).
+int host_pipelined_step(Device* d, const TensorList* l, const void* host_grads, void* host_params, int num_slices,
+                        const std::function<int(Window)>& launch, const std::function<int()>& finish);
 
 // ---- mixed precision (gm_mixed.cu) ----
 int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd,

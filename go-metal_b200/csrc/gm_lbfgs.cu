@@ -387,6 +387,7 @@ struct LbfgsCtx {
 
 static std::mutex g_lb_mu;
 static std::map<Device*, std::vector<LbfgsCtx*>> g_lb;
+static std::map<Device*, LbfgsCtx*> g_lb_parked;   // the table evicted last, per device
 
 static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* s_flat, uintptr_t* y_flat,
                    const int64_t* numel, LbfgsCtx** out) {
@@ -446,10 +447,13 @@ static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* 
     if (rc != GM_OK) { cudaFree(c->blob); delete c; return rc; }
     std::lock_guard<std::mutex> lk(g_lb_mu);
     auto& v = g_lb[d];
-    if (v.size() >= 8) {                      // bounded: forget the oldest table
+    if (v.size() >= 8) {
+        // Bounded: forget the oldest table.  It is parked until the next eviction rather than
+        // freed at once, because a caller may hold it between its lookup and its launches.
         cudaStreamSynchronize(d->stream);
-        cudaFree(v.front()->blob);
-        delete v.front();
+        LbfgsCtx*& parked = g_lb_parked[d];
+        if (parked) { cudaFree(parked->blob); delete parked; }
+        parked = v.front();
         v.erase(v.begin());
     }
     v.push_back(c);
@@ -475,6 +479,11 @@ static int axpy_grid(Device* d, int num_chunks) {
 // Called when a device handle is destroyed: its pointer tables go with it.
 void lbfgs_release_device(Device* d) {
     std::lock_guard<std::mutex> lk(g_lb_mu);
+    auto pk = g_lb_parked.find(d);
+    if (pk != g_lb_parked.end()) {
+        if (pk->second) { cudaFree(pk->second->blob); delete pk->second; }
+        g_lb_parked.erase(pk);
+    }
     auto it = g_lb.find(d);
     if (it == g_lb.end()) return;
     for (LbfgsCtx* c : it->second) { cudaFree(c->blob); delete c; }

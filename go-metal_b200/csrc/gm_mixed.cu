@@ -72,6 +72,23 @@ static int upload_table(Mixed* m, int len) {
     return GM_OK;
 }
 
+// The device counter can be at most `calls` before the next step; the table must reach
+// calls + 1 unless its tail is already constant.  Doubles until it does.
+static int grow_table(Mixed* m) {
+    while (!m->saturated && m->calls + 1 > m->table_len) {
+        if (m->table_len > (1 << 28)) { set_error("bias-correction table would exceed 2^29 entries"); return GM_ERR_BAD_SIZE; }
+        const int rc = upload_table(m, m->table_len * 2);
+        if (rc != GM_OK) return rc;
+    }
+    return GM_OK;
+}
+
+static bool valid_loss_scale(const gm_loss_scale_t& s) {
+    return s.scale > 0.0f && isfinite(s.scale) && s.growth >= 1.0f && isfinite(s.growth) && s.backoff > 0.0f
+           && s.backoff <= 1.0f && s.interval >= 1 && s.max_scale >= s.scale && isfinite(s.max_scale)
+           && s.adam_t >= 0 && s.good_steps >= 0 && s.skipped >= 0;
+}
+
 // 1 bits at 0x8000 / 0x80000000 mark halves whose exponent field is all ones.
 __device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
     return ((w & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
@@ -525,8 +542,8 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     }
     // The device counter can be at most `calls` before this step; make sure the
     // table reaches calls+1 unless its tail is already constant.
-    if (!m->saturated && m->calls + 1 > m->table_len) {
-        int rc = upload_table(m, m->table_len * 2);
+    {
+        const int rc = grow_table(m);
         if (rc != GM_OK) return rc;
     }
     m->calls += 1;
@@ -589,8 +606,7 @@ uintptr_t gm_mixed_create(uintptr_t device_ptr, const gm_loss_scale_t* initial, 
         init.scale = 65536.0f; init.growth = 2.0f; init.backoff = 0.5f; init.max_scale = 16777216.0f;
         init.interval = 2000; init.good_steps = 0; init.adam_t = 0; init.skipped = 0; init.last_overflow = 0;
     }
-    if (!(init.scale > 0.0f) || !(init.growth >= 1.0f) || !(init.backoff > 0.0f && init.backoff <= 1.0f)
-        || init.interval < 1 || !(init.max_scale >= init.scale)) {
+    if (!valid_loss_scale(init)) {
         set_error("invalid loss-scale configuration (scale %g growth %g backoff %g interval %d max %g)",
                   (double)init.scale, (double)init.growth, (double)init.backoff, init.interval, (double)init.max_scale);
         return 0;
@@ -607,7 +623,7 @@ uintptr_t gm_mixed_create(uintptr_t device_ptr, const gm_loss_scale_t* initial, 
     if (e == cudaSuccess) e = cudaMalloc((void**)&m->d_flag, 256);
     if (e == cudaSuccess) e = cudaMemset(m->d_flag, 0, 256);
     if (e == cudaSuccess) e = cudaMemcpy(m->d_state, &init, sizeof(init), cudaMemcpyHostToDevice);
-    if (e != cudaSuccess || upload_table(m, table_steps > 0 ? table_steps : 32768) != GM_OK) {
+    if (e != cudaSuccess || upload_table(m, table_steps > 0 ? table_steps : 32768) != GM_OK || grow_table(m) != GM_OK) {
         if (e != cudaSuccess) cuda_fail(e, "mixed state allocation");
         if (m->d_state) cudaFree(m->d_state);
         if (m->d_flag) cudaFree(m->d_flag);
@@ -653,16 +669,16 @@ int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scal
     if (!d) return GM_ERR_NIL_DEVICE;
     Mixed* m = as_mixed(mixed);
     if (!m || !in) { if (m) set_error("input is nil"); return GM_ERR_BAD_ARG; }
-    if (!(in->scale > 0.0f) || in->interval < 1 || in->adam_t < 0) { set_error("invalid loss-scale state"); return GM_ERR_BAD_ARG; }
+    if (!valid_loss_scale(*in)) {
+        set_error("invalid loss-scale state (scale %g growth %g backoff %g interval %d max %g step %d)", (double)in->scale,
+                  (double)in->growth, (double)in->backoff, in->interval, (double)in->max_scale, in->adam_t);
+        return GM_ERR_BAD_ARG;
+    }
     DeviceGuard g(d);
     GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
     GM_CUDA_CHECK(cudaMemcpy(m->d_state, in, sizeof(*in), cudaMemcpyHostToDevice));
     m->calls = in->adam_t;
-    while (!m->saturated && m->calls + 1 > m->table_len) {
-        int rc = upload_table(m, m->table_len * 2);
-        if (rc != GM_OK) return rc;
-    }
-    return GM_OK;
+    return grow_table(m);
 }
 
 int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable) {

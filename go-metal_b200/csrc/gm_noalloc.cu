@@ -121,7 +121,11 @@ extern "C" {
 // array and it keeps the previous call's chunk sums: the ticket word is cleared
 // on the stream before every launch, and two calls whose kernels can overlap on
 // the GPU (different streams, no ordering between them) race on it -- order
-// them.  No cudaMalloc, cudaFree or other allocating routine is called.
+// them.  No cudaMalloc, cudaFree or other allocating routine is called; the one
+// thing that can still reserve device memory is CUDA itself, which on the first
+// call per device may load this library's code onto the GPU and, with it, place
+// the built-in array (lazy module loading).  The looked-up address is cached per
+// process and device ordinal and does not survive a cudaDeviceReset.
 int gm_dot_canonical_static(uintptr_t a, uintptr_t b, int64_t n, uintptr_t out, uintptr_t stream) {
     if (!a || !b || !out) { set_error("gm_dot_canonical_static: a, b and out must be device pointers"); return GM_ERR_NIL_BUFFER; }
     if (n <= 0) { set_error("gm_dot_canonical_static: length %lld is not positive", (long long)n); return GM_ERR_BAD_SIZE; }

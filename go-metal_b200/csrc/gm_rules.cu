@@ -134,7 +134,16 @@ struct AdaDeltaRule {
     }
 };
 
-int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
+int apply_window(const TensorList* l, Window win, DevList* out) {
+    *out = l->dl;
+    if (win.count < 0) return GM_OK;
+    if (win.begin < 0 || win.begin + win.count > l->dl.num_chunks) { set_error("launch window outside the list"); return GM_ERR_BAD_ARG; }
+    out->chunk_rec += win.begin;
+    out->num_chunks = win.count;
+    return GM_OK;
+}
+
+int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win) {
     DeviceGuard guard(d);
     const int use_wd = h.weight_decay > 0.0f ? 1 : 0;
     switch (rule) {
@@ -146,7 +155,7 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.bc2 = 1.0f - powf(h.beta2, (float)h.step);
             p.omb1 = 1.0f - h.beta1;
             p.omb2 = 1.0f - h.beta2;
-            return launch_apply<AdamRule>(d, l, p);
+            return launch_apply<AdamRule>(d, l, p, win);
         }
         case GM_RULE_NADAM: {
             if (h.step < 1) { set_error("NAdam step count %d must be >= 1", h.step); return GM_ERR_BAD_ARG; }
@@ -158,13 +167,13 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.omb2 = 1.0f - h.beta2;
             p.mu_next = h.beta1 * (1.0f - 0.5f * powf(0.96f, (float)(h.step + 1) * 0.004f));
             p.om_mu = 1.0f - p.mu_next;
-            return launch_apply<NadamRule>(d, l, p);
+            return launch_apply<NadamRule>(d, l, p, win);
         }
         case GM_RULE_SGD: {
             SgdScalars p;
             p.lr = h.lr; p.momentum = h.beta1; p.wd = h.weight_decay; p.use_wd = use_wd; p.nesterov = h.nesterov ? 1 : 0;
-            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule>(d, l, p);
-            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule>(d, l, p);
+            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule>(d, l, p, win);
+            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule>(d, l, p, win);
             set_error("SGD needs streams w,g (momentum==0) or w,g,mom (momentum>0); got %d streams, momentum %g",
                       l->dl.num_streams, (double)h.beta1);
             return GM_ERR_BAD_ARG;
@@ -174,20 +183,20 @@ int launch_rule(Device* d, int rule, TensorList* l, const gm_hyper_t& h) {
             p.lr = h.lr; p.alpha = h.beta1; p.oma = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay;
             p.momentum = h.momentum; p.use_wd = use_wd;
             const bool mom = h.momentum > 0.0f, cen = h.centered != 0;
-            if (mom && cen) return launch_apply<RmsPropRule<true, true>>(d, l, p);
-            if (mom) return launch_apply<RmsPropRule<true, false>>(d, l, p);
-            if (cen) return launch_apply<RmsPropRule<false, true>>(d, l, p);
-            return launch_apply<RmsPropRule<false, false>>(d, l, p);
+            if (mom && cen) return launch_apply<RmsPropRule<true, true>>(d, l, p, win);
+            if (mom) return launch_apply<RmsPropRule<true, false>>(d, l, p, win);
+            if (cen) return launch_apply<RmsPropRule<false, true>>(d, l, p, win);
+            return launch_apply<RmsPropRule<false, false>>(d, l, p, win);
         }
         case GM_RULE_ADAGRAD: {
             AdaGradRule::P p;
             p.lr = h.lr; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaGradRule>(d, l, p);
+            return launch_apply<AdaGradRule>(d, l, p, win);
         }
         case GM_RULE_ADADELTA: {
             AdaDeltaRule::P p;
             p.rho = h.beta1; p.omr = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaDeltaRule>(d, l, p);
+            return launch_apply<AdaDeltaRule>(d, l, p, win);
         }
         default:
             set_error("unknown rule %d", rule);
@@ -224,59 +233,19 @@ static int dropin_step(uintptr_t device_ptr, int rule, int num_streams, uintptr_
     return GM_OK;
 }
 
-}  // namespace gm
-
-using namespace gm;
-
-extern "C" {
-
-int gm_step_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper) {
-    Device* d = as_device(device_ptr);
-    if (!d) return GM_ERR_NIL_DEVICE;
-    TensorList* l = as_list(list);
-    if (!l) return GM_ERR_BAD_ARG;
-    if (!hyper) { set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
-    if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
-    return launch_rule(d, rule, l, *hyper);
-}
-
-int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, float* elapsed_ms) {
-    Device* d = as_device(device_ptr);
-    if (!d) return GM_ERR_NIL_DEVICE;
-    TensorList* l = as_list(list);
-    if (!l) return GM_ERR_BAD_ARG;
-    if (!hyper || !elapsed_ms) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
-    DeviceGuard guard(d);
-    GM_CUDA_CHECK(cudaEventRecord(d->ev_start, d->stream));
-    int rc = launch_rule(d, rule, l, *hyper);
-    if (rc != GM_OK) return rc;
-    GM_CUDA_CHECK(cudaEventRecord(d->ev_stop, d->stream));
-    GM_CUDA_CHECK(cudaEventSynchronize(d->ev_stop));
-    GM_CUDA_CHECK(cudaEventElapsedTime(elapsed_ms, d->ev_start, d->ev_stop));
-    return GM_OK;
-}
-
-// One optimizer step for a caller whose gradients and parameters live in HOST
-// memory (pinned): the list is cut into `num_slices` groups of whole tensors and
-// the three stages of each slice -- gradients host->device, update kernel,
-// parameters device->host -- run on three streams, so the upload of slice s+1
-// and the download of slice s-1 overlap the update of slice s and both PCIe
-// directions are busy at once.  host_grads / host_params hold the tensors back
-// to back in list order; the device gradient (stream 1) and parameter (stream
-// 0) tensors may be one flat run or separate allocations.  Synchronous: host_params is complete on return.
-int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, const void* host_grads,
-                 void* host_params, int num_slices) {
-    Device* d = as_device(device_ptr);
-    if (!d) return GM_ERR_NIL_DEVICE;
-    TensorList* l = as_list(list);
-    if (!l) return GM_ERR_BAD_ARG;
-    if (!hyper || !host_grads || !host_params) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
-    if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
+// The list is cut into `num_slices` groups of whole tensors and the three stages of each
+// slice -- gradients host->device, `launch` over the slice's chunks, parameters
+// device->host -- run on three streams, so the upload of slice s+1 and the download of
+// slice s-1 overlap the kernel of slice s and both PCIe directions are busy at once.
+// host_grads / host_params hold the tensors back to back in list order; the device
+// gradient (stream 1) and parameter (stream 0) tensors may be one flat run (one copy per
+// slice and direction) or separate allocations (one copy each).  `finish`, when given, is
+// enqueued on the device stream after the last slice.  Waits for everything.
+int host_pipelined_step(Device* d, const TensorList* l, const void* host_grads, void* host_params, int num_slices,
+                        const std::function<int(Window)>& launch, const std::function<int()>& finish) {
     if (l->dl.num_streams < 2) { set_error("list needs at least the parameter and gradient streams"); return GM_ERR_BAD_ARG; }
     const int T = l->dl.num_tensors;
     if (l->elem_bytes[0] != 4 || l->elem_bytes[1] != 4) { set_error("the host-buffer step needs fp32 parameters and gradients"); return GM_ERR_BAD_ARG; }
-    // Tensors that lie back to back on the device (a flat arena) move with one copy per slice
-    // and direction; separately allocated tensors move one by one.
     bool packed = true;
     for (int t = 0; t + 1 < T && packed; ++t)
         for (int s = 0; s < 2; ++s)
@@ -312,10 +281,10 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
         }
         GM_CUDA_CHECK(cudaEventRecord(in, d->h2d_stream));
         GM_CUDA_CHECK(cudaStreamWaitEvent(d->stream, in, 0));
-        l->win_begin = l->chunk_prefix[t0];
-        l->win_count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
-        rc = launch_rule(d, rule, l, *hyper);
-        l->win_begin = 0; l->win_count = -1;
+        Window win;
+        win.begin = l->chunk_prefix[t0];
+        win.count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
+        rc = launch(win);
         if (rc != GM_OK) break;
         GM_CUDA_CHECK(cudaEventRecord(done, d->stream));
         GM_CUDA_CHECK(cudaStreamWaitEvent(d->d2h_stream, done, 0));
@@ -331,6 +300,7 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
         }
         host_off += bytes;
     }
+    if (rc == GM_OK && finish) rc = finish();
     cudaError_t e1 = cudaStreamSynchronize(d->h2d_stream);
     cudaError_t e2 = cudaStreamSynchronize(d->stream);
     cudaError_t e3 = cudaStreamSynchronize(d->d2h_stream);
@@ -339,6 +309,53 @@ int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_
     if (e2 != cudaSuccess) return cuda_fail(e2, "host step (update)");
     if (e3 != cudaSuccess) return cuda_fail(e3, "host step (download)");
     return GM_OK;
+}
+
+}  // namespace gm
+
+using namespace gm;
+
+extern "C" {
+
+int gm_step_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    TensorList* l = as_list(list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (!hyper) { set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
+    if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
+    return launch_rule(d, rule, l, *hyper);
+}
+
+int gm_step_timed(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, float* elapsed_ms) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    TensorList* l = as_list(list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (!hyper || !elapsed_ms) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
+    DeviceGuard guard(d);
+    GM_CUDA_CHECK(cudaEventRecord(d->ev_start, d->stream));
+    int rc = launch_rule(d, rule, l, *hyper);
+    if (rc != GM_OK) return rc;
+    GM_CUDA_CHECK(cudaEventRecord(d->ev_stop, d->stream));
+    GM_CUDA_CHECK(cudaEventSynchronize(d->ev_stop));
+    GM_CUDA_CHECK(cudaEventElapsedTime(elapsed_ms, d->ev_start, d->ev_stop));
+    return GM_OK;
+}
+
+// One optimizer step for a caller whose gradients and parameters live in HOST
+// memory (pinned): see host_pipelined_step.  Synchronous: host_params is complete on return.
+int gm_step_host(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper, const void* host_grads,
+                 void* host_params, int num_slices) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    TensorList* l = as_list(list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (!hyper || !host_grads || !host_params) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
+    if (l->dev != d) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
+    const gm_hyper_t hy = *hyper;
+    return host_pipelined_step(d, l, host_grads, host_params, num_slices,
+                               [&](Window win) { return launch_rule(d, rule, l, hy, win); }, nullptr);
 }
 
 int execute_adam_step_cuda(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_t* m, uintptr_t* v,

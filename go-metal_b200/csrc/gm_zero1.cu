@@ -45,6 +45,7 @@ struct NcclApi {
     ncclResult_t (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
+    std::string load_error;           // why `ok` is false, captured once when the load was tried
 };
 
 static NcclApi& nccl() {
@@ -55,6 +56,8 @@ static NcclApi& nccl() {
         for (const char* n : names) {
             api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
             if (api.handle) break;
+            const char* why = dlerror();                 // one call: it also clears the message
+            api.load_error = why ? why : "dlopen failed";
         }
         if (!api.handle) return;
         api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(api.handle, "ncclGetUniqueId");
@@ -66,6 +69,7 @@ static NcclApi& nccl() {
         api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
         api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.AllReduce
                  && api.GetErrorString;
+        if (!api.ok) api.load_error = "libnccl was loaded but lacks a required symbol";
     });
     return api;
 }
@@ -87,6 +91,7 @@ struct Zero1 {
     uintptr_t local_base = 0;
     size_t local_bytes = 0;            // size of the exported allocation (0 = unknown)
     int* barrier_word = nullptr;       // device int used by the closing all-reduce
+    bool push_prefetch = true;         // GOMETAL_PUSH_PREFETCH=0 selects the push kernel without the software prefetch
     // copy-engine path: one stream per peer, one event per slice, one "done" event per peer
     cudaStream_t copy_stream[kMaxPeers] = {nullptr};
     cudaEvent_t copy_done[kMaxPeers] = {nullptr};
@@ -113,7 +118,9 @@ struct PeerDst {
 // Adam over this rank's shard list; every new parameter vector is stored to the
 // local arena and to the same offset of each peer's arena.
 // NP = number of peers, a template parameter so that the store loop unrolls
-// and the peer offsets stay in registers.
+// and the peer offsets stay in registers.  Like mta_apply_kernel, a thread issues
+// the loads of its next pass before the arithmetic and the stores of the current
+// one, so the remote stores leave while loads are in flight.
 template <int NP>
 __global__ void __launch_bounds__(kApplyThreads, 4)
 zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst peers) {
@@ -152,6 +159,80 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
         const long long b = (long long)h + (long long)k * chunk;
         const long long e = (b + chunk < n) ? b + chunk : n;
         if (k == 0 && tid < h) scalar_at(tid);
+        const int nvec = (int)((e - b) >> 2);
+        float4* q[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) q[s] = reinterpret_cast<float4*>(p[s] + b);
+
+        int i = tid;
+        float4 cur[NS];
+        if (i < nvec) {
+#pragma unroll
+            for (int s = 0; s < NS; ++s) cur[s] = ld_stream(q[s] + i);
+        }
+        while (i < nvec) {
+            const int nx = i + NT;
+            float4 nxt[NS];
+            if (nx < nvec) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) nxt[s] = ld_stream(q[s] + nx);
+            }
+            float x0[NS], x1[NS], x2[NS], x3[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) { x0[s] = cur[s].x; x1[s] = cur[s].y; x2[s] = cur[s].z; x3[s] = cur[s].w; }
+            AdamRule::elem(x0, prm); AdamRule::elem(x1, prm); AdamRule::elem(x2, prm); AdamRule::elem(x3, prm);
+            const float4 wn = make_float4(x0[0], x1[0], x2[0], x3[0]);
+#pragma unroll
+            for (int r = 0; r < NP; ++r)
+                *reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[r]) = wn;
+            *(q[0] + i) = wn;                                            // local copy stays cacheable
+            st_stream(q[2] + i, make_float4(x0[2], x1[2], x2[2], x3[2]));
+            st_stream(q[3] + i, make_float4(x0[3], x1[3], x2[3], x3[3]));
+#pragma unroll
+            for (int s = 0; s < NS; ++s) cur[s] = nxt[s];
+            i = nx;
+        }
+        const long long tb = b + ((long long)nvec << 2);
+        if (tb + tid < e) scalar_at(tb + tid);
+    }
+}
+
+// The version without the software prefetch (GOMETAL_PUSH_PREFETCH=0), kept for comparison.
+template <int NP>
+__global__ void __launch_bounds__(kApplyThreads, 4)
+zero1_adam_push_plain_kernel(const DevList L, const AdamRule::P prm, const PeerDst peers) {
+    constexpr int NS = 4;
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const long long chunk = L.chunk_elems;
+    for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
+        const int2 rec = __ldg(L.chunk_rec + c);
+        const int t = rec.x, k = rec.y;
+        const long long n = __ldg(L.numel + t);
+        const int h = __ldg(L.head + t);
+        float* p[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) p[s] = reinterpret_cast<float*>(__ldg(L.ptrs + (size_t)s * T + t));
+        auto scalar_at = [&](long long i) {
+            float x[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) x[s] = p[s][i];
+            AdamRule::elem(x, prm);
+            p[0][i] = x[0]; p[2][i] = x[2]; p[3][i] = x[3];
+#pragma unroll
+            for (int r = 0; r < NP; ++r)
+                *reinterpret_cast<float*>(reinterpret_cast<char*>(p[0] + i) + peers.delta[r]) = x[0];
+        };
+        if (h < 0) {
+            const long long b = (long long)k * chunk;
+            const long long e = (b + chunk < n) ? b + chunk : n;
+            for (long long i = b + tid; i < e; i += NT) scalar_at(i);
+            continue;
+        }
+        const long long b = (long long)h + (long long)k * chunk;
+        const long long e = (b + chunk < n) ? b + chunk : n;
+        if (k == 0 && tid < h) scalar_at(tid);
         const long long nvec = (e - b) >> 2;
         float4* q[NS];
 #pragma unroll
@@ -165,7 +246,7 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
             for (int s = 0; s < NS; ++s) { x0[s] = v[s].x; x1[s] = v[s].y; x2[s] = v[s].z; x3[s] = v[s].w; }
             AdamRule::elem(x0, prm); AdamRule::elem(x1, prm); AdamRule::elem(x2, prm); AdamRule::elem(x3, prm);
             const float4 wn = make_float4(x0[0], x1[0], x2[0], x3[0]);
-            *(q[0] + i) = wn;                                            // local copy stays cacheable
+            *(q[0] + i) = wn;
             st_stream(q[2] + i, make_float4(x0[2], x1[2], x2[2], x3[2]));
             st_stream(q[3] + i, make_float4(x0[3], x1[3], x2[3], x3[3]));
 #pragma unroll
@@ -177,6 +258,20 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
     }
 }
 
+using PushFn = void (*)(const DevList, const AdamRule::P, const PeerDst);
+
+static PushFn push_kernel_for(int peers, bool prefetch) {
+    switch (peers) {
+        case 0: case 1: return prefetch ? zero1_adam_push_kernel<1> : zero1_adam_push_plain_kernel<1>;
+        case 2: return prefetch ? zero1_adam_push_kernel<2> : zero1_adam_push_plain_kernel<2>;
+        case 3: return prefetch ? zero1_adam_push_kernel<3> : zero1_adam_push_plain_kernel<3>;
+        case 4: return prefetch ? zero1_adam_push_kernel<4> : zero1_adam_push_plain_kernel<4>;
+        case 5: return prefetch ? zero1_adam_push_kernel<5> : zero1_adam_push_plain_kernel<5>;
+        case 6: return prefetch ? zero1_adam_push_kernel<6> : zero1_adam_push_plain_kernel<6>;
+        default: return prefetch ? zero1_adam_push_kernel<7> : zero1_adam_push_plain_kernel<7>;
+    }
+}
+
 }  // namespace gm
 
 using namespace gm;
@@ -185,7 +280,7 @@ extern "C" {
 
 int gm_zero1_unique_id(void* out_id) {
     if (!out_id) { set_error("output is nil"); return GM_ERR_BAD_ARG; }
-    if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded: %s", dlerror() ? dlerror() : "symbols missing"); return GM_ERR_UNSUPPORTED; }
+    if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded: %s", nccl().load_error.c_str()); return GM_ERR_UNSUPPORTED; }
     ncclUniqueId id;
     ncclResult_t r = nccl().GetUniqueId(&id);
     if (r != 0) return nccl_fail(r, "ncclGetUniqueId");
@@ -199,12 +294,13 @@ uintptr_t gm_zero1_create(uintptr_t device_ptr, const void* unique_id, int rank,
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) { set_error("bad rank %d / world %d (max %d)", rank, world, kMaxPeers); return 0; }
     Zero1* z = new Zero1();
     z->dev = d; z->rank = rank; z->world = world;
+    if (const char* e = getenv("GOMETAL_PUSH_PREFETCH")) z->push_prefetch = atoi(e) != 0;
     DeviceGuard g(d);
     if (cudaMalloc((void**)&z->barrier_word, 256) != cudaSuccess) { cuda_fail(cudaGetLastError(), "cudaMalloc"); delete z; return 0; }
     cudaMemset(z->barrier_word, 0, 256);
     if (world > 1) {
         if (!unique_id) { set_error("unique id is nil"); cudaFree(z->barrier_word); delete z; return 0; }
-        if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded"); cudaFree(z->barrier_word); delete z; return 0; }
+        if (!nccl().ok) { set_error("libnccl.so.2 could not be loaded: %s", nccl().load_error.c_str()); cudaFree(z->barrier_word); delete z; return 0; }
         ncclUniqueId id;
         memcpy(&id, unique_id, sizeof(id));
         ncclResult_t r = nccl().CommInitRank(&z->comm, world, id, rank);
@@ -302,9 +398,17 @@ int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 6
     GM_CUDA_CHECK(cudaIpcGetMemHandle(&mh, (void*)arena_base));
     static_assert(sizeof(mh) == 64, "cudaIpcMemHandle_t is 64 bytes");
     memcpy(out_handle, &mh, sizeof(mh));
+    size_t bytes = at_base == 1 ? alloc_bytes : 0;
+    if (bytes == 0 && registered_size(arena_base) > 0) bytes = (size_t)registered_size(arena_base);
+    if (bytes == 0) {
+        // Neither the driver's address-range query nor the library's own registry knows where this
+        // allocation starts and ends: the peers' stores could not be checked against it.
+        set_error("cannot establish the bounds of the arena's allocation; the peer-store paths need them "
+                  "(use gm_zero1_adam_step_async, which exchanges through NCCL, instead)");
+        return GM_ERR_UNSUPPORTED;
+    }
     z->local_base = arena_base;
-    z->local_bytes = at_base == 1 ? alloc_bytes : 0;          // 0: size unknown, no range check
-    if (z->local_bytes == 0 && registered_size(arena_base) > 0) z->local_bytes = (size_t)registered_size(arena_base);
+    z->local_bytes = bytes;
     return GM_OK;
 }
 
@@ -340,7 +444,7 @@ static int check_inside_arena(const Zero1* z, const TensorList* l) {
     for (size_t t = 0; t < l->numel.size(); ++t) {
         const uintptr_t p = l->ptrs[0][t];
         const uintptr_t end = p + (uintptr_t)l->numel[t] * 4;
-        if (p < z->local_base || (z->local_bytes && end > z->local_base + z->local_bytes)) {
+        if (p < z->local_base || end > z->local_base + z->local_bytes) {
             set_error("parameter tensor %zu lies outside the arena exported to the peers", t);
             return GM_ERR_BAD_ARG;
         }
@@ -348,17 +452,8 @@ static int check_inside_arena(const Zero1* z, const TensorList* l) {
     return GM_OK;
 }
 
-int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper) {
-    Zero1* z = as_zero1(h);
-    if (!z) return GM_ERR_BAD_ARG;
-    TensorList* l = as_list(shard_list);
-    if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
-    if (l->dl.num_streams != 4) { set_error("Adam shard list needs w,g,m,v"); return GM_ERR_BAD_ARG; }
-    if (hyper->step < 1) { set_error("Adam step count %d must be >= 1", hyper->step); return GM_ERR_BAD_ARG; }
-    {
-        const int rc = check_inside_arena(z, l);
-        if (rc != GM_OK) return rc;
-    }
+// Launches the fused update + push kernel over a window of the shard list (no barrier).
+static int push_launch(Zero1* z, const TensorList* l, const gm_hyper_t& hyper, Window win) {
     Device* d = z->dev;
     PeerDst peers{};
     peers.count = 0;
@@ -369,32 +464,73 @@ int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hy
         peers.delta[peers.count++] = (long long)z->peer_base[r] - (long long)z->local_base;
     }
     AdamRule::P p;
-    p.lr = hyper->lr; p.beta1 = hyper->beta1; p.beta2 = hyper->beta2; p.eps = hyper->eps;
-    p.wd = hyper->weight_decay; p.use_wd = hyper->weight_decay > 0.0f ? 1 : 0;
-    p.bc1 = 1.0f - powf(hyper->beta1, (float)hyper->step);
-    p.bc2 = 1.0f - powf(hyper->beta2, (float)hyper->step);
-    p.omb1 = 1.0f - hyper->beta1;
-    p.omb2 = 1.0f - hyper->beta2;
+    p.lr = hyper.lr; p.beta1 = hyper.beta1; p.beta2 = hyper.beta2; p.eps = hyper.eps;
+    p.wd = hyper.weight_decay; p.use_wd = hyper.weight_decay > 0.0f ? 1 : 0;
+    p.bc1 = 1.0f - powf(hyper.beta1, (float)hyper.step);
+    p.bc2 = 1.0f - powf(hyper.beta2, (float)hyper.step);
+    p.omb1 = 1.0f - hyper.beta1;
+    p.omb2 = 1.0f - hyper.beta2;
+    DevList dl;
+    const int rc = apply_window(l, win, &dl);
+    if (rc != GM_OK) return rc;
+    if (dl.num_chunks == 0) return GM_OK;
     DeviceGuard g(d);
-    const int grid = launch_grid(d, nullptr, kApplyThreads, l->dl.num_chunks);
-    switch (peers.count) {
-        case 0: case 1: zero1_adam_push_kernel<1><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        case 2: zero1_adam_push_kernel<2><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        case 3: zero1_adam_push_kernel<3><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        case 4: zero1_adam_push_kernel<4><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        case 5: zero1_adam_push_kernel<5><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        case 6: zero1_adam_push_kernel<6><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-        default: zero1_adam_push_kernel<7><<<grid, kApplyThreads, 0, d->stream>>>(l->dl, p, peers); break;
-    }
+    const PushFn kernel = push_kernel_for(peers.count, z->push_prefetch);
+    const int grid = launch_grid(d, (const void*)kernel, kApplyThreads, dl.num_chunks);
+    kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, p, peers);
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
-    if (z->world > 1) {
-        // Completes only after every rank's push kernel has finished.
-        ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, d->stream);
-        if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
-        d->launches++;
-    }
     return GM_OK;
+}
+
+// One-word all-reduce on the device stream: completes only after every rank's pushes
+// (everything enqueued before it on each rank's stream) have finished.
+static int push_barrier(Zero1* z) {
+    if (z->world <= 1) return GM_OK;
+    DeviceGuard g(z->dev);
+    ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, z->dev->stream);
+    if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
+    z->dev->launches++;
+    return GM_OK;
+}
+
+static int push_validate(Zero1* z, const TensorList* l, const gm_hyper_t* hyper) {
+    if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
+    if (l->dev != z->dev) { set_error("tensor list belongs to another device"); return GM_ERR_BAD_ARG; }
+    if (l->dl.num_streams != 4) { set_error("Adam shard list needs w,g,m,v"); return GM_ERR_BAD_ARG; }
+    for (int s = 0; s < 4; ++s) if (l->elem_bytes[s] != 4) { set_error("stream %d is not fp32", s); return GM_ERR_BAD_ARG; }
+    if (hyper->step < 1) { set_error("Adam step count %d must be >= 1", hyper->step); return GM_ERR_BAD_ARG; }
+    return check_inside_arena(z, l);
+}
+
+int gm_zero1_adam_push_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    int rc = push_validate(z, l, hyper);
+    if (rc != GM_OK) return rc;
+    rc = push_launch(z, l, *hyper, Window());
+    if (rc != GM_OK) return rc;
+    return push_barrier(z);
+}
+
+// The sharded step for a caller whose gradients and parameters live in pinned HOST memory:
+// the rank's gradient shard is uploaded, updated and pushed to the peers, and the rank's new
+// parameters are downloaded, slice by slice on three streams (see gm_step_host); the closing
+// barrier tells every rank that its arena is complete.  Synchronous.
+int gm_zero1_adam_push_step_host(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper, const void* host_grads,
+                                 void* host_params, int num_slices) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    int rc = push_validate(z, l, hyper);
+    if (rc != GM_OK) return rc;
+    if (!host_grads || !host_params) { set_error("nil host buffer"); return GM_ERR_BAD_ARG; }
+    const gm_hyper_t hy = *hyper;
+    rc = host_pipelined_step(z->dev, l, host_grads, host_params, num_slices,
+                             [&](Window win) { return push_launch(z, l, hy, win); },
+                             [&]() { return push_barrier(z); });
+    return rc;
 }
 
 // Update + exchange with the copy engines: the shard is cut into `num_slices`
@@ -442,10 +578,10 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
     for (int s = 0; s < num_slices && rc == GM_OK; ++s) {
         const int t0 = (int)((long long)T * s / num_slices), t1 = (int)((long long)T * (s + 1) / num_slices);
         if (t1 <= t0) continue;
-        l->win_begin = l->chunk_prefix[t0];
-        l->win_count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
-        rc = launch_rule(d, GM_RULE_ADAM, l, *hyper);
-        l->win_begin = 0; l->win_count = -1;
+        Window win;
+        win.begin = l->chunk_prefix[t0];
+        win.count = l->chunk_prefix[t1] - l->chunk_prefix[t0];
+        rc = launch_rule(d, GM_RULE_ADAM, l, *hyper, win);
         if (rc != GM_OK) break;
         GM_CUDA_CHECK(cudaEventRecord(z->slice_ready[s], d->stream));
         const uintptr_t src = l->ptrs[0][t0];
@@ -463,12 +599,7 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
         GM_CUDA_CHECK(cudaEventRecord(z->copy_done[r], z->copy_stream[r]));
         GM_CUDA_CHECK(cudaStreamWaitEvent(d->stream, z->copy_done[r], 0));
     }
-    if (z->world > 1) {
-        ncclResult_t r = nccl().AllReduce(z->barrier_word, z->barrier_word, 1, kNcclInt32, kNcclSum, z->comm, d->stream);
-        if (r != 0) return nccl_fail(r, "ncclAllReduce(barrier)");
-        d->launches++;
-    }
-    return GM_OK;
+    return push_barrier(z);
 }
 
 // Mixed-precision Adam on sharded fp16 gradients: the overflow flag of every

@@ -75,6 +75,7 @@ _SIGS = {
     "gm_device_sm_count": (i, [u]),
     "gm_device_stream": (u, [u]),
     "gm_device_synchronize": (i, [u]),
+    "gm_device_synchronize_timeout": (i, [u, i]),
     "gm_device_launch_count": (i64, [u]),
     "gm_buffer_alloc": (u, [u, i64]),
     "gm_buffer_free": (None, [u]),
@@ -122,6 +123,7 @@ _SIGS = {
     "gm_zero1_ipc_handle": (i, [u, u, vp]),
     "gm_zero1_open_peers": (i, [u, vp]),
     "gm_zero1_adam_push_step_async": (i, [u, u, C.POINTER(Hyper)]),
+    "gm_zero1_adam_push_step_host": (i, [u, u, C.POINTER(Hyper), vp, vp, i]),
     "gm_zero1_adam_dma_step_async": (i, [u, u, C.POINTER(Hyper), i]),
     "gm_zero1_mixed_step_async": (i, [u, u, u, f, f, f, u, i64]),
     "gm_zero1_reduce_scatter_async": (i, [u, u, i64, i]),

@@ -39,7 +39,7 @@ extern "C" {
 #define GM_ERR_BAD_SIZE      -9   /* size <= 0, not a multiple of the element, or too small */
 #define GM_ERR_BAD_ARG      -10   /* any other invalid argument */
 #define GM_ERR_UNSUPPORTED  -11   /* valid call that this build cannot serve (e.g. NCCL missing) */
-#define GM_ERR_TIMEOUT      -12   /* a bounded device-side wait ran out */
+#define GM_ERR_TIMEOUT      -12   /* a bounded wait ran out (gm_device_synchronize_timeout) */
 
 /* ===================================================================== */
 /* Part 1 -- drop-in entries                                              */
@@ -160,6 +160,11 @@ int gm_device_ordinal(uintptr_t device_ptr);
 int gm_device_sm_count(uintptr_t device_ptr);
 uintptr_t gm_device_stream(uintptr_t device_ptr);/* cudaStream_t the device launches on */
 int gm_device_synchronize(uintptr_t device_ptr);
+/* The same wait with a deadline: polls the stream and returns GM_ERR_TIMEOUT when it has
+ * not drained after timeout_ms.  Nothing is cancelled; the caller decides (wait again,
+ * tear the group down).  Meant for sharded steps, where a peer that never enters its
+ * collective would otherwise block this rank for ever. */
+int gm_device_synchronize_timeout(uintptr_t device_ptr, int timeout_ms);
 /* Number of kernels this library has launched on the device so far. */
 int64_t gm_device_launch_count(uintptr_t device_ptr);
 
@@ -276,8 +281,11 @@ int gm_dot_canonical(uintptr_t device_ptr, uintptr_t a, uintptr_t b, int64_t n, 
  * GM_DOT_STATIC_MAX_ELEMENTS; longer vectors are rejected with GM_ERR_BAD_SIZE.
  * a, b, out (one float) are device pointers on the current device; stream is a
  * cudaStream_t (0 = default).  Asynchronous.  The first call on a device looks
- * up the array's address and should come before any stream capture.  Calls on
- * one device share the array: calls that can overlap on the GPU race. */
+ * up the array's address and should come before any stream capture; on that call
+ * CUDA may also load the library's code onto the GPU (lazy module loading), which
+ * is when the array takes its place in device memory.  The address is cached per
+ * process and device and does not survive a cudaDeviceReset.  Calls on one device
+ * share the array: calls that can overlap on the GPU race. */
 #define GM_DOT_STATIC_MAX_ELEMENTS 67108864LL
 int gm_dot_canonical_static(uintptr_t a, uintptr_t b, int64_t n, uintptr_t out_device, uintptr_t stream);
 
@@ -307,6 +315,12 @@ int gm_zero1_world(uintptr_t zero1);
 int gm_zero1_ipc_handle(uintptr_t zero1, uintptr_t arena_base, void* out_handle);
 int gm_zero1_open_peers(uintptr_t zero1, const void* handles);
 int gm_zero1_adam_push_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper);
+/* The same step for a caller whose gradients and parameters live in pinned HOST memory:
+ * the rank's gradient shard is uploaded, updated and pushed, and its new parameters are
+ * downloaded, slice by slice on three streams as in gm_step_host.  host_grads /
+ * host_params hold the shard's tensors back to back in list order.  Synchronous. */
+int gm_zero1_adam_push_step_host(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper,
+                                 const void* host_grads, void* host_params, int num_slices);
 /* Update + exchange through the copy engines: the shard is updated in
  * `num_slices` groups of whole tensors and every finished slice is copied to
  * the same offset of each peer's arena (one cudaMemcpyAsync per peer and

@@ -13,6 +13,7 @@ for p in (ROOT, os.path.join(ROOT, "go-metal_b200", "python"), os.path.dirname(o
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "slow: a full-size, full-length configuration (minutes); deselect with -m 'gpu and not slow'")
 
 
 @pytest.fixture(scope="session")

@@ -28,6 +28,9 @@ def test_reference_arm_prints_one_contract_line():
         assert key in d, key
     assert d["unit"] == "Gparams/s" and d["higher_is_better"] is True and d["vs_baseline"] is None
     assert d["dtype"] == "f32" and d["data"] == "synthetic" and "workload" in d["config"]
+    sys.path.insert(0, ROOT)
+    import bench
+    assert d["config"] == bench.CONFIG, "both arms print the same config object"
     assert d["value"] > 0 and d["ms_per_step"] > 0
     cpu = d["cpu_baseline"]
     assert cpu["kind"] == "port" and cpu["cores"] >= 1 and cpu["value"] == d["value"] and cpu["sample"]

@@ -327,3 +327,30 @@ def test_adam_with_state_in_a_flat_arena(gm, H, oracle):
         gm.lib.deallocate_cuda_buffer(p)
     H.gmh_mm_destroy(mm)
     H.gmh_device_destroy(dev)
+
+
+def test_synchronize_with_a_deadline(gm, dev):
+    """gm_device_synchronize_timeout returns GM_ERR_TIMEOUT (-12) while the stream still has
+    work and GM_OK once it has drained; nothing is cancelled by the timeout."""
+    import ctypes as C
+    L = gm.lib
+    n = 1 << 26
+    bufs = [dev.alloc(4 * n) for _ in range(4)]
+    for p in bufs:
+        gm.check(L.gm_buffer_zero(dev.h, p, 4 * n), "zero")
+    lst = dev.tensor_list([[p] for p in bufs], [n])
+    try:
+        assert L.gm_device_synchronize_timeout(dev.h, 1000) == 0
+        hy = gm.Hyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1)
+        for step in range(1, 201):                          # about 60 ms of queued work
+            hy.step = step
+            gm.check(L.gm_step_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy)), "adam")
+        assert L.gm_device_synchronize_timeout(dev.h, 0) == -12
+        assert "did not drain" in gm.last_error()
+        assert L.gm_device_synchronize_timeout(dev.h, 20000) == 0
+        assert L.gm_device_synchronize_timeout(dev.h, -1) == -10
+        assert L.gm_device_synchronize_timeout(0, 5) == -1
+    finally:
+        L.gm_tensor_list_destroy(lst)
+        for p in bufs:
+            dev.free(p)

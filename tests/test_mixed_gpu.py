@@ -371,3 +371,65 @@ def test_fp32_streams_on_16_but_not_32_byte_boundaries(gm, dev, oracle):
         L.gm_tensor_list_destroy(lst)
         for k in keys:
             dev.free(bufs[k])
+
+
+def test_resume_at_a_late_step_with_slow_betas(gm, dev, oracle):
+    """A state created (or restored) at a step count far beyond the initial table, with
+    betas whose corrections are still below 1 there: the bias corrections of the next
+    steps must be those of that step count, not of the table's last entry."""
+    O, L = oracle, gm.lib
+    sizes = [4099, 33]
+    b1, b2, t0 = 0.9999, 0.9999, 100_000
+    for how in ("create", "set_state"):
+        A = PackedArenas(gm, dev, sizes)
+        st = O.new_loss_scale(adam_t=t0)
+        init = gm.LossScale(scale=st.scale, growth=st.growth, backoff=st.backoff, max_scale=st.max_scale,
+                            interval=st.interval, good_steps=0, adam_t=t0 if how == "create" else 0, skipped=0, last_overflow=0)
+        mx = L.gm_mixed_create(dev.h, C.byref(init), b1, b2, 64)
+        assert mx, gm.last_error()
+        try:
+            if how == "set_state":
+                init.adam_t = t0
+                gm.check(L.gm_mixed_set_state(dev.h, mx, C.byref(init)), "set state")
+            master = [O.fill_uniform(n, -0.05, 0.05, 17, k) for k, n in enumerate(sizes)]
+            m = [O.fill_normal(n, 0, 1e-3, 17, 10 + k) for k, n in enumerate(sizes)]
+            v = [np.abs(O.fill_normal(n, 0, 1e-6, 17, 20 + k)) for k, n in enumerate(sizes)]
+            p16 = [O.f32_to_f16(w) for w in master]
+            for key, arrs in (("w", master), ("m", m), ("v", v), ("p", p16)):
+                A.put(key, arrs)
+            for step in range(3):
+                g16 = [O.f32_to_f16(O.fill_normal(n, 0, 1e-3, 17, 100 * step + k) * np.float32(st.scale)) for k, n in enumerate(sizes)]
+                A.put("g", g16)
+                gm.check(L.gm_mixed_step_async(dev.h, mx, A.list, LR, EPS, WD), "step")
+                O.mixed_adam_step(g16, master, m, v, p16, LR, b1, b2, EPS, WD, st)
+            got = gm.LossScale()
+            gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(got)), "state")
+            assert same_state(got, st) and st.adam_t == t0 + 3
+            bc = O.adam_scalars(b1, b2, t0 + 1)
+            assert bc[0] < 1.0 and bc[1] < 1.0, "the case must sit where the corrections still matter"
+            for key, want in (("w", master), ("m", m), ("v", v)):
+                got_list, _ = A.get(key)
+                for t, (a, b) in enumerate(zip(got_list, want)):
+                    assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), f"{how}: {key}[{t}] differs"
+        finally:
+            L.gm_mixed_destroy(mx)
+            A.close()
+
+
+def test_set_state_validates_like_create(gm, dev):
+    L = gm.lib
+    mx = L.gm_mixed_create(dev.h, None, B1, B2, 0)
+    try:
+        ok = gm.LossScale(scale=1024.0, growth=2.0, backoff=0.5, max_scale=65536.0, interval=10, good_steps=0, adam_t=0,
+                          skipped=0, last_overflow=0)
+        assert L.gm_mixed_set_state(dev.h, mx, C.byref(ok)) == 0
+        for field, value in (("max_scale", 0.0), ("growth", 0.5), ("backoff", 0.0), ("backoff", 1.5), ("scale", -1.0),
+                             ("interval", 0), ("adam_t", -1), ("scale", float("inf"))):
+            bad = gm.LossScale(scale=1024.0, growth=2.0, backoff=0.5, max_scale=65536.0, interval=10, good_steps=0,
+                               adam_t=0, skipped=0, last_overflow=0)
+            setattr(bad, field, value)
+            assert L.gm_mixed_set_state(dev.h, mx, C.byref(bad)) == -10, field
+            assert "invalid loss-scale state" in gm.last_error()
+        assert L.gm_mixed_create(dev.h, C.byref(gm.LossScale(scale=1.0, growth=2.0, backoff=0.5, max_scale=0.5, interval=1)), B1, B2, 0) == 0
+    finally:
+        L.gm_mixed_destroy(mx)

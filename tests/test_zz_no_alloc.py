@@ -39,7 +39,9 @@ def test_static_dot_matches_allocating_entry_twice_in_a_row(gm, dev, oracle):
     try:
         # two different problems back to back: the second call finds the first
         # call's chunk sums still in the built-in array and must not be affected
-        cases = [(1_000_003, 41), (70_001, 42), (1_000_003, 41), (5, 43), (4096, 44)]
+        # 5,000,003 elements = 1,221 chunks: more chunks than CTAs (each CTA loops) and more than
+        # 256 (the last CTA's lanes each add several chunk sums)
+        cases = [(1_000_003, 41), (70_001, 42), (1_000_003, 41), (5, 43), (4096, 44), (5_000_003, 45)]
         for n, seed in cases:
             a = O.fill_normal(n, 0, 1, seed, 1)
             b = O.fill_normal(n, 0, 1, seed, 2)
@@ -58,6 +60,35 @@ def test_static_dot_matches_allocating_entry_twice_in_a_row(gm, dev, oracle):
             dev.free(pb)
     finally:
         dev.free(pout)
+
+
+def test_static_dot_at_its_size_limit(gm, dev, oracle):
+    """n = GM_DOT_STATIC_MAX_ELEMENTS exactly: every slot of the built-in array is used (two
+    256 MB operands); one element more is refused in the test below."""
+    torch = pytest.importorskip("torch")
+    O = oracle
+    n = LIMIT
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(46)
+    a = torch.empty(n, dtype=torch.float32, device="cuda").normal_(0.0, 1.0, generator=gen)
+    b = torch.empty(n, dtype=torch.float32, device="cuda").normal_(0.0, 1.0, generator=gen)
+    torch.cuda.synchronize()
+    pout = dev.alloc(256)
+    try:
+        want = reference_dot(gm, dev, a.data_ptr(), b.data_ptr(), n)
+        for _ in range(2):
+            got = static_dot(gm, dev, a.data_ptr(), b.data_ptr(), n, pout)
+            assert got.view(np.uint32) == want.view(np.uint32), f"{got} vs {want}"
+        O.set_threads(O.all_cores())
+        try:
+            cpu = O.dot_canonical(a.cpu().numpy(), b.cpu().numpy())
+        finally:
+            O.set_threads(1)
+        assert want.view(np.uint32) == cpu.view(np.uint32)
+    finally:
+        dev.free(pout)
+        del a, b
+        torch.cuda.empty_cache()
 
 
 def test_static_dot_refuses_what_it_cannot_hold(gm, dev):

@@ -2,9 +2,10 @@
 tests/test_zero1_multigpu.py through torch.distributed.run).
 
 Every rank keeps the full parameter arena, updates its own shard with the CUDA
-library and exchanges parameters, first with the NCCL all-gather path and then
-with the fused update+push kernel; after each step every rank's arena must
-equal, bit for bit, the oracle's update of ALL tensors.
+library and exchanges parameters: with the NCCL all-gather path, the fused
+update+push kernel, the copy-engine path and the push path fed from host
+buffers; after each step every rank's arena must equal, bit for bit, the
+oracle's update of ALL tensors.
 """
 import ctypes as C
 import os
@@ -44,7 +45,7 @@ def main():
     assert z, gm.last_error()
     assert L.gm_zero1_rank(z) == rank and L.gm_zero1_world(z) == world
 
-    for exchange in ("nccl", "push", "dma"):
+    for exchange in ("nccl", "push", "dma", "push_host"):
         w0 = O.fill_uniform(T * E, -0.1, 0.1, 91, 1)
         full, fm, fv = w0.copy(), np.zeros(T * E, np.float32), np.zeros(T * E, np.float32)
         arena = dev.to_device(w0)
@@ -54,7 +55,7 @@ def main():
         w_ptrs = [arena + 4 * plan.tensor_offset(k) for k in plan.owned]
         loc = lambda base: [base + 4 * plan.local_offset(k) for k in plan.owned]
         lst = dev.tensor_list([w_ptrs, loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
-        if exchange in ("push", "dma"):
+        if exchange in ("push", "dma", "push_host"):
             mine = (C.c_ubyte * 64)()
             # an address inside the allocation cannot be exported: the peers would map the
             # allocation's first byte and store at the wrong offset
@@ -77,15 +78,21 @@ def main():
         for step in range(1, STEPS + 1):
             grads = [O.fill_normal(E, 0.0, 0.01, 91, 1000 * step + k) for k in range(T)]
             shard_g = np.concatenate([grads[k] for k in plan.owned])
-            dev.upload(dg, shard_g)
+            if exchange != "push_host":
+                dev.upload(dg, shard_g)
             dist.barrier()                       # nobody pushes into an arena that is still being read
             hy = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=step)
             if exchange == "nccl":
                 gm.check(L.gm_zero1_adam_step_async(z, lst, C.byref(hy), arena, plan.shard_elems), "zero1 step")
             elif exchange == "push":
                 gm.check(L.gm_zero1_adam_push_step_async(z, lst, C.byref(hy)), "zero1 push step")
-            else:
+            elif exchange == "dma":
                 gm.check(L.gm_zero1_adam_dma_step_async(z, lst, C.byref(hy), 3), "zero1 dma step")
+            else:
+                # gradients come from host memory and the rank's new parameters go back to it, in 3 slices
+                host_w = np.empty(plan.shard_elems, np.float32)
+                gm.check(L.gm_zero1_adam_push_step_host(z, lst, C.byref(hy), shard_g.ctypes.data, host_w.ctypes.data, 3),
+                         "zero1 push step with host buffers")
             dev.sync()
             for k in range(T):
                 a = k * E
@@ -96,6 +103,9 @@ def main():
             bad = np.flatnonzero(got.view(np.uint32) != full.view(np.uint32))
             assert bad.size == 0, (f"rank {rank} {exchange} step {step}: {bad.size} parameters differ, first at "
                                    f"{bad[0]} (tensor {bad[0] // E})")
+            if exchange == "push_host":
+                want_w = full[plan.shard_offset:plan.shard_offset + plan.shard_elems]
+                assert np.array_equal(host_w.view(np.uint32), want_w.view(np.uint32)), f"rank {rank}: downloaded shard differs"
             got_m = dev.to_host(dm, plan.shard_elems)
             want_m = fm[plan.shard_offset:plan.shard_offset + plan.shard_elems]
             assert np.array_equal(got_m.view(np.uint32), want_m.view(np.uint32)), f"rank {rank}: m differs"
