@@ -41,6 +41,51 @@ __device__ __forceinline__ float root0(float a) {
     return __fsqrt_rn(a);
 }
 
+// a / c for a divisor c that is the same for a whole launch, given r = RN(1/c):
+//     q0 = RN(a*r); e0 = a - q0*c (one fma); q1 = RN(q0 + e0*r); e1 = a - q1*c; q = RN(q1 + e1*r).
+// q0 is within 2^-23 of a/c in relative terms, so q1 = RN((a/c)(1 + d)) with |d| < 2^-46 is a
+// faithful quotient, its residual e1 is exact, and by Markstein's theorem (a faithful quotient
+// corrected once with the correctly rounded reciprocal) the last step returns RN(a/c): the bits
+// of __fdiv_rn(a, c) at five instructions, without the reciprocal estimate and its refinement.
+// That needs every intermediate to be a normal number.  The host only enables the path for
+// 2^-24 <= c <= 1 with a significand that is not all ones (const_div_ok); here a must lie in
+// [2^-100, 2^100), which the exponent test checks (zero, denormals, huge values, inf and NaN
+// take the IEEE division).  The selftest entry gm_selftest_const_div compares the two over
+// all 2^32 values of a for a given c.
+__device__ __forceinline__ float div_const(float a, float c, float r) {
+    const unsigned biased = (__float_as_uint(a) >> 23) & 0xffu;
+    if (biased - 27u < 200u) {                               // 27 <= exponent field <= 226
+        float q = __fmul_rn(a, r);
+        float e = __fmaf_rn(-q, c, a);
+        q = __fmaf_rn(e, r, q);
+        e = __fmaf_rn(-q, c, a);
+        return __fmaf_rn(e, r, q);
+    }
+    return dvd0(a, c);
+}
+__host__ __device__ __forceinline__ bool const_div_ok(float c) {
+    union { float f; unsigned u; } b;
+    b.f = c;
+    return c >= 5.9604644775390625e-08f && c <= 1.0f && (b.u & 0x7fffffu) != 0x7fffffu;
+}
+
+// Sum of the 256 lane values of a CTA in the library's fixed order (xor tree per warp, warp
+// sums in ascending order); result valid in thread 0.  warp_sum: 8 floats of shared memory.
+__device__ __forceinline__ float cta_sum_256(float acc, float* warp_sum) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc = add(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    float total = 0.0f;
+    if (threadIdx.x == 0) {
+        total = warp_sum[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total = add(total, warp_sum[w]);
+    }
+    __syncthreads();
+    return total;
+}
+
 // Streaming accesses: every byte is touched once per step, so lines are marked
 // evict-first on the way in and on the way out.
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
@@ -62,13 +107,17 @@ __device__ __forceinline__ int find_tensor(const int* __restrict__ prefix, int n
 struct AdamRule {
     static constexpr int NS = 4;                 // w, g, m, v
     static constexpr unsigned WMASK = 0b1101;
-    struct P { float lr, beta1, beta2, omb1, omb2, bc1, bc2, eps, wd; int use_wd; };
-    static __device__ __forceinline__ void elem(float (&x)[NS], const P& p) {
+    struct P { float lr, beta1, beta2, omb1, omb2, bc1, bc2, eps, wd; int use_wd; float rbc1, rbc2; };
+    static __device__ __forceinline__ void elem(float (&x)[NS], const P& p) { elem_t<false>(x, p); }
+    // FAST: the two divisions by the bias corrections go through div_const with the
+    // reciprocals rbc1 and rbc2 (same bits; the caller has checked const_div_ok for both).
+    template <bool FAST>
+    static __device__ __forceinline__ void elem_t(float (&x)[NS], const P& p) {
         const float w = x[0], g = x[1];
         const float m_new = add(mul(x[2], p.beta1), mul(g, p.omb1));
         const float v_new = add(mul(x[3], p.beta2), mul(mul(g, g), p.omb2));
-        const float m_hat = dvd0(m_new, p.bc1);
-        const float v_hat = dvd0(v_new, p.bc2);
+        const float m_hat = FAST ? div_const(m_new, p.bc1, p.rbc1) : dvd0(m_new, p.bc1);
+        const float v_hat = FAST ? div_const(v_new, p.bc2, p.rbc2) : dvd0(v_new, p.bc2);
         float upd = dvd0(m_hat, add(root0(v_hat), p.eps));
         if (p.use_wd) upd = add(upd, mul(w, p.wd));
         x[0] = sub(w, mul(upd, p.lr));
@@ -110,14 +159,19 @@ __device__ __forceinline__ uint4 ld_l2(const uint4* a, const unsigned long long 
 //   static constexpr unsigned WMASK;    bit s set => stream s is written back
 //   struct P;                           scalars, passed by value
 //   static __device__ void elem(float (&x)[NS], const P&);   in-place on x
-template <class Rule>
+//
+// CLIP: every gradient (stream 1 of every rule) is first multiplied by the
+// global-norm clipping coefficient, a device scalar that a reduction launched
+// earlier on the same stream has left at `clip` (one rounding per gradient).
+template <class Rule, bool CLIP>
 __global__ void __launch_bounds__(kApplyThreads, (Rule::NS <= 4 ? 5 : 4))
-mta_apply_kernel(const DevList L, const typename Rule::P prm) {
+mta_apply_kernel(const DevList L, const typename Rule::P prm, const float* __restrict__ clip) {
     constexpr int NS = Rule::NS;
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
     const int chunk = L.chunk_elems;
+    const float cs = CLIP ? __ldg(clip) : 1.0f;
 
     for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
         const int2 rec = __ldg(L.chunk_rec + c);          // {tensor, chunk index inside the tensor}
@@ -136,6 +190,7 @@ mta_apply_kernel(const DevList L, const typename Rule::P prm) {
                 float x[NS];
 #pragma unroll
                 for (int s = 0; s < NS; ++s) x[s] = ld_stream(p[s] + i);
+                if (CLIP) x[1] = mul(x[1], cs);
                 Rule::elem(x, prm);
 #pragma unroll
                 for (int s = 0; s < NS; ++s) if (Rule::WMASK & (1u << s)) st_stream(p[s] + i, x[s]);
@@ -167,6 +222,7 @@ mta_apply_kernel(const DevList L, const typename Rule::P prm) {
             float x0[NS], x1[NS], x2[NS], x3[NS];
 #pragma unroll
             for (int s = 0; s < NS; ++s) { x0[s] = cur[s].x; x1[s] = cur[s].y; x2[s] = cur[s].z; x3[s] = cur[s].w; }
+            if (CLIP) { x0[1] = mul(x0[1], cs); x1[1] = mul(x1[1], cs); x2[1] = mul(x2[1], cs); x3[1] = mul(x3[1], cs); }
             Rule::elem(x0, prm);
             Rule::elem(x1, prm);
             Rule::elem(x2, prm);
@@ -190,6 +246,7 @@ mta_apply_kernel(const DevList L, const typename Rule::P prm) {
             float x[NS];
 #pragma unroll
             for (int s = 0; s < NS; ++s) x[s] = ld_stream(p[s] + idx);
+            if (CLIP) x[1] = mul(x[1], cs);
             Rule::elem(x, prm);
 #pragma unroll
             for (int s = 0; s < NS; ++s) if (Rule::WMASK & (1u << s)) st_stream(p[s] + idx, x[s]);
@@ -198,7 +255,8 @@ mta_apply_kernel(const DevList L, const typename Rule::P prm) {
 }
 
 template <class Rule>
-int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm, Window win = Window()) {
+int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm, Window win = Window(),
+                 const float* clip = nullptr) {
     if (l->dl.num_streams != Rule::NS) {
         set_error("tensor list has %d streams, rule needs %d", l->dl.num_streams, Rule::NS);
         return GM_ERR_BAD_ARG;
@@ -206,7 +264,7 @@ int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm, Wi
     for (int s = 0; s < Rule::NS; ++s) {
         if (l->elem_bytes[s] != 4) { set_error("stream %d is not fp32", s); return GM_ERR_BAD_ARG; }
     }
-    auto kernel = mta_apply_kernel<Rule>;
+    auto kernel = clip ? mta_apply_kernel<Rule, true> : mta_apply_kernel<Rule, false>;
     DevList dl;
     {
         const int rc = apply_window(l, win, &dl);
@@ -214,7 +272,7 @@ int launch_apply(Device* d, const TensorList* l, const typename Rule::P& prm, Wi
         if (dl.num_chunks == 0) return GM_OK;
     }
     int grid = launch_grid(d, (const void*)kernel, kApplyThreads, dl.num_chunks);
-    kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, prm);
+    kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, prm, clip);
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());
     return GM_OK;

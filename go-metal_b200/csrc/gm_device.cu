@@ -160,6 +160,8 @@ static Device* make_device(int ordinal) {
     if (const char* e5 = getenv("GOMETAL_MIXED_KEEP_G")) d->mixed_keep_g = atoi(e5);
     if (const char* e6 = getenv("GOMETAL_MIXED_OVERLAP")) d->mixed_overlap = atoi(e6);
     if (const char* e8 = getenv("GOMETAL_MIXED_VARIANT")) d->mixed_variant = atoi(e8);
+    if (const char* e = getenv("GOMETAL_MIXED_FASTDIV")) d->mixed_fastdiv = atoi(e);
+    if (const char* e = getenv("GOMETAL_MIXED_PF")) d->mixed_pf = atoi(e);
     if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);
     if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);
     // A blocking stream on purpose: the synchronous copies of the drop-in ABI
@@ -324,7 +326,8 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     // head[t]: number of leading elements to peel so that every stream of the
     // tensor sits on a 16-byte boundary; the vector tile is 8 elements for
     // lists with 2-byte streams so one 16-byte access covers it.
-    std::vector<int> head(nt), prefix(nt + 1);
+    std::vector<int> head(nt), prefix(nt + 1), dot_prefix(nt + 1);
+    dot_prefix[0] = 0;
     int lanes = 4;
     for (int s = 0; s < ns; ++s) if (l->elem_bytes[s] == 2) lanes = 8;
     prefix[0] = 0;
@@ -342,6 +345,9 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
         int64_t nchunks = body > 0 ? (body + chunk - 1) / chunk : 1;
         if ((int64_t)prefix[t] + nchunks > 0x7fffffff) { set_error("tensor list too large"); *err = GM_ERR_BAD_SIZE; delete l; return nullptr; }
         prefix[t + 1] = prefix[t] + (int)nchunks;
+        const int64_t ndot = (numel[t] + kDotChunkElems - 1) / kDotChunkElems;
+        if ((int64_t)dot_prefix[t] + ndot > 0x7fffffff) { set_error("tensor list too large"); *err = GM_ERR_BAD_SIZE; delete l; return nullptr; }
+        dot_prefix[t + 1] = dot_prefix[t] + (int)ndot;
     }
 
     const int num_chunks = prefix[nt];
@@ -350,7 +356,8 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     size_t off_rec = off_numel + sizeof(long long) * nt;
     size_t off_head = off_rec + sizeof(int2) * (size_t)num_chunks;
     size_t off_prefix = off_head + sizeof(int) * nt;
-    size_t bytes = off_prefix + sizeof(int) * (nt + 1);
+    size_t off_dot = off_prefix + sizeof(int) * (nt + 1);
+    size_t bytes = off_dot + sizeof(int) * (nt + 1);
     std::vector<unsigned char> host(bytes);
     for (int s = 0; s < ns; ++s)
         for (int t = 0; t < nt; ++t)
@@ -363,6 +370,7 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     }
     memcpy(host.data() + off_head, head.data(), sizeof(int) * nt);
     memcpy(host.data() + off_prefix, prefix.data(), sizeof(int) * (nt + 1));
+    memcpy(host.data() + off_dot, dot_prefix.data(), sizeof(int) * (nt + 1));
 
     {
         DeviceGuard g(d);
@@ -376,7 +384,10 @@ TensorList* build_list(Device* d, int ns, int nt, const uintptr_t* const* sp, co
     l->dl.head = (const int*)(b + off_head);
     l->dl.chunk_prefix = (const int*)(b + off_prefix);
     l->dl.chunk_rec = (const int2*)(b + off_rec);
+    l->dl.dot_prefix = (const int*)(b + off_dot);
+    l->dl.num_dot_chunks = dot_prefix[nt];
     l->chunk_prefix = prefix;
+    l->head = head;
     l->dl.num_tensors = nt;
     l->dl.num_chunks = prefix[nt];
     l->dl.chunk_elems = chunk;
@@ -805,6 +816,13 @@ void gm_tensor_list_destroy(uintptr_t h) {
 }
 
 int64_t gm_tensor_list_total(uintptr_t h) { TensorList* l = as_list(h); return l ? l->total : -1; }
+int gm_tensor_list_chunk_elems(uintptr_t h) { TensorList* l = as_list(h); return l ? l->dl.chunk_elems : -1; }
+int gm_tensor_list_head(uintptr_t h, int tensor) {
+    TensorList* l = as_list(h);
+    if (!l) return -2;
+    if (tensor < 0 || tensor >= (int)l->head.size()) { set_error("tensor index %d outside the list", tensor); return -2; }
+    return l->head[tensor];
+}
 int gm_tensor_list_num_chunks(uintptr_t h) { TensorList* l = as_list(h); return l ? l->dl.num_chunks : -1; }
 
 }  // extern "C"

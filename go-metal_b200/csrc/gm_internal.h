@@ -28,6 +28,8 @@ struct DevList {
     const int* head;                  // [num_tensors] scalar elements before the 16-B aligned body; -1 = no aligned body
     const int* chunk_prefix;          // [num_tensors+1] first chunk of each tensor
     const int2* chunk_rec;            // [num_chunks] {tensor, chunk index inside the tensor}
+    const int* dot_prefix;            // [num_tensors+1] first 4096-element reduction chunk of each tensor (counted from element 0)
+    int num_dot_chunks;
     int num_tensors;
     int num_chunks;
     int chunk_elems;                  // elements per chunk (multiple of the vector tile)
@@ -47,6 +49,7 @@ struct TensorList {
     std::vector<std::vector<uintptr_t>> ptrs;   // host copy [stream][tensor]
     uint64_t key = 0;                 // cache key (0 = not cached)
     std::vector<int> chunk_prefix;    // host copy: first chunk of each tensor, [num_tensors+1]
+    std::vector<int> head;            // host copy of dl.head
     uint64_t validated_gen = 0;       // registry generation under which the buffers were last checked
 };
 
@@ -70,6 +73,8 @@ struct Device {
     int64_t launches = 0;
     int mixed_keep_g = 1;               // fp16 gradients marked evict_last by the overflow check (GOMETAL_MIXED_KEEP_G)
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
+    int mixed_fastdiv = 1;              // divisions by the bias corrections through div_const (GOMETAL_MIXED_FASTDIV)
+    int mixed_pf = 1;                   // next-pass L2 prefetch in the update kernel (GOMETAL_MIXED_PF)
     int mixed_variant = 0;              // 1: the 4-elements-per-thread update kernel instead of the 8-element one (GOMETAL_MIXED_VARIANT)
     int mixed_overlap = 2;              // update grid launched with programmatic stream serialization: 2 = it may start when the
                                         // check grid's CTAs reach their end (measured best), 1 = from their start, 0 = off
@@ -125,10 +130,14 @@ void free_list(TensorList* l);
 int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items);
 
 int ensure_partials(Device* d, int64_t count);
+constexpr int kDotChunkElems = 4096;    // elements per chunk of the fixed-order reductions
 
 // ---- rule launchers (gm_rules.cu) ----
 void lbfgs_release_device(Device* d);           // frees the L-BFGS pointer tables cached for a device
-int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win = Window());
+// clip: device address of the global-norm clipping coefficient every gradient is multiplied
+// by first (nullptr: gradients are used as they are)
+int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win = Window(),
+                const float* clip = nullptr);
 // Applies a window to a list's descriptor; GM_ERR_BAD_ARG when it lies outside the list.
 int apply_window(const TensorList* l, Window win, DevList* out);
 

@@ -35,6 +35,7 @@ struct Mixed {
     unsigned int* d_flag = nullptr;        // [0] overflow flag, [1] update ticket, [2] check ticket, [3] sum-of-squares
                                            // accumulator, [16..19] StepPrep, [24] last step's sum of squares
     int want_norm = 0;
+    float max_norm = 0.0f;                 // > 0: global-norm clipping with this limit
     float2* d_table = nullptr;             // [table_len+1] {1-b1^t, 1-b2^t}
     int table_len = 0;
     bool saturated = false;                // table[table_len] == {1,1}: later steps reuse it
@@ -96,7 +97,35 @@ __device__ __forceinline__ unsigned nonfinite_mask(unsigned w) {
 
 // What the update kernel needs to know about the step, written once by the
 // check kernel so that every update CTA starts with a single 16-byte load.
-struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; };
+// r1, r2: reciprocals of the bias corrections; fast: both corrections qualify for div_const;
+// clip: the global-norm clipping coefficient of this step (1 when clipping is off).
+struct StepPrep { unsigned overflow; float inv_scale; float bc1; float bc2; float r1; float r2; float clip; unsigned fast; };
+
+__device__ __forceinline__ void publish_prep(StepPrep* prep, unsigned overflow, float scale, float2 bc, float clip) {
+    StepPrep sp;
+    sp.overflow = overflow;
+    sp.inv_scale = dvd(1.0f, scale);
+    sp.bc1 = bc.x;
+    sp.bc2 = bc.y;
+    sp.r1 = dvd(1.0f, bc.x);
+    sp.r2 = dvd(1.0f, bc.y);
+    sp.clip = clip;
+    sp.fast = (const_div_ok(bc.x) && const_div_ok(bc.y)) ? 1u : 0u;
+    *prep = sp;
+}
+
+// acc + (half * inv)^2, the square rounded before the add: the order-defined form the
+// deterministic gradient norm uses.
+__device__ __forceinline__ float sq_acc1(const unsigned short h, const float inv, float acc) {
+    const float a = mul(__half2float(__ushort_as_half(h)), inv);
+    return add(acc, mul(a, a));
+}
+__device__ __forceinline__ float sq_acc2(const unsigned x, const float inv, float acc) {
+    return sq_acc1((unsigned short)(x >> 16), inv, sq_acc1((unsigned short)(x & 0xffffu), inv, acc));
+}
+__device__ __forceinline__ float sq_acc8(const uint4 v, const float inv, float acc) {
+    return sq_acc2(v.w, inv, sq_acc2(v.z, inv, sq_acc2(v.y, inv, sq_acc2(v.x, inv, acc))));
+}
 
 // acc + the squares of the two halves packed in x, each first multiplied by inv.
 __device__ __forceinline__ float sumsq2(const unsigned x, const float inv, float acc) {
@@ -113,13 +142,23 @@ __device__ __forceinline__ float sumsq1(const unsigned short h, const float inv,
     return fmaf(a, a, acc);
 }
 
-// NORM: the same pass also accumulates the sum of squares of the unscaled
-// gradients (warp shuffle tree, one float atomic per CTA); the last CTA moves the
-// total to flag[24] and clears the accumulator flag[3].
+// NORM: the same pass also takes the sum of squares of the unscaled gradients, in a
+// fixed order and without float atomics: per chunk, lane t of 256 adds the squares of
+// the vectors t, t+256, ... it loaded (eight halves each, in memory order), then the
+// element it owns in front of the tensor's first 16-byte boundary (first chunk only),
+// then the element it owns behind the last whole vector; the lane values combine as in
+// cta_sum_256 into partials[chunk]; the CTA that finishes last adds the chunk sums (lane
+// t takes chunks t, t+256, ...) and leaves the total in flag[24] and, when max_norm > 0,
+// the clipping coefficient min(1, max_norm / (sqrt(total) + 1e-6)) in flag[25] and in the
+// published scalars.  The order follows the list's chunking, hence the tensors' offsets
+// from a 16-byte boundary: the same layout always gives the same bits.
 template <bool NORM>
 __global__ void __launch_bounds__(kApplyThreads, NORM ? 6 : 8)
 mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_loss_scale_t* __restrict__ state,
-                   const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g) {
+                   const float2* __restrict__ table, int table_len, StepPrep* __restrict__ prep, const int keep_g,
+                   float* __restrict__ partials, const float max_norm) {
+    __shared__ float warp_ss[kApplyThreads / 32];
+    __shared__ int is_last;
     // flags bit 0: the gradients get the evict_last L2 policy (the update kernel reads them
     // again); bit 1: an update kernel launched with programmatic stream serialization may
     // become resident from the start of this grid, else from the point where its CTAs have
@@ -132,8 +171,7 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
     const int tid = threadIdx.x;
     const long long chunk = L.chunk_elems;
     unsigned bad = 0;
-    float ss = 0.0f;
-    const float inv = NORM ? 1.0f / state->scale : 0.0f;
+    const float inv = NORM ? dvd(1.0f, state->scale) : 0.0f;
 
     // Each CTA walks chunks blockIdx.x, blockIdx.x + gridDim.x, ...  The table
     // lookups of the next chunk are issued while the current chunk's loads are in
@@ -171,78 +209,79 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
         Ref nxt{};
         if (cn < L.num_chunks) nxt = lookup(cn);
         const unsigned short* g = cur.g;
+        float ss = 0.0f;
         if (cur.h < 0) {
             // streams off a common 16-byte boundary: element by element
             for (long long i = cur.b + tid; i < cur.e; i += NT) {
                 bad |= ((g[i] & 0x7c00u) == 0x7c00u);
-                if (NORM) ss = sumsq1(g[i], inv, ss);
+                if (NORM) ss = sq_acc1(g[i], inv, ss);
             }
         } else {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
-                if (NORM) ss = sumsq8(v[u], inv, ss);                       // lanes past the end hold zeros
+                if (NORM) ss = sq_acc8(v[u], inv, ss);                      // lanes past the end hold zeros
             }
             const long long nvec = (cur.e - cur.b) >> 3;
             const uint4* q = reinterpret_cast<const uint4*>(g + cur.b);
             for (long long i = tid + (long long)U * NT; i < nvec; i += NT) {      // chunks larger than U*NT vectors
                 const uint4 w = ld_l2(q + i, pol);
                 bad |= nonfinite_mask(w.x) | nonfinite_mask(w.y) | nonfinite_mask(w.z) | nonfinite_mask(w.w);
-                if (NORM) ss = sumsq8(w, inv, ss);
+                if (NORM) ss = sq_acc8(w, inv, ss);
             }
             if (cur.k == 0 && tid < cur.h) {                                         // elements before the boundary
                 bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
-                if (NORM) ss = sumsq1(g[tid], inv, ss);
+                if (NORM) ss = sq_acc1(g[tid], inv, ss);
             }
             const long long tb = cur.b + (nvec << 3);
             if (tb + tid < cur.e) {                                                  // fewer than 8 after the last vector
                 bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
-                if (NORM) ss = sumsq1(g[tb + tid], inv, ss);
+                if (NORM) ss = sq_acc1(g[tb + tid], inv, ss);
             }
         }
-        if (cn < L.num_chunks) issue(nxt);
+        if (cn < L.num_chunks) issue(nxt);                                           // in flight during the reduction below
+        if (NORM) {
+            const float total = cta_sum_256(ss, warp_ss);
+            if (tid == 0) partials[c] = total;
+        }
         c = cn;
         cur = nxt;
     }
     if (!(keep_g & 2)) asm volatile("griddepcontrol.launch_dependents;");
-    // warp vote, then one atomic for the whole CTA (and only when needed)
-    if (NORM) {
-        __shared__ float warp_ss[NT / 32];
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-        if ((tid & 31) == 0) warp_ss[tid >> 5] = ss;
-        __syncthreads();
-        if (tid == 0) {
-            float total = 0.0f;
-#pragma unroll
-            for (int w = 0; w < NT / 32; ++w) total += warp_ss[w];
-            atomicAdd(reinterpret_cast<float*>(flag + 3), total);
-        }
-    }
+    // block vote, then one atomic for the whole CTA (and only when needed)
     const int any_bad = __syncthreads_or(bad != 0);
     if (tid == 0) {
         if (any_bad) atomicOr(flag, 1u);
         __threadfence();
         const unsigned ticket = atomicAdd(flag + 2, 1u);
-        if (ticket == gridDim.x - 1) {
-            // last CTA: every vote is in; publish the step's scalars
-            __threadfence();
-            const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
-            const float scale = state->scale;
-            const int tstep = state->adam_t + 1;
-            const float2 bc = table[tstep < table_len ? tstep : table_len];
-            StepPrep sp;
-            sp.overflow = overflow;
-            sp.inv_scale = dvd(1.0f, scale);
-            sp.bc1 = bc.x;
-            sp.bc2 = bc.y;
-            *prep = sp;
-            flag[2] = 0u;
-            if (NORM) {
-                flag[24] = *reinterpret_cast<volatile unsigned int*>(flag + 3);
-                flag[3] = 0u;
+        is_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    // last CTA: every vote and every chunk sum is in; publish the step's scalars
+    __threadfence();
+    float total = 0.0f;
+    if (NORM) {
+        float acc = 0.0f;
+        const volatile float* pv = partials;
+        for (int k = tid; k < L.num_chunks; k += NT) acc = add(acc, pv[k]);
+        total = cta_sum_256(acc, warp_ss);
+    }
+    if (tid == 0) {
+        const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
+        const int tstep = state->adam_t + 1;
+        const float2 bc = table[tstep < table_len ? tstep : table_len];
+        float clip = 1.0f;
+        if (NORM) {
+            if (max_norm > 0.0f) {
+                clip = dvd(max_norm, add(root(total), 1e-6f));
+                if (!(clip < 1.0f)) clip = 1.0f;
             }
+            flag[24] = __float_as_uint(total);
+            flag[25] = __float_as_uint(clip);
         }
+        publish_prep(prep, overflow, state->scale, bc, clip);
+        flag[2] = 0u;
     }
 }
 
@@ -267,20 +306,17 @@ __global__ void mixed_prep_kernel(const unsigned int* __restrict__ flag, const g
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     const int tstep = state->adam_t + 1;
     const float2 bc = table[tstep < table_len ? tstep : table_len];
-    StepPrep sp;
-    sp.overflow = flag[0] != 0u ? 1u : 0u;
-    sp.inv_scale = dvd(1.0f, state->scale);
-    sp.bc1 = bc.x;
-    sp.bc2 = bc.y;
-    *prep = sp;
+    publish_prep(prep, flag[0] != 0u ? 1u : 0u, state->scale, bc, 1.0f);
 }
 
 struct MixedScalars { float lr, beta1, beta2, omb1, omb2, eps, wd; int use_wd; };
 
-__device__ __forceinline__ void mixed_elem(float g16_as_f32, float inv_scale, float& w, float& m, float& v,
+template <bool FAST, bool CLIP>
+__device__ __forceinline__ void mixed_elem(float g16_as_f32, float inv_scale, float clip, float& w, float& m, float& v,
                                            unsigned short& p16, const AdamRule::P& p) {
     float x[4] = {w, mul(g16_as_f32, inv_scale), m, v};
-    AdamRule::elem(x, p);
+    if (CLIP) x[1] = mul(x[1], clip);
+    AdamRule::elem_t<FAST>(x, p);
     w = x[0]; m = x[2]; v = x[3];
     p16 = __half_as_ushort(__float2half_rn(x[0]));
 }
@@ -300,7 +336,12 @@ __device__ __forceinline__ void st256(float* p, const F8& r) {
                  :: "l"(p), "f"(r.v[0]), "f"(r.v[1]), "f"(r.v[2]), "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]), "f"(r.v[7]) : "memory");
 }
 
-template <bool WIDE, int MINB>
+// WIDE: 8 elements per thread per pass with 256-bit fp32 accesses (else 4 with a software
+// prefetch).  FAST: the divisions by the two bias corrections use div_const when the
+// published scalars allow it.  PF: while a pass is computed, the lines of the next pass
+// are requested into L2 (no registers held).  CLIP: gradients are multiplied by the
+// published clipping coefficient.
+template <bool WIDE, int MINB, bool FAST, bool PF, bool CLIP>
 __global__ void __launch_bounds__(kApplyThreads, MINB)
 mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
                     const StepPrep* __restrict__ prep, const MixedScalars sc) {
@@ -332,14 +373,18 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
     // The step's scalars were published by the check kernel; the loss-scale
     // state itself is only rewritten by the CTA that finishes last.
     const uint4 raw = *reinterpret_cast<const uint4*>(prep);
+    const uint4 raw2 = *(reinterpret_cast<const uint4*>(prep) + 1);
     const unsigned overflow = raw.x;
 
     if (!overflow) {
         AdamRule::P p;
         p.lr = sc.lr; p.beta1 = sc.beta1; p.beta2 = sc.beta2; p.omb1 = sc.omb1; p.omb2 = sc.omb2;
         p.bc1 = __uint_as_float(raw.z); p.bc2 = __uint_as_float(raw.w);
+        p.rbc1 = __uint_as_float(raw2.x); p.rbc2 = __uint_as_float(raw2.y);
         p.eps = sc.eps; p.wd = sc.wd; p.use_wd = sc.use_wd;
         const float inv_scale = __uint_as_float(raw.y);
+        const float clip = __uint_as_float(raw2.z);
+        const bool fast = FAST && raw2.w != 0u;           // uniform over the grid
 
         for (int c = blockIdx.x; c < L.num_chunks; c += gridDim.x) {
             const int2 rec = __ldg(L.chunk_rec + c);
@@ -355,7 +400,7 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
             auto scalar_at = [&](long long i) {
                 float wi = w[i], mi = m[i], vi = v[i];
                 unsigned short pi;
-                mixed_elem(half_bits_to_float(g[i]), inv_scale, wi, mi, vi, pi, p);
+                mixed_elem<false, CLIP>(half_bits_to_float(g[i]), inv_scale, clip, wi, mi, vi, pi, p);
                 w[i] = wi; m[i] = mi; v[i] = vi; o[i] = pi;
             };
 
@@ -385,14 +430,32 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                 for (int i = tid; i < nv8; i += NT) {
                     const uint4 gc = __ldcs(gq8 + i);
                     F8 W = ld256(w + b + 8LL * i), M = ld256(m + b + 8LL * i), V = ld256(v + b + 8LL * i);
+                    if (PF && i + NT < nv8 && (tid & 3) == 0) {
+                        // four threads share a 128-byte line of each fp32 stream: one of them asks for
+                        // the line the four will load in the next pass
+                        const long long nx = b + 8LL * (i + NT);
+                        asm volatile("prefetch.global.L2 [%0];" :: "l"(w + nx));
+                        asm volatile("prefetch.global.L2 [%0];" :: "l"(m + nx));
+                        asm volatile("prefetch.global.L2 [%0];" :: "l"(v + nx));
+                    }
                     const unsigned gw[4] = {gc.x, gc.y, gc.z, gc.w};
                     unsigned ow[4];
+                    if (fast) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        unsigned short lo, hi;
-                        mixed_elem(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, W.v[2 * j], M.v[2 * j], V.v[2 * j], lo, p);
-                        mixed_elem(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, W.v[2 * j + 1], M.v[2 * j + 1], V.v[2 * j + 1], hi, p);
-                        ow[j] = (unsigned)lo | ((unsigned)hi << 16);
+                        for (int j = 0; j < 4; ++j) {
+                            unsigned short lo, hi;
+                            mixed_elem<true, CLIP>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, clip, W.v[2 * j], M.v[2 * j], V.v[2 * j], lo, p);
+                            mixed_elem<true, CLIP>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, clip, W.v[2 * j + 1], M.v[2 * j + 1], V.v[2 * j + 1], hi, p);
+                            ow[j] = (unsigned)lo | ((unsigned)hi << 16);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            unsigned short lo, hi;
+                            mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, clip, W.v[2 * j], M.v[2 * j], V.v[2 * j], lo, p);
+                            mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, clip, W.v[2 * j + 1], M.v[2 * j + 1], V.v[2 * j + 1], hi, p);
+                            ow[j] = (unsigned)lo | ((unsigned)hi << 16);
+                        }
                     }
                     st256(w + b + 8LL * i, W); st256(m + b + 8LL * i, M); st256(v + b + 8LL * i, V);
                     __stcs(oq8 + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
@@ -418,10 +481,10 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                 uint2 gn; float4 wn, mn, vn;
                 if (nx < nvec) { gn = __ldcs(gq + nx); wn = __ldcs(wq + nx); mn = __ldcs(mq + nx); vn = __ldcs(vq + nx); }
                 unsigned short h0, h1, h2, h3;
-                mixed_elem(half_bits_to_float((unsigned short)(gc.x & 0xffffu)), inv_scale, wc.x, mc.x, vc.x, h0, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gc.x >> 16)), inv_scale, wc.y, mc.y, vc.y, h1, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gc.y & 0xffffu)), inv_scale, wc.z, mc.z, vc.z, h2, p);
-                mixed_elem(half_bits_to_float((unsigned short)(gc.y >> 16)), inv_scale, wc.w, mc.w, vc.w, h3, p);
+                mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.x & 0xffffu)), inv_scale, clip, wc.x, mc.x, vc.x, h0, p);
+                mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.x >> 16)), inv_scale, clip, wc.y, mc.y, vc.y, h1, p);
+                mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.y & 0xffffu)), inv_scale, clip, wc.z, mc.z, vc.z, h2, p);
+                mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.y >> 16)), inv_scale, clip, wc.w, mc.w, vc.w, h3, p);
                 __stcs(wq + i, wc); __stcs(mq + i, mc); __stcs(vq + i, vc);
                 __stcs(oq + i, make_uint2((unsigned)h0 | ((unsigned)h1 << 16), (unsigned)h2 | ((unsigned)h3 << 16)));
                 gc = gn; wc = wn; mc = mn; vc = vn;
@@ -550,15 +613,26 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     MixedScalars sc;
     sc.lr = lr; sc.beta1 = m->beta1; sc.beta2 = m->beta2; sc.omb1 = 1.0f - m->beta1; sc.omb2 = 1.0f - m->beta2;
     sc.eps = eps; sc.wd = wd; sc.use_wd = wd > 0.0f ? 1 : 0;
+    const bool clipping = m->max_norm > 0.0f;
+    if (clipping && hook) {
+        set_error("clipping is not available in the sharded mixed-precision step: the norm would cover one rank's shard only");
+        return GM_ERR_UNSUPPORTED;
+    }
+    const bool norm = m->want_norm || clipping;
+    if (norm) {
+        const int rc = ensure_partials(d, l->dl.num_chunks);
+        if (rc != GM_OK) return rc;
+    }
     DeviceGuard g(d);
     int grid_c = check_grid(d, l->dl.num_chunks);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
-    if (m->want_norm)
-        mixed_check_kernel<true><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                          m->table_len, prep, (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0));
+    const int check_flags = (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0);
+    if (norm)
+        mixed_check_kernel<true><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table, m->table_len,
+                                                                          prep, check_flags, d->partials, clipping ? m->max_norm : 0.0f);
     else
-        mixed_check_kernel<false><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table,
-                                                                           m->table_len, prep, (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0));
+        mixed_check_kernel<false><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table, m->table_len,
+                                                                           prep, check_flags, nullptr, 0.0f);
     d->launches++;
     if (hook) {
         int rc = hook(ctx, m->d_flag);
@@ -567,10 +641,26 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         d->launches++;
     }
     using UpdateFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, const StepPrep*, const MixedScalars);
-    // 8 elements per thread with 256-bit fp32 accesses measured 2.2 % ahead of 4 elements per
-    // thread with a software prefetch (136.0 vs 139.2 us on the 25 M-parameter list); the
-    // latter stays selectable for comparison
-    UpdateFn update = d->mixed_variant == 1 ? mixed_update_kernel<false, 4> : mixed_update_kernel<true, 4>;
+    // Variant 0 (default): 8 elements per thread with 256-bit fp32 accesses, the divisions by the
+    // bias corrections through div_const, next-pass L2 prefetch.  GOMETAL_MIXED_FASTDIV=0 and
+    // GOMETAL_MIXED_PF=0 switch the last two off; GOMETAL_MIXED_VARIANT=1 selects the older
+    // 4-elements-per-thread kernel with a software prefetch.  All produce the same bits.
+    UpdateFn update;
+    if (d->mixed_variant == 1) {
+        update = clipping ? mixed_update_kernel<false, 4, false, false, true> : mixed_update_kernel<false, 4, false, false, false>;
+    } else {
+        const int sel = (d->mixed_fastdiv ? 1 : 0) | (d->mixed_pf ? 2 : 0) | (clipping ? 4 : 0);
+        switch (sel) {
+            case 0: update = mixed_update_kernel<true, 4, false, false, false>; break;
+            case 1: update = mixed_update_kernel<true, 4, true, false, false>; break;
+            case 2: update = mixed_update_kernel<true, 4, false, true, false>; break;
+            case 3: update = mixed_update_kernel<true, 4, true, true, false>; break;
+            case 4: update = mixed_update_kernel<true, 4, false, false, true>; break;
+            case 5: update = mixed_update_kernel<true, 4, true, false, true>; break;
+            case 6: update = mixed_update_kernel<true, 4, false, true, true>; break;
+            default: update = mixed_update_kernel<true, 4, true, true, true>; break;
+        }
+    }
     int grid_u = launch_grid(d, (const void*)update, kApplyThreads, l->dl.num_chunks);
     if (!hook && d->mixed_overlap) {
         // the update grid may become resident while the check grid drains
@@ -688,12 +778,35 @@ int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable) {
     return GM_OK;
 }
 
+int gm_mixed_set_clip(uintptr_t mixed, float max_norm) {
+    Mixed* m = as_mixed(mixed);
+    if (!m) return GM_ERR_BAD_ARG;
+    if (!(max_norm >= 0.0f) || !isfinite(max_norm)) { set_error("max_norm %g must be finite and >= 0 (0 turns clipping off)", (double)max_norm); return GM_ERR_BAD_ARG; }
+    m->max_norm = max_norm;
+    return GM_OK;
+}
+
+int gm_mixed_last_clip(uintptr_t device_ptr, uintptr_t mixed, float* out_sumsq, float* out_coef) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    Mixed* m = as_mixed(mixed);
+    if (!m || !out_sumsq || !out_coef) { if (m) set_error("output is nil"); return GM_ERR_BAD_ARG; }
+    if (!(m->max_norm > 0.0f) && !m->want_norm) { set_error("neither clipping nor the gradient norm is enabled on this state"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    float two[2];
+    GM_CUDA_CHECK(cudaMemcpy(two, m->d_flag + 24, sizeof(two), cudaMemcpyDeviceToHost));
+    *out_sumsq = two[0];
+    *out_coef = two[1];
+    return GM_OK;
+}
+
 int gm_mixed_last_grad_sumsq(uintptr_t device_ptr, uintptr_t mixed, float* out) {
     Device* d = as_device(device_ptr);
     if (!d) return GM_ERR_NIL_DEVICE;
     Mixed* m = as_mixed(mixed);
     if (!m || !out) { if (m) set_error("output is nil"); return GM_ERR_BAD_ARG; }
-    if (!m->want_norm) { set_error("the gradient norm is not enabled on this mixed-precision state"); return GM_ERR_BAD_ARG; }
+    if (!m->want_norm && !(m->max_norm > 0.0f)) { set_error("the gradient norm is not enabled on this mixed-precision state"); return GM_ERR_BAD_ARG; }
     DeviceGuard g(d);
     GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
     GM_CUDA_CHECK(cudaMemcpy(out, m->d_flag + 24, sizeof(float), cudaMemcpyDeviceToHost));

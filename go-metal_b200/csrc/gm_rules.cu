@@ -143,7 +143,7 @@ int apply_window(const TensorList* l, Window win, DevList* out) {
     return GM_OK;
 }
 
-int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win) {
+int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, Window win, const float* clip) {
     DeviceGuard guard(d);
     const int use_wd = h.weight_decay > 0.0f ? 1 : 0;
     switch (rule) {
@@ -155,7 +155,8 @@ int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, W
             p.bc2 = 1.0f - powf(h.beta2, (float)h.step);
             p.omb1 = 1.0f - h.beta1;
             p.omb2 = 1.0f - h.beta2;
-            return launch_apply<AdamRule>(d, l, p, win);
+            p.rbc1 = 0.0f; p.rbc2 = 0.0f;
+            return launch_apply<AdamRule>(d, l, p, win, clip);
         }
         case GM_RULE_NADAM: {
             if (h.step < 1) { set_error("NAdam step count %d must be >= 1", h.step); return GM_ERR_BAD_ARG; }
@@ -167,13 +168,13 @@ int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, W
             p.omb2 = 1.0f - h.beta2;
             p.mu_next = h.beta1 * (1.0f - 0.5f * powf(0.96f, (float)(h.step + 1) * 0.004f));
             p.om_mu = 1.0f - p.mu_next;
-            return launch_apply<NadamRule>(d, l, p, win);
+            return launch_apply<NadamRule>(d, l, p, win, clip);
         }
         case GM_RULE_SGD: {
             SgdScalars p;
             p.lr = h.lr; p.momentum = h.beta1; p.wd = h.weight_decay; p.use_wd = use_wd; p.nesterov = h.nesterov ? 1 : 0;
-            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule>(d, l, p, win);
-            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule>(d, l, p, win);
+            if (l->dl.num_streams == 3 && h.beta1 > 0.0f) return launch_apply<SgdMomentumRule>(d, l, p, win, clip);
+            if (l->dl.num_streams == 2) return launch_apply<SgdPlainRule>(d, l, p, win, clip);
             set_error("SGD needs streams w,g (momentum==0) or w,g,mom (momentum>0); got %d streams, momentum %g",
                       l->dl.num_streams, (double)h.beta1);
             return GM_ERR_BAD_ARG;
@@ -183,20 +184,20 @@ int launch_rule(Device* d, int rule, const TensorList* l, const gm_hyper_t& h, W
             p.lr = h.lr; p.alpha = h.beta1; p.oma = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay;
             p.momentum = h.momentum; p.use_wd = use_wd;
             const bool mom = h.momentum > 0.0f, cen = h.centered != 0;
-            if (mom && cen) return launch_apply<RmsPropRule<true, true>>(d, l, p, win);
-            if (mom) return launch_apply<RmsPropRule<true, false>>(d, l, p, win);
-            if (cen) return launch_apply<RmsPropRule<false, true>>(d, l, p, win);
-            return launch_apply<RmsPropRule<false, false>>(d, l, p, win);
+            if (mom && cen) return launch_apply<RmsPropRule<true, true>>(d, l, p, win, clip);
+            if (mom) return launch_apply<RmsPropRule<true, false>>(d, l, p, win, clip);
+            if (cen) return launch_apply<RmsPropRule<false, true>>(d, l, p, win, clip);
+            return launch_apply<RmsPropRule<false, false>>(d, l, p, win, clip);
         }
         case GM_RULE_ADAGRAD: {
             AdaGradRule::P p;
             p.lr = h.lr; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaGradRule>(d, l, p, win);
+            return launch_apply<AdaGradRule>(d, l, p, win, clip);
         }
         case GM_RULE_ADADELTA: {
             AdaDeltaRule::P p;
             p.rho = h.beta1; p.omr = 1.0f - h.beta1; p.eps = h.eps; p.wd = h.weight_decay; p.use_wd = use_wd;
-            return launch_apply<AdaDeltaRule>(d, l, p, win);
+            return launch_apply<AdaDeltaRule>(d, l, p, win, clip);
         }
         default:
             set_error("unknown rule %d", rule);

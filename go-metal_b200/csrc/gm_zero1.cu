@@ -470,6 +470,7 @@ static int push_launch(Zero1* z, const TensorList* l, const gm_hyper_t& hyper, W
     p.bc2 = 1.0f - powf(hyper.beta2, (float)hyper.step);
     p.omb1 = 1.0f - hyper.beta1;
     p.omb2 = 1.0f - hyper.beta2;
+    p.rbc1 = 0.0f; p.rbc2 = 0.0f;
     DevList dl;
     const int rc = apply_window(l, win, &dl);
     if (rc != GM_OK) return rc;

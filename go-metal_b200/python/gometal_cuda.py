@@ -98,6 +98,12 @@ _SIGS = {
     "gm_tensor_list_destroy": (None, [u]),
     "gm_tensor_list_total": (i64, [u]),
     "gm_tensor_list_num_chunks": (i, [u]),
+    "gm_tensor_list_chunk_elems": (i, [u]),
+    "gm_tensor_list_head": (i, [u, i]),
+    "gm_grad_clip_coef_async": (i, [u, u, f, u]),
+    "gm_step_clipped_async": (i, [u, i, u, C.POINTER(Hyper), u]),
+    "gm_step_with_clip_async": (i, [u, i, u, C.POINTER(Hyper), f]),
+    "gm_last_clip": (i, [u, C.POINTER(f)]),
     "gm_step_async": (i, [u, i, u, C.POINTER(Hyper)]),
     "gm_step_timed": (i, [u, i, u, C.POINTER(Hyper), C.POINTER(f)]),
     "gm_step_host": (i, [u, i, u, C.POINTER(Hyper), vp, vp, i]),
@@ -109,6 +115,8 @@ _SIGS = {
     "gm_mixed_state_device_ptr": (u, [u]),
     "gm_mixed_enable_grad_norm": (i, [u, i]),
     "gm_mixed_last_grad_sumsq": (i, [u, u, C.POINTER(f)]),
+    "gm_mixed_set_clip": (i, [u, f]),
+    "gm_mixed_last_clip": (i, [u, u, C.POINTER(f), C.POINTER(f)]),
     "gm_grad_sumsq_async": (i, [u, u, i, f, u]),
     "gm_lbfgs_set_mode": (i, [u, i]),
     "gm_dot_canonical": (i, [u, u, u, i64, C.POINTER(f)]),
@@ -127,6 +135,7 @@ _SIGS = {
     "gm_zero1_adam_dma_step_async": (i, [u, u, C.POINTER(Hyper), i]),
     "gm_zero1_mixed_step_async": (i, [u, u, u, f, f, f, u, i64]),
     "gm_zero1_reduce_scatter_async": (i, [u, u, i64, i]),
+    "gm_selftest_const_div": (i, [u, f, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), ip]),
     "gm_timer_start": (i, [u]),
     "gm_timer_stop": (i, [u, C.POINTER(f)]),
 }

@@ -199,6 +199,11 @@ uintptr_t gm_tensor_list_create(uintptr_t device_ptr, int num_streams, int num_t
 void gm_tensor_list_destroy(uintptr_t list);
 int64_t gm_tensor_list_total(uintptr_t list);
 int gm_tensor_list_num_chunks(uintptr_t list);
+int gm_tensor_list_chunk_elems(uintptr_t list);      /* elements per chunk of this list */
+/* Elements of tensor `tensor` in front of the first address at which every stream of
+ * the tensor is 16-byte aligned; -1 when the streams share no such address (that
+ * tensor is then walked element by element); -2 on a bad handle or index. */
+int gm_tensor_list_head(uintptr_t list, int tensor);
 
 /* Optimizer rule selector for gm_step_async(). */
 enum {
@@ -250,19 +255,45 @@ int gm_mixed_set_state(uintptr_t device_ptr, uintptr_t mixed, const gm_loss_scal
 uintptr_t gm_mixed_state_device_ptr(uintptr_t mixed);   /* device address of the gm_loss_scale_t */
 /* Gradient norm from the overflow-check pass itself (no extra pass over the
  * gradients): when enabled, every step also leaves sum((g16 / scale)^2) over the
- * list, accumulated in fp32 with one float atomic per CTA (so the last bits vary
- * from run to run; inf or NaN on an overflow step).  gm_mixed_last_grad_sumsq
- * waits for the stream and returns the last step's value.  Under
- * gm_zero1_mixed_step_async the value covers the rank's own shard.  No
- * counterpart in the reference, which has no clipping or norm. */
+ * list (inf or NaN on an overflow step).  The sum is taken in a fixed order without
+ * float atomics -- per chunk of the list a fixed lane walk and xor tree, chunk sums
+ * added by the CTA that finishes last -- so a given memory layout (sizes and each
+ * tensor's offset from a 16-byte boundary, see gm_tensor_list_head) always gives the
+ * same bits.  gm_mixed_last_grad_sumsq waits for the stream and returns the last
+ * step's value.  Under gm_zero1_mixed_step_async the value covers the rank's own
+ * shard.  No counterpart in the reference, which has no clipping or norm.
+ * gm_mixed_set_clip(max_norm > 0) turns on global-norm clipping: the same pass forms
+ * coef = min(1, max_norm / (sqrt(sum) + 1e-6)) on the device and the update multiplies
+ * every unscaled gradient by it (one rounding) before the Adam rule; 0 turns it off.
+ * Not available in the sharded step.  gm_mixed_last_clip returns the last step's sum
+ * and coefficient. */
 int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable);
 int gm_mixed_last_grad_sumsq(uintptr_t device_ptr, uintptr_t mixed, float* out);
+int gm_mixed_set_clip(uintptr_t mixed, float max_norm);
+int gm_mixed_last_clip(uintptr_t device_ptr, uintptr_t mixed, float* out_sumsq, float* out_coef);
 
 /* ---- gradient norm (sum of squares; one float atomic per CTA) ---- */
 /* list stream 0 is the gradient (4 B or 2 B elements).  *out_sumsq is a
  * device float the kernel accumulates into after zeroing it. */
 int gm_grad_sumsq_async(uintptr_t device_ptr, uintptr_t list, int elem_bytes, float inv_scale,
                         uintptr_t out_sumsq_device);
+
+/* ---- deterministic gradient norm and global-norm clipping (fp32 rules) ----
+ * No counterpart in the reference (docs/guides/optimizers.md:568-569 names the concept).
+ * gm_grad_clip_coef_async leaves {sum g^2, coef, norm} (three floats) at out3_device, with
+ * coef = min(1, max_norm / (sqrt(sum g^2) + 1e-6)) computed in binary32 on the device; the
+ * gradients are stream 1 of the list.  The sum uses the library's fixed order (4096-element
+ * chunks from element 0 of each tensor, fixed lane walk, xor tree, chunk sums added by the
+ * CTA that finishes last), no float atomics: the same gradients give the same bits whatever
+ * the grid or the addresses.  gm_step_clipped_async is gm_step_async with every gradient
+ * multiplied by the float at coef_device first (one rounding).  gm_step_with_clip_async
+ * chains the two on the device's stream; gm_last_clip waits and returns its three floats. */
+int gm_grad_clip_coef_async(uintptr_t device_ptr, uintptr_t list, float max_norm, uintptr_t out3_device);
+int gm_step_clipped_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
+                          uintptr_t coef_device);
+int gm_step_with_clip_async(uintptr_t device_ptr, int rule, uintptr_t list, const gm_hyper_t* hyper,
+                            float max_norm);
+int gm_last_clip(uintptr_t device_ptr, float* out3);
 
 /* ---- L-BFGS controls ---- */
 /* mode is a bit set.  Bit 0: y[prev] = g - old_g is formed before old_g is
@@ -339,6 +370,17 @@ int gm_zero1_mixed_step_async(uintptr_t zero1, uintptr_t mixed, uintptr_t shard_
 /* Gradient hand-off of data-parallel training: in-place reduce-scatter (sum) of
  * the full gradient arena; afterwards rank r's shard holds the sum over ranks. */
 int gm_zero1_reduce_scatter_async(uintptr_t zero1, uintptr_t grad_arena_base, int64_t count_per_rank, int elem_bytes);
+
+/* ---- self-check ----
+ * The mixed-precision update divides by the two Adam bias corrections, which are the
+ * same for every element of a step, with a five-instruction sequence built on the
+ * correctly rounded reciprocal instead of the general IEEE division; it must give the
+ * same bits.  This entry compares the two on the GPU over all 2^32 values of the
+ * dividend for one divisor c and reports how many differ (and the first such bit
+ * pattern, 0xffffffff if none).  *fast_path_allowed is 0 when c lies outside the range
+ * the library enables the sequence for (it then uses the IEEE division). */
+int gm_selftest_const_div(uintptr_t device_ptr, float c, uint64_t* mismatches, uint32_t* first_bad_bits,
+                          int* fast_path_allowed);
 
 /* ---- timing on the device's stream (CUDA events) ---- */
 int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */
