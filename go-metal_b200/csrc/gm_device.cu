@@ -162,6 +162,8 @@ static Device* make_device(int ordinal) {
     if (const char* e8 = getenv("GOMETAL_MIXED_VARIANT")) d->mixed_variant = atoi(e8);
     if (const char* e = getenv("GOMETAL_MIXED_FASTDIV")) d->mixed_fastdiv = atoi(e);
     if (const char* e = getenv("GOMETAL_MIXED_PF")) d->mixed_pf = atoi(e);
+    if (const char* e = getenv("GOMETAL_MIXED_RING")) d->mixed_ring = atoi(e);
+    if (const char* e = getenv("GOMETAL_BARRIER_BUDGET_CYCLES")) { const long long v = atoll(e); if (v > 0) d->barrier_budget_cycles = v; }
     if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);
     if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);
     // A blocking stream on purpose: the synchronous copies of the drop-in ABI
@@ -567,6 +569,37 @@ int gm_device_synchronize_timeout(uintptr_t h, int timeout_ms) {
         }
         if (++spins > 200) std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
+}
+
+// Launch-strategy switches of a device handle (the GOMETAL_* environment variables set
+// the same fields when the handle is created).  Every setting computes the same bits.
+int gm_device_set_tuning(uintptr_t h, const char* name, long long value) {
+    Device* d = as_device(h);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!name) { set_error("name is nil"); return GM_ERR_BAD_ARG; }
+    const std::string n(name);
+    if (n == "mixed_ring") { if (value < 0 || value > 2) { set_error("mixed_ring is 0, 1 or 2"); return GM_ERR_BAD_ARG; } d->mixed_ring = (int)value; }
+    else if (n == "mixed_fastdiv") d->mixed_fastdiv = value ? 1 : 0;
+    else if (n == "mixed_pf") d->mixed_pf = value ? 1 : 0;
+    else if (n == "mixed_variant") d->mixed_variant = value ? 1 : 0;
+    else if (n == "lbfgs_coop") d->lbfgs_coop = value ? 1 : 0;
+    else if (n == "barrier_budget_cycles") { if (value <= 0) { set_error("the budget must be positive"); return GM_ERR_BAD_ARG; } d->barrier_budget_cycles = value; }
+    else { set_error("unknown tuning name '%s'", name); return GM_ERR_BAD_ARG; }
+    return GM_OK;
+}
+
+long long gm_device_get_tuning(uintptr_t h, const char* name) {
+    Device* d = as_device(h);
+    if (!d || !name) return -1;
+    const std::string n(name);
+    if (n == "mixed_ring") return d->mixed_ring;
+    if (n == "mixed_fastdiv") return d->mixed_fastdiv;
+    if (n == "mixed_pf") return d->mixed_pf;
+    if (n == "mixed_variant") return d->mixed_variant;
+    if (n == "lbfgs_coop") return d->lbfgs_coop;
+    if (n == "barrier_budget_cycles") return d->barrier_budget_cycles;
+    set_error("unknown tuning name '%s'", name);
+    return -1;
 }
 
 int gm_timer_start(uintptr_t h) {

@@ -75,6 +75,10 @@ struct Device {
     int mixed_check_persistent = 1;     // overflow check as one resident wave of looping CTAs (GOMETAL_MIXED_CHECK_PERSISTENT)
     int mixed_fastdiv = 1;              // divisions by the bias corrections through div_const (GOMETAL_MIXED_FASTDIV)
     int mixed_pf = 1;                   // next-pass L2 prefetch in the update kernel (GOMETAL_MIXED_PF)
+    int mixed_ring = 0;                 // 2: the mixed step as one cooperative launch, 1: check kernel + ring update,
+                                        // 0: check kernel + one-CTA-per-chunk update (GOMETAL_MIXED_RING)
+    long long barrier_budget_cycles = 1LL << 31;   // bound of every device-side barrier wait, about a second
+                                        // (GOMETAL_BARRIER_BUDGET_CYCLES)
     int mixed_variant = 0;              // 1: the 4-elements-per-thread update kernel instead of the 8-element one (GOMETAL_MIXED_VARIANT)
     int mixed_overlap = 2;              // update grid launched with programmatic stream serialization: 2 = it may start when the
                                         // check grid's CTAs reach their end (measured best), 1 = from their start, 0 = off
@@ -86,6 +90,7 @@ struct Device {
     int lbfgs_waves = 1;                // resident-CTA waves of the pipelined L-BFGS pass (GOMETAL_LBFGS_WAVES)
     int grid_waves = 0;                 // 0: one CTA per chunk; >0: waves of resident CTAs (GOMETAL_GRID_WAVES)
     int chunk_elems = 0;                // 0: default tile; else elements per chunk (GOMETAL_CHUNK_ELEMS)
+    int lbfgs_coop = 0;                 // L-BFGS step as one cooperative launch with the direction kept on chip (GOMETAL_LBFGS_COOP)
     int lbfgs_mode = 3;                 // bit 0: corrected curvature pair, bit 1: descent direction
     // scratch for reductions (dot partials, tickets); grown on demand
     float* partials = nullptr;

@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <algorithm>
 #include <set>
 
 #include "gm_apply.cuh"
@@ -41,6 +42,7 @@ struct Mixed {
     bool saturated = false;                // table[table_len] == {1,1}: later steps reuse it
     float beta1 = 0.9f, beta2 = 0.999f;
     int64_t calls = 0;                     // upper bound of the device step counter
+    unsigned epoch = 0;                    // barrier epoch of the last single-launch step
 };
 
 static std::mutex g_mixed_mu;
@@ -526,6 +528,10 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
     }
 }
 
+}  // namespace gm
+#include "gm_mixed_ring.cuh"
+namespace gm {
+
 // ---- sum of squares (grad-norm): warp shuffle tree, one float atomic per CTA ----
 template <bool HALF>
 __global__ void __launch_bounds__(kApplyThreads)
@@ -627,6 +633,53 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     int grid_c = check_grid(d, l->dl.num_chunks);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
     const int check_flags = (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0);
+
+    // The ring kernels (gm_mixed_ring.cuh): 2 = the whole step as one cooperative launch, 1 = the
+    // check kernel followed by the ring update.  They carry neither the norm nor the clipping, and
+    // the sharded step needs the flag exchange between check and update, so those keep two launches.
+    int ring = d->mixed_ring;
+    if (norm) ring = 0;
+    if (hook && ring == 2) ring = 1;
+    if (l->dl.chunk_elems % kTileElems) ring = 0;
+    using RingFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, StepPrep*, const MixedScalars, const float2*,
+                            const int, const unsigned, const int, const long long);
+    RingFn ring_fn = nullptr;
+    int ring_grid = 0;
+    if (ring) {
+        ring_fn = ring == 2 ? (d->mixed_fastdiv ? mixed_ring_kernel<true, true> : mixed_ring_kernel<true, false>)
+                            : (d->mixed_fastdiv ? mixed_ring_kernel<false, true> : mixed_ring_kernel<false, false>);
+        static thread_local std::set<const void*> prepared;
+        if (!prepared.count((const void*)ring_fn)) {
+            GM_CUDA_CHECK(cudaFuncSetAttribute((const void*)ring_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingBytes));
+            prepared.insert((const void*)ring_fn);
+        }
+        int per_sm = 0;
+        GM_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)ring_fn, kApplyThreads, kRingBytes));
+        if (per_sm < 1) { ring = 0; }
+        const long long tiles = (long long)l->dl.num_chunks * (l->dl.chunk_elems / kTileElems);
+        ring_grid = (int)std::min<long long>((long long)per_sm * d->sm_count, tiles);
+        if (ring_grid < 1) ring_grid = 1;
+    }
+    if (ring == 2) {
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, d->ordinal);
+        if (!coop) ring = 1;
+    }
+    if (ring == 2) {
+        m->epoch += 1;
+        DevList dl = l->dl;
+        gm_loss_scale_t* st = m->d_state;
+        unsigned int* fl = m->d_flag;
+        const float2* tb = m->d_table;
+        int tlen = m->table_len;
+        unsigned ep = m->epoch;
+        int kg = check_flags;
+        long long budget = d->barrier_budget_cycles;
+        void* args[] = {&dl, &st, &fl, &prep, &sc, &tb, &tlen, &ep, &kg, &budget};
+        GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)ring_fn, dim3(ring_grid), dim3(kApplyThreads), args, kRingBytes, d->stream));
+        d->launches++;
+        return GM_OK;
+    }
     if (norm)
         mixed_check_kernel<true><<<grid_c, kApplyThreads, 0, d->stream>>>(l->dl, m->d_flag, m->d_state, m->d_table, m->table_len,
                                                                           prep, check_flags, d->partials, clipping ? m->max_norm : 0.0f);
@@ -662,6 +715,19 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         }
     }
     int grid_u = launch_grid(d, (const void*)update, kApplyThreads, l->dl.num_chunks);
+    if (ring == 1) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(ring_grid); cfg.blockDim = dim3(kApplyThreads); cfg.dynamicSmemBytes = kRingBytes; cfg.stream = d->stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        if (!hook && d->mixed_overlap) { cfg.attrs = &attr; cfg.numAttrs = 1; }
+        GM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, ring_fn, l->dl, m->d_state, m->d_flag, prep, sc, (const float2*)m->d_table, m->table_len,
+                                         0u, check_flags, d->barrier_budget_cycles));
+        d->launches++;
+        GM_CUDA_CHECK(cudaGetLastError());
+        return GM_OK;
+    }
     if (!hook && d->mixed_overlap) {
         // the update grid may become resident while the check grid drains
         cudaLaunchConfig_t cfg{};
@@ -751,6 +817,16 @@ int gm_mixed_get_state(uintptr_t device_ptr, uintptr_t mixed, gm_loss_scale_t* o
     DeviceGuard g(d);
     GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
     GM_CUDA_CHECK(cudaMemcpy(out, m->d_state, sizeof(*out), cudaMemcpyDeviceToHost));
+    unsigned int ctl[3] = {0, 0, 0};                          // arrive count, go epoch, error word
+    GM_CUDA_CHECK(cudaMemcpy(ctl, m->d_flag + kCtlArrive, sizeof(ctl), cudaMemcpyDeviceToHost));
+    if (ctl[2]) {
+        // a grid-barrier wait of the single-launch step ran out: put the control block back in its
+        // initial state so that the handle stays usable, and tell the caller
+        GM_CUDA_CHECK(cudaMemset(m->d_flag, 0, 256));
+        m->epoch = 0;
+        set_error("a grid-barrier wait of the mixed-precision step ran out; that step's buffers are partly updated");
+        return GM_ERR_TIMEOUT;
+    }
     return GM_OK;
 }
 
@@ -775,6 +851,24 @@ int gm_mixed_enable_grad_norm(uintptr_t mixed, int enable) {
     Mixed* m = as_mixed(mixed);
     if (!m) return GM_ERR_BAD_ARG;
     m->want_norm = enable ? 1 : 0;
+    return GM_OK;
+}
+
+// A bounded device-side wait on a word that nothing sets: it must give up after
+// budget_cycles and report it (gave_up = 1), leaving the context usable.
+int gm_selftest_barrier_timeout(uintptr_t device_ptr, long long budget_cycles, int* gave_up) {
+    Device* d = as_device(device_ptr);
+    if (!d) return GM_ERR_NIL_DEVICE;
+    if (!gave_up || budget_cycles <= 0 || budget_cycles > (1LL << 33)) { set_error("bad self-test arguments"); return GM_ERR_BAD_ARG; }
+    DeviceGuard g(d);
+    unsigned* word = reinterpret_cast<unsigned*>(d->scalars + 40);
+    int* status = reinterpret_cast<int*>(d->scalars + 41);
+    GM_CUDA_CHECK(cudaMemsetAsync(word, 0, 8, d->stream));
+    barrier_timeout_selftest_kernel<<<1, 32, 0, d->stream>>>(word, budget_cycles, status);
+    d->launches++;
+    GM_CUDA_CHECK(cudaGetLastError());
+    GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+    GM_CUDA_CHECK(cudaMemcpy(gave_up, status, sizeof(int), cudaMemcpyDeviceToHost));
     return GM_OK;
 }
 

@@ -1,0 +1,319 @@
+// gm_mixed_ring.cuh -- the mixed-precision step as ONE cooperative launch of
+// resident CTAs that feed themselves through an asynchronous shared-memory ring.
+// Included by gm_mixed.cu after StepPrep, MixedScalars and mixed_elem.
+//
+// Why: the two-launch step (overflow check, then update) spends a sixth of its
+// time outside the update's steady state: a 50 MB check pass that is all ramp and
+// tail, and the ramp and tail of a 5-wave update grid.  Here every CTA is resident
+// for the whole step (cooperative launch, so that is guaranteed, not assumed):
+//
+//   prologue  the loads of the CTA's first tiles of master/m/v/g16 are started
+//             (cp.async into the ring; they need no decision yet);
+//   check     the CTA reads the fp16 gradients of all ITS tiles once, marking the
+//             lines evict_last in L2, and ORs its overflow vote into the flag;
+//   barrier   one grid-wide barrier; the CTA that arrives last publishes the
+//             step's scalars (overflow, 1/scale, bias corrections);
+//   update    unless the step overflowed, the CTA walks its tiles: while tile q is
+//             computed from shared memory, tiles q+1 .. q+S-1 are in flight.  A
+//             thread only ever reads the ring slots it filled itself, so the ring
+//             needs no barrier, only cp.async.wait_group;
+//   finish    the CTA that takes the last ticket runs the loss-scale state machine.
+//
+// A tile is 2,048 consecutive elements of one chunk (8 per thread); tiles are
+// dealt round-robin to the CTAs, so all CTAs carry the same load to within one
+// tile.  The arithmetic is mixed_elem, the same statements in the same order as
+// the two-launch kernels: the results are bit-identical.
+//
+// The barrier wait is bounded (kBarrierBudgetCycles): a CTA whose wait runs out
+// records the fact in the control block, skips its tiles and returns, and the
+// loss-scale state is left alone, so a fault elsewhere can never turn into a hang
+// here; the host reports GM_ERR_TIMEOUT on its next query (the buffers of that step
+// are then partly updated and must be restored by the caller).
+#pragma once
+
+namespace gm {
+
+constexpr int kRingStages = 3;
+constexpr int kRingSlots = 7;                       // per thread and stage: g16, 2 x master, 2 x m, 2 x v (16 bytes each)
+constexpr int kTileElems = kApplyThreads * 8;       // 2,048
+constexpr size_t kRingBytes = (size_t)kRingStages * kRingSlots * kApplyThreads * 16;
+constexpr long long kBarrierBudgetCycles = 1LL << 31;   // about a second
+
+// words of the control block (the 64-word flag buffer of a Mixed state)
+constexpr int kCtlArrive = 32;     // CTAs that have reached the barrier
+constexpr int kCtlGo = 33;         // epoch of the last barrier that was released
+constexpr int kCtlError = 34;      // 1: a barrier wait ran out
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+// Where global tile qg lies: tensor, chunk bounds and this thread's vector in it.
+struct TileRef {
+    int t, k, j, h;              // tensor, chunk inside the tensor, tile inside the chunk, head of the tensor
+    long long n, b, e;           // tensor length, chunk bounds [b, e)
+    long long off;               // element offset of this thread's 8 elements
+    bool valid;                  // this thread has a whole vector in the tile
+};
+
+__device__ __forceinline__ TileRef locate_tile(const DevList& L, const int tiles_per_chunk, const int qg, const int tid) {
+    TileRef r;
+    const int c = qg / tiles_per_chunk;
+    r.j = qg - c * tiles_per_chunk;
+    const int2 rec = __ldg(L.chunk_rec + c);
+    r.t = rec.x; r.k = rec.y;
+    r.n = __ldg(L.numel + r.t);
+    r.h = __ldg(L.head + r.t);
+    const long long chunk = L.chunk_elems;
+    r.b = (long long)(r.h > 0 ? r.h : 0) + (long long)r.k * chunk;
+    r.e = (r.b + chunk < r.n) ? r.b + chunk : r.n;
+    const long long nv8 = r.h < 0 ? 0 : ((r.e - r.b) >> 3);
+    const long long i = (long long)r.j * kApplyThreads + tid;
+    r.valid = i < nv8;
+    r.off = r.b + 8 * i;
+    return r;
+}
+
+// Waits until *word == epoch, but no longer than `budget` clock cycles.  False: gave up.
+__device__ __forceinline__ bool bounded_wait_for(const unsigned* word, const unsigned epoch, const long long budget) {
+    const long long t0 = clock64();
+    while (ld_acquire(word) != epoch) {
+        if (clock64() - t0 > budget) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
+// FUSED: the overflow check and the grid barrier run inside this kernel (cooperative launch);
+// otherwise the check kernel has run before and this kernel starts from its published scalars.
+template <bool FUSED, bool FAST>
+__global__ void __launch_bounds__(kApplyThreads, 2)
+mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
+                  StepPrep* __restrict__ prep, const MixedScalars sc, const float2* __restrict__ table,
+                  const int table_len, const unsigned epoch, const int keep_g, const long long barrier_budget) {
+    extern __shared__ uint4 ring[];                  // [stage][slot][thread]
+    __shared__ int s_decision;
+    constexpr int NT = kApplyThreads;
+    const int tid = threadIdx.x;
+    const int T = L.num_tensors;
+    const int tpc = L.chunk_elems / kTileElems;
+    const int total_tiles = L.num_chunks * tpc;
+    const int G = gridDim.x;
+    const int mine = (int)blockIdx.x < total_tiles ? (total_tiles - (int)blockIdx.x + G - 1) / G : 0;
+
+    auto slot = [&](int stage, int s) -> uint4* { return ring + ((size_t)(stage * kRingSlots + s) * NT + tid); };
+    auto stream_ptr = [&](int s, int t) -> unsigned long long { return __ldg(L.ptrs + (size_t)s * T + t); };
+
+    // starts the loads of this CTA's k-th tile; always closes a group so that the counting is uniform
+    auto issue = [&](int k) {
+        if (k < mine) {
+            const TileRef r = locate_tile(L, tpc, blockIdx.x + k * G, tid);
+            if (r.valid) {
+                const int st = k % kRingStages;
+                const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t)) + r.off;
+                const float* w = reinterpret_cast<const float*>(stream_ptr(1, r.t)) + r.off;
+                const float* m = reinterpret_cast<const float*>(stream_ptr(2, r.t)) + r.off;
+                const float* v = reinterpret_cast<const float*>(stream_ptr(3, r.t)) + r.off;
+                cp_async16(slot(st, 0), g);
+                cp_async16(slot(st, 1), w); cp_async16(slot(st, 2), w + 4);
+                cp_async16(slot(st, 3), m); cp_async16(slot(st, 4), m + 4);
+                cp_async16(slot(st, 5), v); cp_async16(slot(st, 6), v + 4);
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int k = 0; k < kRingStages - 1; ++k) issue(k);
+
+    int decision = 0;                                // 0 update, 1 overflow: skip, 2 the barrier wait ran out
+    if (FUSED) {
+        const unsigned long long pol = l2_policy((keep_g & 1) != 0);
+        unsigned bad = 0;
+        for (int k0 = 0; k0 < mine; k0 += 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (k0 + u < mine) {
+                    const TileRef r = locate_tile(L, tpc, blockIdx.x + (k0 + u) * G, tid);
+                    const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t));
+                    if (r.valid) v[u] = ld_l2(reinterpret_cast<const uint4*>(g + r.off), pol);
+                    if (r.j == 0) {                  // the chunk's scalar pieces go with its first tile
+                        if (r.h < 0) {
+                            for (long long i = r.b + tid; i < r.e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
+                        } else {
+                            if (r.k == 0 && tid < r.h) bad |= ((g[tid] & 0x7c00u) == 0x7c00u);
+                            const long long tb = r.b + (((r.e - r.b) >> 3) << 3);
+                            if (tb + tid < r.e) bad |= ((g[tb + tid] & 0x7c00u) == 0x7c00u);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
+        }
+        const int any_bad = __syncthreads_or(bad != 0);
+        if (tid == 0) {
+            int d = 0;
+            if (any_bad) atomicOr(flag, 1u);
+            __threadfence();
+            const unsigned arrived = atomicAdd(flag + kCtlArrive, 1u);
+            if (arrived == (unsigned)G - 1u) {
+                // every vote is in: publish the step's scalars and release the others
+                __threadfence();
+                const unsigned overflow = *reinterpret_cast<volatile unsigned int*>(flag);
+                const int tstep = state->adam_t + 1;
+                const float2 bc = table[tstep < table_len ? tstep : table_len];
+                publish_prep(prep, overflow, state->scale, bc, 1.0f);
+                flag[kCtlArrive] = 0u;
+                __threadfence();
+                st_release(flag + kCtlGo, epoch);
+            } else if (!bounded_wait_for(flag + kCtlGo, epoch, barrier_budget)) {
+                atomicExch(flag + kCtlError, 1u);
+                d = 2;
+            }
+            s_decision = d;
+        }
+        __syncthreads();
+        decision = s_decision;
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+
+    // the scalars were written by another CTA (or the check kernel): read them past L1
+    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(prep));
+    const uint4 raw2 = __ldcg(reinterpret_cast<const uint4*>(prep) + 1);
+    const unsigned overflow = raw.x;
+    if (decision == 0 && overflow) decision = 1;
+
+    if (decision == 0) {
+        AdamRule::P p;
+        p.lr = sc.lr; p.beta1 = sc.beta1; p.beta2 = sc.beta2; p.omb1 = sc.omb1; p.omb2 = sc.omb2;
+        p.bc1 = __uint_as_float(raw.z); p.bc2 = __uint_as_float(raw.w);
+        p.rbc1 = __uint_as_float(raw2.x); p.rbc2 = __uint_as_float(raw2.y);
+        p.eps = sc.eps; p.wd = sc.wd; p.use_wd = sc.use_wd;
+        const float inv_scale = __uint_as_float(raw.y);
+        const bool fast = FAST && raw2.w != 0u;
+
+        for (int k = 0; k < mine; ++k) {
+            issue(k + kRingStages - 1);
+            const TileRef r = locate_tile(L, tpc, blockIdx.x + k * G, tid);
+            float* w = reinterpret_cast<float*>(stream_ptr(1, r.t));
+            float* m = reinterpret_cast<float*>(stream_ptr(2, r.t));
+            float* v = reinterpret_cast<float*>(stream_ptr(3, r.t));
+            unsigned short* o = reinterpret_cast<unsigned short*>(stream_ptr(4, r.t));
+            cp_async_wait<kRingStages - 1>();                 // this tile's group has landed
+            if (r.valid) {
+                const int st = k % kRingStages;
+                const uint4 gc = *slot(st, 0);
+                const float4 w0 = *reinterpret_cast<const float4*>(slot(st, 1)), w1 = *reinterpret_cast<const float4*>(slot(st, 2));
+                const float4 m0 = *reinterpret_cast<const float4*>(slot(st, 3)), m1 = *reinterpret_cast<const float4*>(slot(st, 4));
+                const float4 v0 = *reinterpret_cast<const float4*>(slot(st, 5)), v1 = *reinterpret_cast<const float4*>(slot(st, 6));
+                float W[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                float M[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+                float V[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                const unsigned gw[4] = {gc.x, gc.y, gc.z, gc.w};
+                unsigned ow[4];
+                if (fast) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        unsigned short lo, hi;
+                        mixed_elem<true, false>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, 1.0f, W[2 * j], M[2 * j], V[2 * j], lo, p);
+                        mixed_elem<true, false>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, 1.0f, W[2 * j + 1], M[2 * j + 1], V[2 * j + 1], hi, p);
+                        ow[j] = (unsigned)lo | ((unsigned)hi << 16);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        unsigned short lo, hi;
+                        mixed_elem<false, false>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, 1.0f, W[2 * j], M[2 * j], V[2 * j], lo, p);
+                        mixed_elem<false, false>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, 1.0f, W[2 * j + 1], M[2 * j + 1], V[2 * j + 1], hi, p);
+                        ow[j] = (unsigned)lo | ((unsigned)hi << 16);
+                    }
+                }
+                float4* wq = reinterpret_cast<float4*>(w + r.off);
+                float4* mq = reinterpret_cast<float4*>(m + r.off);
+                float4* vq = reinterpret_cast<float4*>(v + r.off);
+                __stcs(wq, make_float4(W[0], W[1], W[2], W[3])); __stcs(wq + 1, make_float4(W[4], W[5], W[6], W[7]));
+                __stcs(mq, make_float4(M[0], M[1], M[2], M[3])); __stcs(mq + 1, make_float4(M[4], M[5], M[6], M[7]));
+                __stcs(vq, make_float4(V[0], V[1], V[2], V[3])); __stcs(vq + 1, make_float4(V[4], V[5], V[6], V[7]));
+                __stcs(reinterpret_cast<uint4*>(o + r.off), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            }
+            if (r.j == 0) {
+                // the chunk's scalar pieces: elements in front of the tensor's 16-byte boundary, the
+                // fewer-than-eight behind the last whole vector, or the whole chunk of a tensor whose
+                // streams share no boundary
+                const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t));
+                auto scalar_at = [&](long long i) {
+                    float wi = w[i], mi = m[i], vi = v[i];
+                    unsigned short pi;
+                    mixed_elem<false, false>(half_bits_to_float(g[i]), inv_scale, 1.0f, wi, mi, vi, pi, p);
+                    w[i] = wi; m[i] = mi; v[i] = vi; o[i] = pi;
+                };
+                if (r.h < 0) {
+                    for (long long i = r.b + tid; i < r.e; i += NT) scalar_at(i);
+                } else {
+                    if (r.k == 0 && tid < r.h) scalar_at(tid);
+                    const long long tb = r.b + (((r.e - r.b) >> 3) << 3);
+                    if (tb + tid < r.e) scalar_at(tb + tid);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();                              // nothing of this CTA is in flight when it leaves
+
+    // the CTA that takes the last ticket runs the loss-scale state machine
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned ticket = atomicAdd(flag + 1, 1u);
+        if (ticket == (unsigned)G - 1u) {
+            const unsigned failed = *reinterpret_cast<volatile unsigned int*>(flag + kCtlError);
+            if (!failed) {
+                gm_loss_scale_t s = *state;
+                if (overflow) {
+                    s.scale = mul(s.scale, s.backoff);
+                    s.good_steps = 0;
+                    s.skipped += 1;
+                    s.last_overflow = 1;
+                } else {
+                    s.adam_t += 1;
+                    s.last_overflow = 0;
+                    s.good_steps += 1;
+                    if (s.good_steps >= s.interval) {
+                        float grown = mul(s.scale, s.growth);
+                        if (grown > s.max_scale) grown = s.max_scale;
+                        s.scale = grown;
+                        s.good_steps = 0;
+                    }
+                }
+                *state = s;
+            }
+            flag[0] = 0u;
+            flag[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+// A wait that nothing releases, with a short budget: the bounded wait must give up and say so.
+__global__ void barrier_timeout_selftest_kernel(const unsigned* word, const long long budget, int* status) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) *status = bounded_wait_for(word, 0x5eedu, budget) ? 0 : 1;
+}
+
+}  // namespace gm

@@ -136,6 +136,9 @@ _SIGS = {
     "gm_zero1_mixed_step_async": (i, [u, u, u, f, f, f, u, i64]),
     "gm_zero1_reduce_scatter_async": (i, [u, u, i64, i]),
     "gm_selftest_const_div": (i, [u, f, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), ip]),
+    "gm_selftest_barrier_timeout": (i, [u, C.c_longlong, ip]),
+    "gm_device_set_tuning": (i, [u, C.c_char_p, C.c_longlong]),
+    "gm_device_get_tuning": (C.c_longlong, [u, C.c_char_p]),
     "gm_timer_start": (i, [u]),
     "gm_timer_stop": (i, [u, C.POINTER(f)]),
 }

@@ -165,6 +165,13 @@ int gm_device_synchronize(uintptr_t device_ptr);
  * tear the group down).  Meant for sharded steps, where a peer that never enters its
  * collective would otherwise block this rank for ever. */
 int gm_device_synchronize_timeout(uintptr_t device_ptr, int timeout_ms);
+/* Launch-strategy switches of a handle; every setting computes the same bits.  Names:
+ * "mixed_ring" (2: the mixed-precision step as one cooperative launch, 1: overflow check
+ * followed by the shared-memory-ring update, 0: check followed by the one-CTA-per-chunk
+ * update), "mixed_fastdiv", "mixed_pf", "mixed_variant", "lbfgs_coop",
+ * "barrier_budget_cycles" (bound of every device-side barrier wait). */
+int gm_device_set_tuning(uintptr_t device_ptr, const char* name, long long value);
+long long gm_device_get_tuning(uintptr_t device_ptr, const char* name);   /* -1: unknown name */
 /* Number of kernels this library has launched on the device so far. */
 int64_t gm_device_launch_count(uintptr_t device_ptr);
 
@@ -381,6 +388,11 @@ int gm_zero1_reduce_scatter_async(uintptr_t zero1, uintptr_t grad_arena_base, in
  * the library enables the sequence for (it then uses the IEEE division). */
 int gm_selftest_const_div(uintptr_t device_ptr, float c, uint64_t* mismatches, uint32_t* first_bad_bits,
                           int* fast_path_allowed);
+/* The single-launch steps synchronise their CTAs with a grid-wide barrier whose wait is
+ * bounded.  This entry runs that wait on a word nothing sets, with a budget of
+ * budget_cycles GPU clock cycles: it must return with *gave_up == 1 and leave the device
+ * usable (a step whose barrier gives up reports GM_ERR_TIMEOUT). */
+int gm_selftest_barrier_timeout(uintptr_t device_ptr, long long budget_cycles, int* gave_up);
 
 /* ---- timing on the device's stream (CUDA events) ---- */
 int gm_timer_start(uintptr_t device_ptr);                  /* records the start event */
