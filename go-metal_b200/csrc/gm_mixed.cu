@@ -640,7 +640,7 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     int ring = d->mixed_ring;
     if (norm) ring = 0;
     if (hook && ring == 2) ring = 1;
-    if (l->dl.chunk_elems % kTileElems) ring = 0;
+    if (l->dl.chunk_elems % kCheckElems) ring = 0;
     using RingFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, StepPrep*, const MixedScalars, const float2*,
                             const int, const unsigned, const int, const long long);
     RingFn ring_fn = nullptr;

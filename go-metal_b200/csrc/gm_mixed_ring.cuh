@@ -2,10 +2,15 @@
 // resident CTAs that feed themselves through an asynchronous shared-memory ring.
 // Included by gm_mixed.cu after StepPrep, MixedScalars and mixed_elem.
 //
-// Why: the two-launch step (overflow check, then update) spends a sixth of its
-// time outside the update's steady state: a 50 MB check pass that is all ramp and
-// tail, and the ramp and tail of a 5-wave update grid.  Here every CTA is resident
-// for the whole step (cooperative launch, so that is guaranteed, not assumed):
+// MEASURED SLOWER than the two-launch step and therefore not the default (25.2 M
+// parameters in 48 ragged tensors on B200: 135.5 us for the check kernel followed by the
+// one-CTA-per-chunk update; 167 us for the check kernel followed by this ring update; 189 us
+// for this kernel doing the whole step).  It stays selectable ("mixed_ring" of
+// gm_device_set_tuning) because it is the only strategy that needs no second launch, and
+// it carries the bounded grid barrier.  The idea it tests: the two-launch step spends a
+// sixth of its time outside the update's steady state (a 50 MB check pass that is all ramp
+// and tail, and the ramp and tail of a 5-wave update grid), so keep every CTA resident for
+// the whole step (cooperative launch, so that is guaranteed, not assumed):
 //
 //   prologue  the loads of the CTA's first tiles of master/m/v/g16 are started
 //             (cp.async into the ring; they need no decision yet);
@@ -19,10 +24,15 @@
 //             needs no barrier, only cp.async.wait_group;
 //   finish    the CTA that takes the last ticket runs the loss-scale state machine.
 //
-// A tile is 2,048 consecutive elements of one chunk (8 per thread); tiles are
-// dealt round-robin to the CTAs, so all CTAs carry the same load to within one
-// tile.  The arithmetic is mixed_elem, the same statements in the same order as
-// the two-launch kernels: the results are bit-identical.
+// A tile is 1,024 consecutive elements of one chunk (4 per thread, so that four CTAs
+// of 256 threads with a three-stage ring fit one SM: the arithmetic needs that many
+// warps to hide its own latency); tiles are dealt round-robin to the CTAs, so all
+// CTAs carry the same load to within one tile.  The check walks the gradients in
+// units of 2,048 elements (16 bytes per thread), dealt the same way.  The arithmetic is
+// mixed_elem, the same statements in the same order as the two-launch kernels: the
+// results are bit-identical.  What it loses to: the per-tile table lookups (two per four
+// elements per thread, against one per thirty-two in the chunk kernel) and the trip
+// through shared memory cost more issue slots than the deeper pipeline wins back.
 //
 // The barrier wait is bounded (kBarrierBudgetCycles): a CTA whose wait runs out
 // records the fact in the control block, skips its tiles and returns, and the
@@ -34,9 +44,12 @@
 namespace gm {
 
 constexpr int kRingStages = 3;
-constexpr int kRingSlots = 7;                       // per thread and stage: g16, 2 x master, 2 x m, 2 x v (16 bytes each)
-constexpr int kTileElems = kApplyThreads * 8;       // 2,048
-constexpr size_t kRingBytes = (size_t)kRingStages * kRingSlots * kApplyThreads * 16;
+constexpr int kRingV = 4;                           // elements per thread and tile
+constexpr int kTileElems = kApplyThreads * kRingV;  // 1,024
+constexpr int kCheckElems = kApplyThreads * 8;      // 2,048: unit of the fused check
+constexpr int kRingWide = 3;                        // 16-byte slots per thread and stage: master, m, v
+constexpr size_t kRingStageBytes = (size_t)kApplyThreads * (kRingWide * 16 + 8);   // + 8 bytes of fp16 gradients
+constexpr size_t kRingBytes = kRingStages * kRingStageBytes;
 constexpr long long kBarrierBudgetCycles = 1LL << 31;   // about a second
 
 // words of the control block (the 64-word flag buffer of a Mixed state)
@@ -47,6 +60,10 @@ constexpr int kCtlError = 34;      // 1: a barrier wait ran out
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(s), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -69,6 +86,8 @@ struct TileRef {
     bool valid;                  // this thread has a whole vector in the tile
 };
 
+// V: elements per thread (the tile holds 256 * V elements)
+template <int V>
 __device__ __forceinline__ TileRef locate_tile(const DevList& L, const int tiles_per_chunk, const int qg, const int tid) {
     TileRef r;
     const int c = qg / tiles_per_chunk;
@@ -80,10 +99,10 @@ __device__ __forceinline__ TileRef locate_tile(const DevList& L, const int tiles
     const long long chunk = L.chunk_elems;
     r.b = (long long)(r.h > 0 ? r.h : 0) + (long long)r.k * chunk;
     r.e = (r.b + chunk < r.n) ? r.b + chunk : r.n;
-    const long long nv8 = r.h < 0 ? 0 : ((r.e - r.b) >> 3);
+    const long long nvec = r.h < 0 ? 0 : ((r.e - r.b) / V);
     const long long i = (long long)r.j * kApplyThreads + tid;
-    r.valid = i < nv8;
-    r.off = r.b + 8 * i;
+    r.valid = i < nvec;
+    r.off = r.b + V * i;
     return r;
 }
 
@@ -100,11 +119,11 @@ __device__ __forceinline__ bool bounded_wait_for(const unsigned* word, const uns
 // FUSED: the overflow check and the grid barrier run inside this kernel (cooperative launch);
 // otherwise the check kernel has run before and this kernel starts from its published scalars.
 template <bool FUSED, bool FAST>
-__global__ void __launch_bounds__(kApplyThreads, 2)
+__global__ void __launch_bounds__(kApplyThreads, 4)
 mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
                   StepPrep* __restrict__ prep, const MixedScalars sc, const float2* __restrict__ table,
                   const int table_len, const unsigned epoch, const int keep_g, const long long barrier_budget) {
-    extern __shared__ uint4 ring[];                  // [stage][slot][thread]
+    extern __shared__ uint4 ring[];                  // per stage: [3][256] x 16 bytes, then [256] x 8 bytes
     __shared__ int s_decision;
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
@@ -114,23 +133,24 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
     const int G = gridDim.x;
     const int mine = (int)blockIdx.x < total_tiles ? (total_tiles - (int)blockIdx.x + G - 1) / G : 0;
 
-    auto slot = [&](int stage, int s) -> uint4* { return ring + ((size_t)(stage * kRingSlots + s) * NT + tid); };
+    auto wide = [&](int stage, int s) -> uint4* {
+        return reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + stage * kRingStageBytes) + s * NT + tid;
+    };
+    auto narrow = [&](int stage) -> uint2* {
+        return reinterpret_cast<uint2*>(reinterpret_cast<char*>(ring) + stage * kRingStageBytes + (size_t)kRingWide * NT * 16) + tid;
+    };
     auto stream_ptr = [&](int s, int t) -> unsigned long long { return __ldg(L.ptrs + (size_t)s * T + t); };
 
     // starts the loads of this CTA's k-th tile; always closes a group so that the counting is uniform
     auto issue = [&](int k) {
         if (k < mine) {
-            const TileRef r = locate_tile(L, tpc, blockIdx.x + k * G, tid);
+            const TileRef r = locate_tile<kRingV>(L, tpc, blockIdx.x + k * G, tid);
             if (r.valid) {
                 const int st = k % kRingStages;
-                const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t)) + r.off;
-                const float* w = reinterpret_cast<const float*>(stream_ptr(1, r.t)) + r.off;
-                const float* m = reinterpret_cast<const float*>(stream_ptr(2, r.t)) + r.off;
-                const float* v = reinterpret_cast<const float*>(stream_ptr(3, r.t)) + r.off;
-                cp_async16(slot(st, 0), g);
-                cp_async16(slot(st, 1), w); cp_async16(slot(st, 2), w + 4);
-                cp_async16(slot(st, 3), m); cp_async16(slot(st, 4), m + 4);
-                cp_async16(slot(st, 5), v); cp_async16(slot(st, 6), v + 4);
+                cp_async16(wide(st, 0), reinterpret_cast<const float*>(stream_ptr(1, r.t)) + r.off);
+                cp_async16(wide(st, 1), reinterpret_cast<const float*>(stream_ptr(2, r.t)) + r.off);
+                cp_async16(wide(st, 2), reinterpret_cast<const float*>(stream_ptr(3, r.t)) + r.off);
+                cp_async8(narrow(st), reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t)) + r.off);
             }
         }
         cp_async_commit();
@@ -142,17 +162,21 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
     int decision = 0;                                // 0 update, 1 overflow: skip, 2 the barrier wait ran out
     if (FUSED) {
         const unsigned long long pol = l2_policy((keep_g & 1) != 0);
+        const int upc = L.chunk_elems / kCheckElems;
+        const int total_units = L.num_chunks * upc;
+        const int units = (int)blockIdx.x < total_units ? (total_units - (int)blockIdx.x + G - 1) / G : 0;
+        constexpr int U = 8;                         // 16-byte loads in flight per thread
         unsigned bad = 0;
-        for (int k0 = 0; k0 < mine; k0 += 4) {
-            uint4 v[4];
+        for (int k0 = 0; k0 < units; k0 += U) {
+            uint4 v[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 v[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (k0 + u < mine) {
-                    const TileRef r = locate_tile(L, tpc, blockIdx.x + (k0 + u) * G, tid);
+                if (k0 + u < units) {
+                    const TileRef r = locate_tile<8>(L, upc, blockIdx.x + (k0 + u) * G, tid);
                     const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t));
                     if (r.valid) v[u] = ld_l2(reinterpret_cast<const uint4*>(g + r.off), pol);
-                    if (r.j == 0) {                  // the chunk's scalar pieces go with its first tile
+                    if (r.j == 0) {                  // the chunk's scalar pieces go with its first unit
                         if (r.h < 0) {
                             for (long long i = r.b + tid; i < r.e; i += NT) bad |= ((g[i] & 0x7c00u) == 0x7c00u);
                         } else {
@@ -164,7 +188,7 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
                 bad |= nonfinite_mask(v[u].x) | nonfinite_mask(v[u].y) | nonfinite_mask(v[u].z) | nonfinite_mask(v[u].w);
         }
         const int any_bad = __syncthreads_or(bad != 0);
@@ -212,7 +236,7 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
 
         for (int k = 0; k < mine; ++k) {
             issue(k + kRingStages - 1);
-            const TileRef r = locate_tile(L, tpc, blockIdx.x + k * G, tid);
+            const TileRef r = locate_tile<kRingV>(L, tpc, blockIdx.x + k * G, tid);
             float* w = reinterpret_cast<float*>(stream_ptr(1, r.t));
             float* m = reinterpret_cast<float*>(stream_ptr(2, r.t));
             float* v = reinterpret_cast<float*>(stream_ptr(3, r.t));
@@ -220,18 +244,18 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
             cp_async_wait<kRingStages - 1>();                 // this tile's group has landed
             if (r.valid) {
                 const int st = k % kRingStages;
-                const uint4 gc = *slot(st, 0);
-                const float4 w0 = *reinterpret_cast<const float4*>(slot(st, 1)), w1 = *reinterpret_cast<const float4*>(slot(st, 2));
-                const float4 m0 = *reinterpret_cast<const float4*>(slot(st, 3)), m1 = *reinterpret_cast<const float4*>(slot(st, 4));
-                const float4 v0 = *reinterpret_cast<const float4*>(slot(st, 5)), v1 = *reinterpret_cast<const float4*>(slot(st, 6));
-                float W[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                float M[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-                float V[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                const unsigned gw[4] = {gc.x, gc.y, gc.z, gc.w};
-                unsigned ow[4];
+                const uint2 gc = *narrow(st);
+                const float4 w0 = *reinterpret_cast<const float4*>(wide(st, 0));
+                const float4 m0 = *reinterpret_cast<const float4*>(wide(st, 1));
+                const float4 v0 = *reinterpret_cast<const float4*>(wide(st, 2));
+                float W[4] = {w0.x, w0.y, w0.z, w0.w};
+                float M[4] = {m0.x, m0.y, m0.z, m0.w};
+                float V[4] = {v0.x, v0.y, v0.z, v0.w};
+                const unsigned gw[2] = {gc.x, gc.y};
+                unsigned ow[2];
                 if (fast) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 2; ++j) {
                         unsigned short lo, hi;
                         mixed_elem<true, false>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, 1.0f, W[2 * j], M[2 * j], V[2 * j], lo, p);
                         mixed_elem<true, false>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, 1.0f, W[2 * j + 1], M[2 * j + 1], V[2 * j + 1], hi, p);
@@ -239,24 +263,21 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 2; ++j) {
                         unsigned short lo, hi;
                         mixed_elem<false, false>(half_bits_to_float((unsigned short)(gw[j] & 0xffffu)), inv_scale, 1.0f, W[2 * j], M[2 * j], V[2 * j], lo, p);
                         mixed_elem<false, false>(half_bits_to_float((unsigned short)(gw[j] >> 16)), inv_scale, 1.0f, W[2 * j + 1], M[2 * j + 1], V[2 * j + 1], hi, p);
                         ow[j] = (unsigned)lo | ((unsigned)hi << 16);
                     }
                 }
-                float4* wq = reinterpret_cast<float4*>(w + r.off);
-                float4* mq = reinterpret_cast<float4*>(m + r.off);
-                float4* vq = reinterpret_cast<float4*>(v + r.off);
-                __stcs(wq, make_float4(W[0], W[1], W[2], W[3])); __stcs(wq + 1, make_float4(W[4], W[5], W[6], W[7]));
-                __stcs(mq, make_float4(M[0], M[1], M[2], M[3])); __stcs(mq + 1, make_float4(M[4], M[5], M[6], M[7]));
-                __stcs(vq, make_float4(V[0], V[1], V[2], V[3])); __stcs(vq + 1, make_float4(V[4], V[5], V[6], V[7]));
-                __stcs(reinterpret_cast<uint4*>(o + r.off), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+                __stcs(reinterpret_cast<float4*>(w + r.off), make_float4(W[0], W[1], W[2], W[3]));
+                __stcs(reinterpret_cast<float4*>(m + r.off), make_float4(M[0], M[1], M[2], M[3]));
+                __stcs(reinterpret_cast<float4*>(v + r.off), make_float4(V[0], V[1], V[2], V[3]));
+                __stcs(reinterpret_cast<uint2*>(o + r.off), make_uint2(ow[0], ow[1]));
             }
             if (r.j == 0) {
                 // the chunk's scalar pieces: elements in front of the tensor's 16-byte boundary, the
-                // fewer-than-eight behind the last whole vector, or the whole chunk of a tensor whose
+                // fewer-than-four behind the last whole vector, or the whole chunk of a tensor whose
                 // streams share no boundary
                 const unsigned short* g = reinterpret_cast<const unsigned short*>(stream_ptr(0, r.t));
                 auto scalar_at = [&](long long i) {
@@ -269,7 +290,7 @@ mixed_ring_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned
                     for (long long i = r.b + tid; i < r.e; i += NT) scalar_at(i);
                 } else {
                     if (r.k == 0 && tid < r.h) scalar_at(tid);
-                    const long long tb = r.b + (((r.e - r.b) >> 3) << 3);
+                    const long long tb = r.b + (((r.e - r.b) / kRingV) * kRingV);
                     if (tb + tid < r.e) scalar_at(tb + tid);
                 }
             }
