@@ -365,6 +365,144 @@ def run_only(args):
     return 0
 
 
+def mixed_scaling_case(gm, dev, torch, dist, zero1, rank, world, steps, exchange_wanted):
+    """Second scaling case: mixed-precision Adam on the headline's 2^30 parameters (256 flat
+    tensors of 4 Mi), master weights, moments and fp16 gradients sharded over the ranks, the
+    fp16 parameter arena exchanged every step (2 B/param instead of 4).  Strong scaling.
+    Returns the block for the JSON line (rank 0) or None."""
+    import numpy as np
+    L = gm.lib
+    per_rank = 256 // world
+    shard = per_rank * TENSOR_ELEMS
+    total = 256 * TENSOR_ELEMS
+    first = rank * per_rank
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 77)
+    p16 = torch.empty(total, dtype=torch.float32, device="cuda").uniform_(-0.05, 0.05, generator=gen).to(torch.float16)
+    master = p16[first * TENSOR_ELEMS: first * TENSOR_ELEMS + shard].to(torch.float32)
+    gen.manual_seed(SEED + 78 + rank)
+    g16 = torch.empty(shard, dtype=torch.float32, device="cuda").normal_(0.0, 1e-3 * 65536.0, generator=gen).to(torch.float16)
+    m = torch.zeros(shard, dtype=torch.float32, device="cuda")
+    v = torch.zeros(shard, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    tp = lambda a, eb, off=0: [a.data_ptr() + eb * (off + t) * TENSOR_ELEMS for t in range(per_rank)]
+    lst = dev.tensor_list([tp(g16, 2), tp(master, 4), tp(m, 4), tp(v, 4), tp(p16, 2, first)], [TENSOR_ELEMS] * per_rank, [2, 4, 4, 4, 2])
+    init = gm.LossScale(scale=65536.0, growth=2.0, backoff=0.5, max_scale=16777216.0, interval=1 << 30,
+                        good_steps=0, adam_t=0, skipped=0, last_overflow=0)
+    mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
+    if not mx:
+        raise SystemExit("mixed state: " + gm.last_error())
+    exchange = "none"
+    if world > 1:
+        exchange = "push" if exchange_wanted in ("push", "dma") else "nccl"
+        if exchange == "push":
+            mine_h = (C.c_ubyte * 64)()
+            rc = L.gm_zero1_ipc_handle_slot(zero1, 1, p16.data_ptr(), mine_h)
+            ok = torch.tensor([1 if rc == 0 else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                exchange = "nccl"
+            else:
+                mine_t = torch.tensor(list(bytes(mine_h)), dtype=torch.uint8, device="cuda")
+                all_t = [torch.empty_like(mine_t) for _ in range(world)]
+                dist.all_gather(all_t, mine_t)
+                blob = bytes(b for tt in all_t for b in tt.cpu().tolist())
+                gm.check(L.gm_zero1_open_peers_slot(zero1, 1, (C.c_ubyte * len(blob))(*blob)), "open peers (fp16 arena)")
+
+    # the sample the parity check follows, taken before any step
+    edge = np.concatenate([np.arange(0, 64), np.arange(shard - 64, shard)])
+    idx_np = np.unique(np.concatenate([np.arange(0, total, 4099)] + [edge + r * shard for r in range(world)])).astype(np.int64)
+    owner = idx_np // shard
+    sel = owner == rank
+    mine = torch.from_numpy(idx_np[sel] - rank * shard).cuda()
+    pos = torch.from_numpy(np.nonzero(sel)[0]).cuda()
+
+    def gather_samples(values_i32):
+        buf = torch.zeros(idx_np.size, dtype=torch.int32, device="cuda")
+        buf[pos] = values_i32
+        if dist is not None:
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM)
+        return buf.cpu().numpy()
+
+    g_s = gather_samples(g16[mine].view(torch.int16).to(torch.int32)).astype(np.uint16)
+    w_s = gather_samples(master[mine].view(torch.int32)).view(np.float32).copy()
+
+    def step():
+        if world == 1:
+            gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed step")
+        elif exchange == "push":
+            gm.check(L.gm_zero1_mixed_push_step_async(zero1, mx, lst, LR, EPS, WD), "zero1 mixed push step")
+        else:
+            gm.check(L.gm_zero1_mixed_step_async(zero1, mx, lst, LR, EPS, WD, p16.data_ptr(), shard), "zero1 mixed step")
+
+    def sync_all():
+        dev.sync()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def max_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    done = 0
+    for _ in range(3):
+        step()
+        done += 1
+    sync_all()
+    ms = C.c_float()
+    gm.check(L.gm_timer_start(dev.h), "timer")
+    for _ in range(steps):
+        step()
+        done += 1
+    gm.check(L.gm_timer_stop(dev.h, C.byref(ms)), "timer")
+    sync_all()
+    step_ms = max_ranks(float(ms.value)) / steps
+
+    # parity: the sampled fp16 parameters of the whole arena on every rank, and the owner's master weights
+    from oracle import oracle as O
+    st = O.new_loss_scale(interval=1 << 30)
+    m_s, v_s, p_s = np.zeros_like(w_s), np.zeros_like(w_s), np.zeros(w_s.size, np.uint16)
+    for _ in range(done):
+        O.mixed_adam_step([g_s], [w_s], [m_s], [v_s], [p_s], LR, B1, B2, EPS, WD, st)
+    got_p = p16[torch.from_numpy(idx_np).cuda()].view(torch.int16).cpu().numpy().view(np.uint16)
+    ok = bool(np.array_equal(got_p, p_s)) and bool(np.array_equal(master[mine].cpu().numpy().view(np.uint32), w_s[sel].view(np.uint32)))
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    if dist is not None:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+
+    update_ms = step_ms
+    if world > 1:
+        gm.check(L.gm_timer_start(dev.h), "timer")
+        for _ in range(steps):
+            gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed step")
+        gm.check(L.gm_timer_stop(dev.h, C.byref(ms)), "timer")
+        sync_all()
+        update_ms = max_ranks(float(ms.value)) / steps
+    L.gm_mixed_destroy(mx)
+    L.gm_tensor_list_destroy(lst)
+    sync_all()
+    peak, peak_kind = measured_peak_gbs()
+    bytes_in = 2 * (total - shard)
+    out = {
+        "workload": "mixed-precision Adam, 2^30 params in 256 flat tensors of 4 Mi, state sharded over N GPUs, fp16 parameters exchanged",
+        "exchange": exchange, "ms_per_step": step_ms, "gparams_s": total / step_ms / 1e6, "steps": steps,
+        "update_only_ms_per_step": update_ms,
+        "update_dram_gbs": 28 * shard / update_ms / 1e6, "update_frac": 28 * shard / update_ms / 1e6 / peak, "peak_source": f"of {peak_kind}",
+        "dram_basis": "28 B/param (fp16 gradients once, master/m/v read and written, fp16 parameters written)",
+        "exchange_bytes_in_per_gpu": bytes_in,
+        "exchange_gbs_in_per_gpu": bytes_in / step_ms / 1e6 if world > 1 else 0.0,
+        "exchange_floor_ms_at_770": bytes_in / NVLINK_MEASURED_GBS / 1e6,
+        "parity_check": {"ranks": world, "sampled": int(idx_np.size), "steps_replayed": done, "ok": bool(int(flag.item()) == 1)},
+    }
+    del p16, master, g16, m, v
+    torch.cuda.empty_cache()
+    return out if rank == 0 else None
+
+
 def run_workloads(gm, dev, torch, reps):
     peak, peak_kind = measured_peak_gbs()
     entries = [workload_mixed(gm, dev, torch, peak, max(reps, 20))]
@@ -697,6 +835,9 @@ def run_gpu(args):
     workloads = None
     if world == 1 and not args.no_workloads and NUM_TENSORS == 256:
         workloads = run_workloads(gm, dev, torch, args.steps)
+    mixed_case = None
+    if not args.no_workloads and NUM_TENSORS == 256:
+        mixed_case = mixed_scaling_case(gm, dev, torch, dist, zero1, rank, world, args.steps, exchange)
 
     line = None
     if rank == 0:
@@ -724,6 +865,8 @@ def run_gpu(args):
             line["update_only_ms_per_step"] = update_ms
         if workloads is not None:
             line["workloads"] = workloads
+        if mixed_case is not None:
+            line["zero1_mixed"] = mixed_case
     if zero1:
         L.gm_zero1_destroy(zero1)
     dev.close()

@@ -99,6 +99,14 @@ struct Device {
     float* scalars = nullptr;           // small device scratch for L-BFGS scalars
 };
 
+// Destinations of a fused update + push kernel: byte offsets from the local arena to each
+// peer's mapping of its own arena (plain peer stores over NVLink).
+constexpr int kMaxPeers = 8;
+struct PeerDst {
+    long long delta[kMaxPeers];
+    int count;                        // number of peers (excluding self)
+};
+
 // ---- error reporting ----
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);   // records and returns GM_ERR_CUDA
@@ -151,8 +159,9 @@ int host_pipelined_step(Device* d, const TensorList* l, const void* host_grads, 
                         const std::function<int(Window)>& launch, const std::function<int()>& finish);
 
 // ---- mixed precision (gm_mixed.cu) ----
+// push: when given, every new fp16 parameter vector is also stored to the peers' arenas
 int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd,
-                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx);
+                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx, const PeerDst* push = nullptr);
 
 // ---- buffer registry (gm_device.cu) ----
 int64_t registered_size(uintptr_t p);   // -1 if unknown

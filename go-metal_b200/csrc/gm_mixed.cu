@@ -342,11 +342,12 @@ __device__ __forceinline__ void st256(float* p, const F8& r) {
 // prefetch).  FAST: the divisions by the two bias corrections use div_const when the
 // published scalars allow it.  PF: while a pass is computed, the lines of the next pass
 // are requested into L2 (no registers held).  CLIP: gradients are multiplied by the
-// published clipping coefficient.
-template <bool WIDE, int MINB, bool FAST, bool PF, bool CLIP>
+// published clipping coefficient.  PUSH: every new fp16 parameter vector is also stored to
+// the same offset of each peer's fp16 arena (sharded step; plain stores over NVLink).
+template <bool WIDE, int MINB, bool FAST, bool PF, bool CLIP, bool PUSH>
 __global__ void __launch_bounds__(kApplyThreads, MINB)
 mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsigned int* __restrict__ flag,
-                    const StepPrep* __restrict__ prep, const MixedScalars sc) {
+                    const StepPrep* __restrict__ prep, const MixedScalars sc, const PeerDst peers) {
     constexpr int NT = kApplyThreads;
     const int tid = threadIdx.x;
     const int T = L.num_tensors;
@@ -404,6 +405,10 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                 unsigned short pi;
                 mixed_elem<false, CLIP>(half_bits_to_float(g[i]), inv_scale, clip, wi, mi, vi, pi, p);
                 w[i] = wi; m[i] = mi; v[i] = vi; o[i] = pi;
+                if (PUSH) {
+                    for (int r = 0; r < peers.count; ++r)
+                        *reinterpret_cast<unsigned short*>(reinterpret_cast<char*>(o + i) + peers.delta[r]) = pi;
+                }
             };
 
             if (h < 0) {
@@ -460,7 +465,12 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                         }
                     }
                     st256(w + b + 8LL * i, W); st256(m + b + 8LL * i, M); st256(v + b + 8LL * i, V);
-                    __stcs(oq8 + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+                    const uint4 packed = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    if (PUSH) {
+                        for (int r = 0; r < peers.count; ++r)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(oq8 + i) + peers.delta[r]) = packed;
+                    }
+                    __stcs(oq8 + i, packed);
                 }
                 const long long tb8 = b + ((long long)nv8 << 3);
                 if (tb8 + tid < e) scalar_at(tb8 + tid);
@@ -488,7 +498,12 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                 mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.y & 0xffffu)), inv_scale, clip, wc.z, mc.z, vc.z, h2, p);
                 mixed_elem<false, CLIP>(half_bits_to_float((unsigned short)(gc.y >> 16)), inv_scale, clip, wc.w, mc.w, vc.w, h3, p);
                 __stcs(wq + i, wc); __stcs(mq + i, mc); __stcs(vq + i, vc);
-                __stcs(oq + i, make_uint2((unsigned)h0 | ((unsigned)h1 << 16), (unsigned)h2 | ((unsigned)h3 << 16)));
+                const uint2 packed = make_uint2((unsigned)h0 | ((unsigned)h1 << 16), (unsigned)h2 | ((unsigned)h3 << 16));
+                if (PUSH) {
+                    for (int r = 0; r < peers.count; ++r)
+                        *reinterpret_cast<uint2*>(reinterpret_cast<char*>(oq + i) + peers.delta[r]) = packed;
+                }
+                __stcs(oq + i, packed);
                 gc = gn; wc = wn; mc = mn; vc = vn;
                 i = nx;
             }
@@ -597,7 +612,7 @@ sumsq_kernel(const DevList L, float inv_scale, float* __restrict__ out) {
 // update kernels with the device address of the overflow word, so that a sharded
 // caller can combine the flag across ranks on the same stream.
 int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, float lr, float eps, float wd,
-                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx) {
+                         int (*hook)(void* ctx, unsigned int* d_flag), void* ctx, const PeerDst* push) {
     Device* d = as_device(device_ptr);
     if (!d) return GM_ERR_NIL_DEVICE;
     Mixed* m = as_mixed(mixed);
@@ -638,7 +653,7 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
     // check kernel followed by the ring update.  They carry neither the norm nor the clipping, and
     // the sharded step needs the flag exchange between check and update, so those keep two launches.
     int ring = d->mixed_ring;
-    if (norm) ring = 0;
+    if (norm || push) ring = 0;
     if (hook && ring == 2) ring = 1;
     if (l->dl.chunk_elems % kCheckElems) ring = 0;
     using RingFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, StepPrep*, const MixedScalars, const float2*,
@@ -693,25 +708,36 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         mixed_prep_kernel<<<1, 32, 0, d->stream>>>(m->d_flag, m->d_state, m->d_table, m->table_len, prep);
         d->launches++;
     }
-    using UpdateFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, const StepPrep*, const MixedScalars);
+    if (push && clipping) { set_error("clipping is not available in the sharded mixed-precision step"); return GM_ERR_UNSUPPORTED; }
+    using UpdateFn = void (*)(const DevList, gm_loss_scale_t*, unsigned int*, const StepPrep*, const MixedScalars, const PeerDst);
+    PeerDst peers{};
+    if (push) peers = *push;
     // Variant 0 (default): 8 elements per thread with 256-bit fp32 accesses, the divisions by the
     // bias corrections through div_const, next-pass L2 prefetch.  GOMETAL_MIXED_FASTDIV=0 and
     // GOMETAL_MIXED_PF=0 switch the last two off; GOMETAL_MIXED_VARIANT=1 selects the older
     // 4-elements-per-thread kernel with a software prefetch.  All produce the same bits.
     UpdateFn update;
-    if (d->mixed_variant == 1) {
-        update = clipping ? mixed_update_kernel<false, 4, false, false, true> : mixed_update_kernel<false, 4, false, false, false>;
+    if (push) {
+        const int sel = (d->mixed_fastdiv ? 1 : 0) | (d->mixed_pf ? 2 : 0);
+        switch (sel) {
+            case 0: update = mixed_update_kernel<true, 4, false, false, false, true>; break;
+            case 1: update = mixed_update_kernel<true, 4, true, false, false, true>; break;
+            case 2: update = mixed_update_kernel<true, 4, false, true, false, true>; break;
+            default: update = mixed_update_kernel<true, 4, true, true, false, true>; break;
+        }
+    } else if (d->mixed_variant == 1) {
+        update = clipping ? mixed_update_kernel<false, 4, false, false, true, false> : mixed_update_kernel<false, 4, false, false, false, false>;
     } else {
         const int sel = (d->mixed_fastdiv ? 1 : 0) | (d->mixed_pf ? 2 : 0) | (clipping ? 4 : 0);
         switch (sel) {
-            case 0: update = mixed_update_kernel<true, 4, false, false, false>; break;
-            case 1: update = mixed_update_kernel<true, 4, true, false, false>; break;
-            case 2: update = mixed_update_kernel<true, 4, false, true, false>; break;
-            case 3: update = mixed_update_kernel<true, 4, true, true, false>; break;
-            case 4: update = mixed_update_kernel<true, 4, false, false, true>; break;
-            case 5: update = mixed_update_kernel<true, 4, true, false, true>; break;
-            case 6: update = mixed_update_kernel<true, 4, false, true, true>; break;
-            default: update = mixed_update_kernel<true, 4, true, true, true>; break;
+            case 0: update = mixed_update_kernel<true, 4, false, false, false, false>; break;
+            case 1: update = mixed_update_kernel<true, 4, true, false, false, false>; break;
+            case 2: update = mixed_update_kernel<true, 4, false, true, false, false>; break;
+            case 3: update = mixed_update_kernel<true, 4, true, true, false, false>; break;
+            case 4: update = mixed_update_kernel<true, 4, false, false, true, false>; break;
+            case 5: update = mixed_update_kernel<true, 4, true, false, true, false>; break;
+            case 6: update = mixed_update_kernel<true, 4, false, true, true, false>; break;
+            default: update = mixed_update_kernel<true, 4, true, true, true, false>; break;
         }
     }
     int grid_u = launch_grid(d, (const void*)update, kApplyThreads, l->dl.num_chunks);
@@ -736,9 +762,9 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = &attr; cfg.numAttrs = 1;
-        GM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, update, l->dl, m->d_state, m->d_flag, (const StepPrep*)prep, sc));
+        GM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, update, l->dl, m->d_state, m->d_flag, (const StepPrep*)prep, sc, peers));
     } else {
-        update<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc);
+        update<<<grid_u, kApplyThreads, 0, d->stream>>>(l->dl, m->d_state, m->d_flag, prep, sc, peers);
     }
     d->launches++;
     GM_CUDA_CHECK(cudaGetLastError());

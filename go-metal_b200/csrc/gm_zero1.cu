@@ -79,17 +79,21 @@ static int nccl_fail(ncclResult_t r, const char* what) {
     return GM_ERR_CUDA;
 }
 
-constexpr int kMaxPeers = 8;
+constexpr int kArenaSlots = 2;         // 0: fp32 parameter arena, 1: fp16 parameter arena (mixed precision)
+
+// One exported arena and the peers' mappings of theirs (index = rank; own entry = local base).
+struct PeerMap {
+    uintptr_t peer_base[kMaxPeers] = {0};
+    bool peer_opened[kMaxPeers] = {false};
+    uintptr_t local_base = 0;
+    size_t local_bytes = 0;            // size of the exported allocation
+};
 
 struct Zero1 {
     Device* dev = nullptr;
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
-    // peer-mapped arena bases for the push path (index = rank; own entry = local base)
-    uintptr_t peer_base[kMaxPeers] = {0};
-    bool peer_opened[kMaxPeers] = {false};
-    uintptr_t local_base = 0;
-    size_t local_bytes = 0;            // size of the exported allocation (0 = unknown)
+    PeerMap map[kArenaSlots];          // peer-mapped arenas for the push paths
     int* barrier_word = nullptr;       // device int used by the closing all-reduce
     bool push_prefetch = true;         // GOMETAL_PUSH_PREFETCH=0 selects the push kernel without the software prefetch
     // copy-engine path: one stream per peer, one event per slice, one "done" event per peer
@@ -110,10 +114,6 @@ static Zero1* as_zero1(uintptr_t h) {
 }
 
 // ---- fused update + push ----
-struct PeerDst {
-    long long delta[kMaxPeers];   // byte offset from the local arena to each peer's mapping
-    int count;                    // number of peers (excluding self)
-};
 
 // Adam over this rank's shard list; every new parameter vector is stored to the
 // local arena and to the same offset of each peer's arena.
@@ -323,7 +323,8 @@ void gm_zero1_destroy(uintptr_t h) {
     for (int r = 0; r < z->world; ++r) {
         if (z->copy_stream[r]) { cudaStreamSynchronize(z->copy_stream[r]); cudaStreamDestroy(z->copy_stream[r]); }
         if (z->copy_done[r]) cudaEventDestroy(z->copy_done[r]);
-        if (z->peer_opened[r]) cudaIpcCloseMemHandle((void*)z->peer_base[r]);
+        for (int slot = 0; slot < kArenaSlots; ++slot)
+            if (z->map[slot].peer_opened[r]) cudaIpcCloseMemHandle((void*)z->map[slot].peer_base[r]);
     }
     for (cudaEvent_t e : z->slice_ready) cudaEventDestroy(e);
     if (z->comm) nccl().CommDestroy(z->comm);
@@ -383,8 +384,17 @@ static int is_allocation_base(uintptr_t arena_base, size_t* alloc_bytes) {
 
 // ---- peer mapping for the push path ----
 int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 64 bytes */) {
+    return gm_zero1_ipc_handle_slot(h, 0, arena_base, out_handle);
+}
+
+int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, rank order */) {
+    return gm_zero1_open_peers_slot(h, 0, handles);
+}
+
+int gm_zero1_ipc_handle_slot(uintptr_t h, int slot, uintptr_t arena_base, void* out_handle /* 64 bytes */) {
     Zero1* z = as_zero1(h);
     if (!z) return GM_ERR_BAD_ARG;
+    if (slot < 0 || slot >= kArenaSlots) { set_error("arena slot %d outside [0,%d)", slot, kArenaSlots); return GM_ERR_BAD_ARG; }
     if (!arena_base || !out_handle) { set_error("nil argument"); return GM_ERR_BAD_ARG; }
     DeviceGuard g(z->dev);
     size_t alloc_bytes = 0;
@@ -407,31 +417,32 @@ int gm_zero1_ipc_handle(uintptr_t h, uintptr_t arena_base, void* out_handle /* 6
                   "(use gm_zero1_adam_step_async, which exchanges through NCCL, instead)");
         return GM_ERR_UNSUPPORTED;
     }
-    z->local_base = arena_base;
-    z->local_bytes = bytes;
+    z->map[slot].local_base = arena_base;
+    z->map[slot].local_bytes = bytes;
     return GM_OK;
 }
 
-int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, rank order */) {
+int gm_zero1_open_peers_slot(uintptr_t h, int slot, const void* handles /* world x 64 bytes, rank order */) {
     Zero1* z = as_zero1(h);
     if (!z) return GM_ERR_BAD_ARG;
+    if (slot < 0 || slot >= kArenaSlots) { set_error("arena slot %d outside [0,%d)", slot, kArenaSlots); return GM_ERR_BAD_ARG; }
     if (!handles) { set_error("handles are nil"); return GM_ERR_BAD_ARG; }
-    if (!z->local_base) { set_error("call gm_zero1_ipc_handle first"); return GM_ERR_BAD_ARG; }
+    if (!z->map[slot].local_base) { set_error("call gm_zero1_ipc_handle first"); return GM_ERR_BAD_ARG; }
     DeviceGuard g(z->dev);
     for (int r = 0; r < z->world; ++r) {
-        if (r == z->rank) { z->peer_base[r] = z->local_base; continue; }
-        if (z->peer_opened[r]) {                 // a new arena replaces an earlier mapping
+        if (r == z->rank) { z->map[slot].peer_base[r] = z->map[slot].local_base; continue; }
+        if (z->map[slot].peer_opened[r]) {                 // a new arena replaces an earlier mapping
             cudaStreamSynchronize(z->dev->stream);
-            cudaIpcCloseMemHandle((void*)z->peer_base[r]);
-            z->peer_opened[r] = false;
-            z->peer_base[r] = 0;
+            cudaIpcCloseMemHandle((void*)z->map[slot].peer_base[r]);
+            z->map[slot].peer_opened[r] = false;
+            z->map[slot].peer_base[r] = 0;
         }
         cudaIpcMemHandle_t mh;
         memcpy(&mh, (const char*)handles + (size_t)r * 64, 64);
         void* p = nullptr;
         GM_CUDA_CHECK(cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
-        z->peer_base[r] = (uintptr_t)p;
-        z->peer_opened[r] = true;
+        z->map[slot].peer_base[r] = (uintptr_t)p;
+        z->map[slot].peer_opened[r] = true;
     }
     return GM_OK;
 }
@@ -439,12 +450,13 @@ int gm_zero1_open_peers(uintptr_t h, const void* handles /* world x 64 bytes, ra
 // Every parameter tensor of the shard must lie inside the exported arena: its address
 // minus the arena base is added to each peer's mapping, and a tensor from elsewhere would
 // turn into a store to an address no peer mapped.
-static int check_inside_arena(const Zero1* z, const TensorList* l) {
-    if (!z->local_base) { set_error("call gm_zero1_ipc_handle and gm_zero1_open_peers first"); return GM_ERR_BAD_ARG; }
+static int check_inside_arena(const Zero1* z, const TensorList* l, const int slot = 0, const int stream = 0,
+                              const int elem_bytes = 4) {
+    if (!z->map[slot].local_base) { set_error("call gm_zero1_ipc_handle and gm_zero1_open_peers first"); return GM_ERR_BAD_ARG; }
     for (size_t t = 0; t < l->numel.size(); ++t) {
-        const uintptr_t p = l->ptrs[0][t];
-        const uintptr_t end = p + (uintptr_t)l->numel[t] * 4;
-        if (p < z->local_base || end > z->local_base + z->local_bytes) {
+        const uintptr_t p = l->ptrs[stream][t];
+        const uintptr_t end = p + (uintptr_t)l->numel[t] * elem_bytes;
+        if (p < z->map[slot].local_base || end > z->map[slot].local_base + z->map[slot].local_bytes) {
             set_error("parameter tensor %zu lies outside the arena exported to the peers", t);
             return GM_ERR_BAD_ARG;
         }
@@ -453,15 +465,23 @@ static int check_inside_arena(const Zero1* z, const TensorList* l) {
 }
 
 // Launches the fused update + push kernel over a window of the shard list (no barrier).
+// rank r stores to r+1, r+2, ... so that at any moment the ranks aim at different peers
+static int peer_destinations(const Zero1* z, const int slot, PeerDst* peers) {
+    peers->count = 0;
+    for (int i = 1; i < z->world; ++i) {
+        const int r = (z->rank + i) % z->world;
+        if (!z->map[slot].peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
+        peers->delta[peers->count++] = (long long)z->map[slot].peer_base[r] - (long long)z->map[slot].local_base;
+    }
+    return GM_OK;
+}
+
 static int push_launch(Zero1* z, const TensorList* l, const gm_hyper_t& hyper, Window win) {
     Device* d = z->dev;
     PeerDst peers{};
-    peers.count = 0;
-    // rank r stores to r+1, r+2, ... so that at any moment the ranks aim at different peers
-    for (int i = 1; i < z->world; ++i) {
-        const int r = (z->rank + i) % z->world;
-        if (!z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
-        peers.delta[peers.count++] = (long long)z->peer_base[r] - (long long)z->local_base;
+    {
+        const int rc = peer_destinations(z, 0, &peers);
+        if (rc != GM_OK) return rc;
     }
     AdamRule::P p;
     p.lr = hyper.lr; p.beta1 = hyper.beta1; p.beta2 = hyper.beta2; p.eps = hyper.eps;
@@ -557,8 +577,9 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
             return GM_ERR_BAD_ARG;
         }
     }
+    const int slot = 0;
     for (int r = 0; r < z->world; ++r) {
-        if (r != z->rank && !z->peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
+        if (r != z->rank && !z->map[slot].peer_base[r]) { set_error("peer %d is not mapped; call gm_zero1_open_peers", r); return GM_ERR_BAD_ARG; }
     }
     {
         const int rc = check_inside_arena(z, l);
@@ -589,7 +610,7 @@ int gm_zero1_adam_dma_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyp
         const size_t bytes = (size_t)(l->ptrs[0][t1 - 1] + (uintptr_t)l->numel[t1 - 1] * 4 - src);
         for (int r = 0; r < z->world; ++r) {
             if (r == z->rank) continue;
-            const uintptr_t dst = src - z->local_base + z->peer_base[r];
+            const uintptr_t dst = src - z->map[slot].local_base + z->map[slot].peer_base[r];
             GM_CUDA_CHECK(cudaStreamWaitEvent(z->copy_stream[r], z->slice_ready[s], 0));
             GM_CUDA_CHECK(cudaMemcpyAsync((void*)dst, (const void*)src, bytes, cudaMemcpyDeviceToDevice, z->copy_stream[r]));
         }
@@ -623,6 +644,26 @@ int gm_zero1_mixed_step_async(uintptr_t h, uintptr_t mixed, uintptr_t shard_list
     int rc = mixed_step_with_hook((uintptr_t)z->dev, mixed, shard_list, lr, eps, wd, zero1_flag_hook, z);
     if (rc != GM_OK) return rc;
     return gm_zero1_allgather_async(h, p16_arena_base, count_per_rank, 2);
+}
+
+// The same step with the exchange fused into the update kernel: every new fp16 parameter
+// vector is stored to the local arena and to the same offset of each peer's fp16 arena
+// (arena slot 1, exported with gm_zero1_ipc_handle_slot / gm_zero1_open_peers_slot); the
+// closing one-word all-reduce is the barrier.  On a skipped step nothing is stored.
+int gm_zero1_mixed_push_step_async(uintptr_t h, uintptr_t mixed, uintptr_t shard_list, float lr, float eps, float wd) {
+    Zero1* z = as_zero1(h);
+    if (!z) return GM_ERR_BAD_ARG;
+    TensorList* l = as_list(shard_list);
+    if (!l) return GM_ERR_BAD_ARG;
+    if (l->dl.num_streams != 5) { set_error("mixed-precision list must be g16, master, m, v, p16"); return GM_ERR_BAD_ARG; }
+    int rc = check_inside_arena(z, l, 1, 4, 2);
+    if (rc != GM_OK) return rc;
+    PeerDst peers{};
+    rc = peer_destinations(z, 1, &peers);
+    if (rc != GM_OK) return rc;
+    rc = mixed_step_with_hook((uintptr_t)z->dev, mixed, shard_list, lr, eps, wd, zero1_flag_hook, z, &peers);
+    if (rc != GM_OK) return rc;
+    return push_barrier(z);
 }
 
 // Gradient hand-off for data-parallel training: every rank holds a full gradient

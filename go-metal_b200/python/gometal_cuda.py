@@ -135,6 +135,9 @@ _SIGS = {
     "gm_zero1_adam_dma_step_async": (i, [u, u, C.POINTER(Hyper), i]),
     "gm_zero1_mixed_step_async": (i, [u, u, u, f, f, f, u, i64]),
     "gm_zero1_reduce_scatter_async": (i, [u, u, i64, i]),
+    "gm_zero1_ipc_handle_slot": (i, [u, i, u, vp]),
+    "gm_zero1_open_peers_slot": (i, [u, i, vp]),
+    "gm_zero1_mixed_push_step_async": (i, [u, u, u, f, f, f]),
     "gm_selftest_const_div": (i, [u, f, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), ip]),
     "gm_selftest_barrier_timeout": (i, [u, C.c_longlong, ip]),
     "gm_device_set_tuning": (i, [u, C.c_char_p, C.c_longlong]),

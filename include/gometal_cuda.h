@@ -374,6 +374,16 @@ int gm_zero1_adam_dma_step_async(uintptr_t zero1, uintptr_t shard_list, const gm
 int gm_zero1_mixed_step_async(uintptr_t zero1, uintptr_t mixed, uintptr_t shard_list, float lr, float eps,
                               float weight_decay, uintptr_t p16_arena_base, int64_t count_per_rank);
 
+/* The same step with the exchange fused into the update kernel: every new fp16 parameter
+ * vector is stored to the local fp16 arena and to the same offset of each peer's, by plain
+ * stores over NVLink, and a one-word all-reduce closes the step.  The fp16 arena is a
+ * second exported arena: slot 1 of gm_zero1_ipc_handle_slot / gm_zero1_open_peers_slot
+ * (slot 0 is the fp32 arena of gm_zero1_ipc_handle / gm_zero1_open_peers). */
+int gm_zero1_ipc_handle_slot(uintptr_t zero1, int slot, uintptr_t arena_base, void* out_handle);
+int gm_zero1_open_peers_slot(uintptr_t zero1, int slot, const void* handles);
+int gm_zero1_mixed_push_step_async(uintptr_t zero1, uintptr_t mixed, uintptr_t shard_list, float lr, float eps,
+                                   float weight_decay);
+
 /* Gradient hand-off of data-parallel training: in-place reduce-scatter (sum) of
  * the full gradient arena; afterwards rank r's shard holds the sum over ranks. */
 int gm_zero1_reduce_scatter_async(uintptr_t zero1, uintptr_t grad_arena_base, int64_t count_per_rank, int elem_bytes);

@@ -117,7 +117,8 @@ def main():
         if exchange == "nccl":
             dev.free(arena)
         # the pushed arena stays mapped by the peers until the group is destroyed
-    mixed_zero1(L, dev, z, plan, rank)
+    mixed_zero1(L, dev, z, plan, rank, "nccl")
+    mixed_zero1(L, dev, z, plan, rank, "push")
     reduce_scatter(L, dev, z, plan, rank, world)
     dist.barrier()
     L.gm_zero1_destroy(z)
@@ -143,10 +144,12 @@ def reduce_scatter(L, dev, z, plan, rank, world):
     dev.free(arena)
 
 
-def mixed_zero1(L, dev, z, plan, rank):
+def mixed_zero1(L, dev, z, plan, rank, exchange):
     """Mixed-precision Adam with sharded fp16 gradients: an overflow in ONE rank's shard
     must make every rank skip; states, master shards and the gathered fp16 arena
-    must equal the oracle's run over all tensors."""
+    must equal the oracle's run over all tensors.  exchange: the fp16 parameters travel by
+    the NCCL all-gather or by peer stores from inside the update kernel."""
+    world = dist.get_world_size()
     sizes = [E] * T
     master = [O.fill_uniform(E, -0.05, 0.05, 93, k) for k in range(T)]
     mm = [np.zeros(E, np.float32) for _ in range(T)]
@@ -166,13 +169,26 @@ def mixed_zero1(L, dev, z, plan, rank):
                         good_steps=0, adam_t=0, skipped=0, last_overflow=0)
     mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
     assert mx, gm.last_error()
+    if exchange == "push":
+        mine = (C.c_ubyte * 64)()
+        assert L.gm_zero1_ipc_handle_slot(z, 2, p16_arena, mine) == -10, "only slots 0 and 1 exist"
+        gm.check(L.gm_zero1_ipc_handle_slot(z, 1, p16_arena, mine), "ipc handle (fp16 arena)")
+        mine_t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device="cuda")
+        all_t = [torch.empty_like(mine_t) for _ in range(world)]
+        dist.all_gather(all_t, mine_t)
+        blob = bytes(b for tt in all_t for b in tt.cpu().tolist())
+        gm.check(L.gm_zero1_open_peers_slot(z, 1, (C.c_ubyte * len(blob))(*blob)), "open peers (fp16 arena)")
+        dist.barrier()
     for step in range(1, 6):
         g16 = [O.f32_to_f16(O.fill_normal(E, 0.0, 1e-3, 93, 100 * step + k) * np.float32(st.scale)) for k in range(T)]
         if step == 2:
             g16[0][17] = 0x7c00                  # +inf in rank 0's shard only
         dev.upload(d_g, np.concatenate([g16[k] for k in own]))
         dist.barrier()
-        gm.check(L.gm_zero1_mixed_step_async(z, mx, lst, LR, EPS, WD, p16_arena, plan.shard_elems), "zero1 mixed step")
+        if exchange == "push":
+            gm.check(L.gm_zero1_mixed_push_step_async(z, mx, lst, LR, EPS, WD), "zero1 mixed push step")
+        else:
+            gm.check(L.gm_zero1_mixed_step_async(z, mx, lst, LR, EPS, WD, p16_arena, plan.shard_elems), "zero1 mixed step")
         O.mixed_adam_step(g16, master, mm, vv, p16, LR, B1, B2, EPS, WD, st)
         got = gm.LossScale()
         gm.check(L.gm_mixed_get_state(dev.h, mx, C.byref(got)), "state")
@@ -187,8 +203,9 @@ def mixed_zero1(L, dev, z, plan, rank):
     assert st.skipped == 1
     L.gm_mixed_destroy(mx)
     L.gm_tensor_list_destroy(lst)
-    for p in (p16_arena, d_master, d_m, d_v, d_g):
-        dev.free(p)
+    dist.barrier()
+    for p in (d_master, d_m, d_v, d_g) + (() if exchange == "push" else (p16_arena,)):
+        dev.free(p)                              # a pushed arena stays mapped by the peers until the group is destroyed
 
 
 if __name__ == "__main__":
