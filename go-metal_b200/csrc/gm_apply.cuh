@@ -86,6 +86,26 @@ __device__ __forceinline__ float cta_sum_256(float acc, float* warp_sum) {
     return total;
 }
 
+// ---- pieces of the bounded grid-wide barrier of the single-launch steps ----
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+// Waits until *word == epoch, but no longer than `budget` clock cycles.  False: gave up.
+__device__ __forceinline__ bool bounded_wait_for(const unsigned* word, const unsigned epoch, const long long budget) {
+    const long long t0 = clock64();
+    while (ld_acquire(word) != epoch) {
+        if (clock64() - t0 > budget) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
 // Streaming accesses: every byte is touched once per step, so lines are marked
 // evict-first on the way in and on the way out.
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }

@@ -163,6 +163,7 @@ static Device* make_device(int ordinal) {
     if (const char* e = getenv("GOMETAL_MIXED_FASTDIV")) d->mixed_fastdiv = atoi(e);
     if (const char* e = getenv("GOMETAL_MIXED_PF")) d->mixed_pf = atoi(e);
     if (const char* e = getenv("GOMETAL_MIXED_RING")) d->mixed_ring = atoi(e);
+    if (const char* e = getenv("GOMETAL_LBFGS_COOP")) d->lbfgs_coop = atoi(e);
     if (const char* e = getenv("GOMETAL_BARRIER_BUDGET_CYCLES")) { const long long v = atoll(e); if (v > 0) d->barrier_budget_cycles = v; }
     if (const char* e7 = getenv("GOMETAL_MIXED_CHECK_PERSISTENT")) d->mixed_check_persistent = atoi(e7);
     if (const char* e3 = getenv("GOMETAL_CHUNK_ELEMS")) d->chunk_elems = atoi(e3);

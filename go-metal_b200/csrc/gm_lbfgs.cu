@@ -376,6 +376,10 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
     finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
 }
 
+}  // namespace gm
+#include "gm_lbfgs_coop.cuh"
+namespace gm {
+
 // ---- host side ----
 struct LbfgsCtx {
     void* blob = nullptr;
@@ -490,6 +494,26 @@ void lbfgs_release_device(Device* d) {
     g_lb.erase(it);
 }
 
+// Grid of the single-launch step (one CTA per SM), or 0 when it cannot serve this problem:
+// too many chunks for the on-chip storage, too long a history, or no cooperative launch.
+static int coop_grid(Device* d, int num_chunks, int m) {
+    if (m > kCoopMaxHistory) return 0;
+    static thread_local int prepared = 0;      // 1 ready, -1 unavailable
+    if (prepared == 0) {
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, d->ordinal);
+        cudaError_t e = cudaFuncSetAttribute((const void*)lbfgs_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kCoopSmemBytes);
+        int per_sm = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)lbfgs_coop_kernel, kCoopThreads, kCoopSmemBytes);
+        if (e != cudaSuccess) cudaGetLastError();
+        prepared = (coop && e == cudaSuccess && per_sm >= 1) ? 1 : -1;
+    }
+    if (prepared < 0) return 0;
+    const int grid = d->sm_count < num_chunks ? d->sm_count : num_chunks;
+    if ((long long)grid * kCoopMaxChunksPerCta < num_chunks) return 0;
+    return grid;
+}
+
 static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in, const bool overlap = true) {
     LbfgsOp op = op_in;
     // Every pass after the first of a step is launched so that it may start while its
@@ -559,6 +583,66 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
     auto rho_of = [&](int idx) { return (const float*)rho_bufs[idx]; };
     auto col_s = [&](int idx) { return COL_HIST + idx; };
     auto col_y = [&](int idx) { return COL_HIST + m + idx; };
+
+    if (d->lbfgs_coop) {
+        const int grid = coop_grid(d, c->tb.num_chunks, m);
+        if (grid > 0) {
+            CoopPlan plan{};
+            int np = 0;
+            {
+                CoopPass& p0 = plan.pass[np++];
+                p0 = CoopPass{0, -1, -1, -1, -1, -1, 0, -1, -1};
+                if (hc > 0) { const int idx = slot(hc - 1); p0.col_dot = col_s(idx); p0.rho_dot = idx; p0.epilogue = 1; p0.out_alpha = hc - 1; }
+            }
+            for (int j = hc - 1; j >= 0; --j) {
+                const int idx = slot(j);
+                CoopPass& ps = plan.pass[np++];
+                ps = CoopPass{1, col_y(idx), -1, idx, -1, j, 0, -1, -1};
+                if (j > 0) { const int nx = slot(j - 1); ps.col_dot = col_s(nx); ps.rho_dot = nx; ps.epilogue = 1; ps.out_alpha = j - 1; }
+                else { const int nx = slot(0); ps.col_dot = col_y(nx); ps.rho_dot = nx; ps.epilogue = 2; ps.alpha_in = 0; }
+            }
+            for (int j = 0; j < hc; ++j) {
+                const int idx = slot(j);
+                CoopPass& ps = plan.pass[np++];
+                ps = CoopPass{2, col_s(idx), -1, idx, -1, -1, 0, -1, -1};
+                if (j + 1 < hc) { const int nx = slot(j + 1); ps.col_dot = col_y(nx); ps.rho_dot = nx; ps.epilogue = 2; ps.alpha_in = j + 1; }
+            }
+            const int prev = (hi - 1 + m) % m;
+            plan.pass[np++] = CoopPass{3, -1, -1, -1, -1, -1, hc > 0 ? 3 : 0, -1, -1};
+            plan.num_passes = np;
+            plan.history = m;
+            plan.descent = (d->lbfgs_mode & 2) ? 1 : 0;
+            plan.corrected = (d->lbfgs_mode & 1) ? 1 : 0;
+            plan.have_pair = hc > 0 ? 1 : 0;
+            plan.col_s_new = col_s(hi); plan.col_y_prev = col_y(prev); plan.col_s_prev = col_s(prev);
+            plan.step = initial_step;
+            plan.epoch_base = d->lbfgs_epoch;
+            d->lbfgs_epoch += (unsigned)np + 1u;
+            for (int k = 0; k < m; ++k) plan.rho[k] = (const float*)rho_bufs[k];
+            plan.alpha = alpha;
+            plan.rho_prev = (float*)rho_bufs[prev];
+            plan.barrier_budget = d->barrier_budget_cycles;
+            rc = ensure_partials(d, 2LL * c->tb.num_chunks);
+            if (rc != GM_OK) return rc;
+            LbfgsTable tbv = c->tb;
+            float* partials = d->partials;
+            unsigned int* ctl = d->ticket;
+            void* args[] = {&tbv, &plan, &partials, &ctl};
+            GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_coop_kernel, dim3(grid), dim3(kCoopThreads), args,
+                                                      kCoopSmemBytes, d->stream));
+            d->launches++;
+            if (step_size) *step_size = initial_step;
+            GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));
+            unsigned int failed = 0;
+            GM_CUDA_CHECK(cudaMemcpy(&failed, d->ticket + kLbError, sizeof(failed), cudaMemcpyDeviceToHost));
+            if (failed) {
+                GM_CUDA_CHECK(cudaMemset(d->ticket + kLbArrive, 0, 3 * sizeof(unsigned int)));
+                set_error("a grid-barrier wait of the single-launch L-BFGS step ran out; the step is incomplete");
+                return GM_ERR_TIMEOUT;
+            }
+            return GM_OK;
+        }
+    }
 
     LbfgsOp op{};
     // q = -g, fused with the dot the newest pair needs

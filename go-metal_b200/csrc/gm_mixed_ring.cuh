@@ -69,15 +69,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
-__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
-}
-
 // Where global tile qg lies: tensor, chunk bounds and this thread's vector in it.
 struct TileRef {
     int t, k, j, h;              // tensor, chunk inside the tensor, tile inside the chunk, head of the tensor
@@ -104,16 +95,6 @@ __device__ __forceinline__ TileRef locate_tile(const DevList& L, const int tiles
     r.valid = i < nvec;
     r.off = r.b + V * i;
     return r;
-}
-
-// Waits until *word == epoch, but no longer than `budget` clock cycles.  False: gave up.
-__device__ __forceinline__ bool bounded_wait_for(const unsigned* word, const unsigned epoch, const long long budget) {
-    const long long t0 = clock64();
-    while (ld_acquire(word) != epoch) {
-        if (clock64() - t0 > budget) return false;
-        __nanosleep(64);
-    }
-    return true;
 }
 
 // FUSED: the overflow check and the grid barrier run inside this kernel (cooperative launch);
