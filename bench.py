@@ -226,8 +226,9 @@ def _entry(name, params, ms, algorithmic_bpp, dram_bpp, dram_basis, peak, **extr
     return d
 
 
-def workload_mixed(gm, dev, torch, peak, reps):
-    """Mixed-precision Adam on 25,165,824 parameters in 48 ragged tensors packed back to back."""
+def workload_mixed(gm, dev, torch, peak, reps, clip=False):
+    """Mixed-precision Adam on 25,165,824 parameters in 48 ragged tensors packed back to back;
+    clip: with global-norm clipping (the norm is formed by the overflow-check pass)."""
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from workloads import ragged_sizes
@@ -251,6 +252,8 @@ def workload_mixed(gm, dev, torch, peak, reps):
     mx = L.gm_mixed_create(dev.h, C.byref(init), B1, B2, 0)
     if not mx:
         raise SystemExit("mixed state: " + gm.last_error())
+    if clip:
+        gm.check(L.gm_mixed_set_clip(mx, 0.1), "clip")         # ||g|| is about 1e-3 * sqrt(25.2 M) = 5: every step is clipped
     torch.cuda.synchronize()
     ms = _event_timed(gm, dev, lambda: gm.check(L.gm_mixed_step_async(dev.h, mx, lst, LR, EPS, WD), "mixed"), reps)
     st = gm.LossScale()
@@ -258,7 +261,10 @@ def workload_mixed(gm, dev, torch, peak, reps):
     L.gm_mixed_destroy(mx)
     L.gm_tensor_list_destroy(lst)
     del g16, w, m, v, p16
-    return _entry("mixed-precision Adam, 25,165,824 params in 48 ragged tensors (config 3)", n, ms, 30, 28,
+    name = "mixed-precision Adam, 25,165,824 params in 48 ragged tensors (config 3)"
+    if clip:
+        name += " with global-norm clipping"
+    return _entry(name, n, ms, 30, 28,
                   "28 B/param: fp16 gradients once (the update re-reads them from L2), master/m/v read and "
                   "written, fp16 parameters written; ncu measured 705 MB per step = 28.0 B/param", peak,
                   kernels="mixed_check_kernel + mixed_update_kernel", steps_timed=reps, clean_steps=int(st.adam_t),
@@ -326,6 +332,22 @@ def workload_rules(gm, dev, torch, peak, reps):
         ("AdaGrad", gm.RULE_ADAGRAD, ["w", "g", "s1"], 20, dict(lr=0.01, eps=1e-10)),
     ]
     out = []
+    # fp32 Adam with global-norm clipping: the fixed-order norm pass (4 B/param) and the clipped step (28)
+    bufs["w"].uniform_(-0.05, 0.05, generator=gen)
+    lst = dev.tensor_list([ptrs[k] for k in ("w", "g", "s1", "s2")], [per] * nt)
+    hy = gm.Hyper(lr=LR, beta1=B1, beta2=B2, eps=EPS, step=1)
+    cnt = {"t": 0}
+
+    def clipped():
+        cnt["t"] += 1
+        hy.step = cnt["t"]
+        gm.check(L.gm_step_with_clip_async(dev.h, gm.RULE_ADAM, lst, C.byref(hy), 1.0), "clipped adam")
+
+    ms = _event_timed(gm, dev, clipped, reps)
+    out.append(_entry("Adam with global-norm clipping, fp32, 2^28 params in 64 tensors", n, ms, 32, 32,
+                      "gradients read twice (norm pass, then the step): 4 + 28 B/param", peak,
+                      kernels="sumsq_canonical_kernel + mta_apply_kernel<AdamRule, clip>", steps_timed=reps))
+    L.gm_tensor_list_destroy(lst)
     for name, rule, streams, bpp, hp in rules:
         bufs["w"].uniform_(-0.05, 0.05, generator=gen)         # one rule's state is not a valid state of the next
         bufs["s1"].zero_()
@@ -358,7 +380,8 @@ def run_only(args):
     torch.cuda.set_device(0)
     dev = gm.Device(0)
     peak, _ = measured_peak_gbs()
-    fn = {"mixed": workload_mixed, "lbfgs": workload_lbfgs, "rules": workload_rules}[args.only]
+    fn = {"mixed": workload_mixed, "mixed_clip": lambda *a: workload_mixed(*a, clip=True), "lbfgs": workload_lbfgs,
+          "rules": workload_rules}[args.only]
     out = fn(gm, dev, torch, peak, max(args.steps, 1))
     dev.close()
     print(json.dumps({"only": args.only, "result": out}))
@@ -506,6 +529,8 @@ def mixed_scaling_case(gm, dev, torch, dist, zero1, rank, world, steps, exchange
 def run_workloads(gm, dev, torch, reps):
     peak, peak_kind = measured_peak_gbs()
     entries = [workload_mixed(gm, dev, torch, peak, max(reps, 20))]
+    torch.cuda.empty_cache()
+    entries.append(workload_mixed(gm, dev, torch, peak, max(reps, 20), clip=True))
     torch.cuda.empty_cache()
     entries.append(workload_lbfgs(gm, dev, torch, peak, max(reps // 2, 8)))
     torch.cuda.empty_cache()
@@ -894,7 +919,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,
                     help="profiling runs only: fewer 4 Mi tensors than the 256 of the workload")
-    ap.add_argument("--only", choices=["mixed", "lbfgs", "rules"],
+    ap.add_argument("--only", choices=["mixed", "mixed_clip", "lbfgs", "rules"],
                     help="profiling runs only: time one of the other configurations alone for --steps repetitions")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,6 +1,16 @@
 // gm_lbfgs_coop.cuh -- one L-BFGS step as ONE cooperative launch with the direction
 // vector kept on chip.  Included by gm_lbfgs.cu (it uses LbfgsTable and the column layout).
 //
+// MEASURED SLOWER than the multi-launch step and therefore not the default (n = 10^7,
+// history 10 on B200: 0.815 ms per step against 0.507 ms; "lbfgs_coop" of
+// gm_device_set_tuning selects it).  What it shows: at this size the direction vector
+// fills the chip -- 13 chunks of shared memory and 32 registers per thread on every SM --
+// and what is left cannot keep enough loads in flight: 512 threads with 64 bytes each are
+// 32 KB per SM where a B200 needs about 100 KB to stream at full rate, so a pass costs
+// ~37 us instead of the 23 us of the multi-launch pass that re-reads the direction from L2.
+// It stays in the library as the step that needs one launch, and for the bounded grid
+// barrier it carries.
+//
 // The multi-launch step (gm_lbfgs.cu) runs 2h+2 passes; in each loop pass the direction
 // is read and rewritten (through L2, where it is kept resident) while two history vectors
 // stream in from DRAM.  Here the direction never leaves the SMs between passes: every CTA
