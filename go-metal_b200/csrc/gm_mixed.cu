@@ -289,10 +289,12 @@ mixed_check_kernel(const DevList L, unsigned int* __restrict__ flag, const gm_lo
 
 // Grid of the check kernel: the CTAs resident at once, trimmed so that every CTA
 // walks the same number of chunks.
-static int check_grid(Device* d, int num_chunks) {
-    static thread_local int per_sm = 0;
+static int check_grid(Device* d, int num_chunks, bool norm) {
+    static thread_local int per_sm_of[2] = {0, 0};      // the two instantiations differ in registers
+    int& per_sm = per_sm_of[norm ? 1 : 0];
     if (per_sm == 0) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel<true>, kApplyThreads, 0);
+        if (norm) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel<true>, kApplyThreads, 0);
+        else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mixed_check_kernel<false>, kApplyThreads, 0);
         if (per_sm < 1) per_sm = 1;
     }
     const long long resident = (long long)per_sm * d->sm_count;
@@ -645,7 +647,7 @@ int mixed_step_with_hook(uintptr_t device_ptr, uintptr_t mixed, uintptr_t list, 
         if (rc != GM_OK) return rc;
     }
     DeviceGuard g(d);
-    int grid_c = check_grid(d, l->dl.num_chunks);
+    int grid_c = check_grid(d, l->dl.num_chunks, norm);
     StepPrep* prep = reinterpret_cast<StepPrep*>(m->d_flag + 16);
     const int check_flags = (d->mixed_keep_g ? 1 : 0) | (d->mixed_overlap == 1 ? 2 : 0);
 
