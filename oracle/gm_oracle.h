@@ -2,7 +2,7 @@
  * gm_oracle.h -- CPU oracle for the go-metal optimizer-step path.
  *
  * TEST INFRASTRUCTURE, NOT PRODUCT.  Only the test-suite, the smoke check and
- * the benchmark's CPU-baseline leg may link or call this code, and only as the
+ * the benchmark's CPU-baseline leg and parity checks may link or call this code, and only as the
  * checker / the timed baseline.  The CUDA library never routes through it.
  *
  * PARITY UNPINNED: the reference computes every update rule inside Apple's

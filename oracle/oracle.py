@@ -1,7 +1,7 @@
 """ctypes access to the CPU oracle (oracle/gm_oracle.c).
 
 TEST INFRASTRUCTURE, NOT PRODUCT: imported only by tests/, by the smoke check
-and by the benchmark's CPU-baseline leg.  Parity unpinned -- the reference has
+and by the benchmark's CPU-baseline leg and parity checks.  Parity unpinned -- the reference has
 no golden vector for an optimizer step (see gm_oracle.h).
 """
 from __future__ import annotations

@@ -110,7 +110,7 @@ def test_memory_manager_reuses_and_caps(env):
 
 
 def test_memory_manager_on_a_flat_arena(H, fake):
-    """The north-star pool: one flat 256-byte-aligned arena instead of per-tier device
+    """The arena-backed pool: one flat 256-byte-aligned arena instead of per-tier device
     allocations.  The reference's tier caps (100 buffers of 1 KB) no longer bind, only the
     arena's size; released buffers are reused; nothing is allocated from or returned to the
     device one by one; the arena goes when the manager goes."""

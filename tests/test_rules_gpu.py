@@ -1,7 +1,7 @@
 """GPU parity of the six elementwise rules against the CPU oracle, called
 through the drop-in C entries (execute_*_step_cuda).
 
-Tolerance: the north-star bound is 2 ulp per step and 1e-5 relative after 100
+Tolerance: the required bound is 2 ulp per step and 1e-5 relative after 100
 steps.  The kernels use the same IEEE operations in the same order as the
 oracle, so the tests first demand bit equality and report the ulp distance if
 that ever fails.
