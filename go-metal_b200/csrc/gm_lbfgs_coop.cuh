@@ -23,7 +23,7 @@
 //
 // The chunk -> lane map, the xor tree, the order of the warp sums and of the chunk sums
 // are those of the multi-launch kernels, and so is every statement on an element: the two
-// produce the same bits (tests/test_lbfgs_gpu.py runs both against the oracle).
+// produce the same bits (the parity tests run both).
 //
 // Capacity: 17 chunks per SM, i.e. 17 * 148 * 4096 = 10,305,536 elements on B200; longer
 // problems, more than kCoopMaxHistory pairs, or a device without cooperative launch take
