@@ -200,6 +200,20 @@ func (m *MixedAdam) GradSumSq() (float32, error) {
 	return float32(out), stepError("grad norm", rc)
 }
 
+// SetClip turns global-norm gradient clipping on (maxNorm > 0) or off (0): the overflow-check
+// pass forms the norm of the unscaled gradients in a fixed order and the update multiplies
+// every gradient by min(1, maxNorm/(norm+1e-6)) before the Adam rule.  LastClip waits for the
+// stream and returns the last step's sum of squares and coefficient.
+func (m *MixedAdam) SetClip(maxNorm float32) error {
+	return stepError("clip", C.gm_mixed_set_clip(m.h, C.float(maxNorm)))
+}
+
+func (m *MixedAdam) LastClip() (sumSq, coef float32, err error) {
+	var s, c C.float
+	rc := C.gm_mixed_last_clip(handle(m.device), m.h, &s, &c)
+	return float32(s), float32(c), stepError("clip", rc)
+}
+
 func (m *MixedAdam) Destroy() { C.gm_mixed_destroy(m.h); m.h = 0 }
 
 // StepHost runs one step with the gradients in (pinned) host memory and the new

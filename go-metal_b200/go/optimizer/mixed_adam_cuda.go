@@ -183,6 +183,12 @@ func (o *MixedAdamOptimizerState) Step(gradientBuffers []unsafe.Pointer) error {
 	return nil
 }
 
+// SetGradClip turns global-norm gradient clipping on (maxNorm > 0) or off (0); LastClip
+// returns the last step's sum of squared unscaled gradients and clipping coefficient.
+func (o *MixedAdamOptimizerState) SetGradClip(maxNorm float32) error { return o.mixed.SetClip(maxNorm) }
+
+func (o *MixedAdamOptimizerState) LastClip() (float32, float32, error) { return o.mixed.LastClip() }
+
 // LossScale waits for the stream and reads the device-resident loss-scale state.
 func (o *MixedAdamOptimizerState) LossScale() (cgo_bridge.LossScale, error) { return o.mixed.State() }
 

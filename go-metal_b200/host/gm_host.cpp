@@ -57,6 +57,8 @@ std::string Backend::load(const std::string& path) {
     resolve(h, "gm_mixed_step_async", &b.mixed_step, &optional);
     resolve(h, "gm_mixed_get_state", &b.mixed_get_state, &optional);
     resolve(h, "gm_mixed_set_state", &b.mixed_set_state, &optional);
+    resolve(h, "gm_mixed_set_clip", &b.mixed_set_clip, &optional);
+    resolve(h, "gm_mixed_last_clip", &b.mixed_last_clip, &optional);
     resolve(h, "gm_tensor_list_create", &b.list_create, &optional);
     resolve(h, "gm_tensor_list_destroy", &b.list_destroy, &optional);
     resolve(h, "gm_device_synchronize", &b.device_synchronize, &optional);

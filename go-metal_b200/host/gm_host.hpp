@@ -53,6 +53,8 @@ struct Backend {
     int (*mixed_step)(uintptr_t, uintptr_t, uintptr_t, float, float, float) = nullptr;
     int (*mixed_get_state)(uintptr_t, uintptr_t, LossScaleC*) = nullptr;
     int (*mixed_set_state)(uintptr_t, uintptr_t, const LossScaleC*) = nullptr;
+    int (*mixed_set_clip)(uintptr_t, float) = nullptr;
+    int (*mixed_last_clip)(uintptr_t, uintptr_t, float*, float*) = nullptr;
     uintptr_t (*list_create)(uintptr_t, int, int, const uintptr_t* const*, const int64_t*, const int*) = nullptr;
     void (*list_destroy)(uintptr_t) = nullptr;
     int (*device_synchronize)(uintptr_t) = nullptr;
@@ -229,6 +231,10 @@ public:
     std::string ReadMaster(int index, float* out, int numel);
     // waits for the stream; the device-resident loss-scale state
     std::string LossScale(Backend::LossScaleC* out);
+    // global-norm gradient clipping: maxNorm > 0 turns it on, 0 off; LastClip waits for the stream and
+    // returns the last step's sum of squared unscaled gradients and the coefficient applied
+    std::string SetGradClip(float maxNorm);
+    std::string LastClip(float* sumSq, float* coef);
 
 private:
     friend std::unique_ptr<MixedAdamOptimizerState> NewMixedAdamOptimizer(const MixedAdamConfig&, const Shapes&, memory::MemoryManager*, uintptr_t, std::string*);

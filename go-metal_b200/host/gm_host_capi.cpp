@@ -223,6 +223,15 @@ GMH_API int gmh_mixed_loss_scale(void* h, void* out) {
     return m ? fail(m->LossScale(static_cast<Backend::LossScaleC*>(out))) : fail("not a MixedAdam optimizer");
 }
 
+GMH_API int gmh_mixed_set_clip(void* h, float max_norm) {
+    auto* m = as_mixed(h);
+    return m ? fail(m->SetGradClip(max_norm)) : fail("not a MixedAdam optimizer");
+}
+GMH_API int gmh_mixed_last_clip(void* h, float* sum_sq, float* coef) {
+    auto* m = as_mixed(h);
+    return m ? fail(m->LastClip(sum_sq, coef)) : fail("not a MixedAdam optimizer");
+}
+
 GMH_API int gmh_lbfgs_history(void* h, int* count, int* index) {
     auto* o = static_cast<OptHandle*>(h);
     if (!o->lbfgs) return -1;

@@ -122,6 +122,20 @@ std::string MixedAdamOptimizerState::Step(const std::vector<uintptr_t>& grads) {
     return "";
 }
 
+std::string MixedAdamOptimizerState::SetGradClip(float maxNorm) {
+    if (!backend().mixed_set_clip) return "the backend has no gradient clipping";
+    int rc = backend().mixed_set_clip(mixed_, maxNorm);
+    if (rc != 0) return fmt("failed to set the clipping norm: error code %d (%s)", rc, backend_error());
+    return "";
+}
+
+std::string MixedAdamOptimizerState::LastClip(float* sumSq, float* coef) {
+    if (!backend().mixed_last_clip) return "the backend has no gradient clipping";
+    int rc = backend().mixed_last_clip(device_, mixed_, sumSq, coef);
+    if (rc != 0) return fmt("failed to read the clipping result: error code %d (%s)", rc, backend_error());
+    return "";
+}
+
 std::string MixedAdamOptimizerState::LossScale(Backend::LossScaleC* out) {
     int rc = backend().mixed_get_state(device_, mixed_, out);
     if (rc != 0) return fmt("failed to read the loss-scale state: error code %d (%s)", rc, backend_error());

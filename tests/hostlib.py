@@ -60,6 +60,7 @@ def load_host():
         "gmh_optimizer_stat": (d, [vp, s]), "gmh_optimizer_get_state": (vp, [vp]), "gmh_optimizer_load_state": (i, [vp, vp]),
         "gmh_mixed_init_master": (i, [vp, i, vp, i]), "gmh_mixed_read_master": (i, [vp, i, vp, i]),
         "gmh_mixed_loss_scale": (i, [vp, vp]),
+        "gmh_mixed_set_clip": (i, [vp, f]), "gmh_mixed_last_clip": (i, [vp, C.POINTER(f), C.POINTER(f)]),
         "gmh_lbfgs_history": (i, [vp, ip, ip]), "gmh_lbfgs_read_rho": (i, [vp, vp, i]),
         "gmh_sched_create": (vp, [i, i, d, d, s]), "gmh_sched_destroy": (None, [vp]), "gmh_sched_get_lr": (d, [vp, i, i, d]),
         "gmh_sched_step": (d, [vp, d, d]), "gmh_sched_name": (s, [vp]), "gmh_apply_scheduler": (i, [vp, vp, i, i, d]),

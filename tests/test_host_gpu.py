@@ -354,3 +354,59 @@ def test_synchronize_with_a_deadline(gm, dev):
         L.gm_tensor_list_destroy(lst)
         for p in bufs:
             dev.free(p)
+
+
+def test_mixed_adam_gradient_clipping_through_host_mirror(gm, H, oracle):
+    """SetGradClip on the MixedAdam optimizer type: the norm, the coefficient and the clipped
+    update match the oracle bit for bit (the mirror's buffers are all 256-byte aligned, so
+    every tensor's offset from a 16-byte boundary is 0)."""
+    O, L = oracle, gm.lib
+    dev = H.gmh_device_create()
+    assert dev, HL.err(H)
+    mm = H.gmh_mm_create(dev)
+    shapes, sizes = [[9000], [130], [64, 33]], [9000, 130, 2112]
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.999, 1e-8, 0.0
+    master = [O.fill_uniform(n, -0.05, 0.05, 23, 50 + k) for k, n in enumerate(sizes)]
+    m = [np.zeros(n, np.float32) for n in sizes]
+    v = [np.zeros(n, np.float32) for n in sizes]
+    p16 = [O.f32_to_f16(w) for w in master]
+    st = O.new_loss_scale(interval=2000)
+
+    def alloc16(arr):
+        p = L.allocate_cuda_buffer(dev, arr.size * 2, 1)
+        assert p, gm.last_error()
+        gm.check(L.copy_data_to_cuda_buffer(p, arr.ctypes.data, arr.size * 2), "upload")
+        return p
+
+    wp = [alloc16(a) for a in p16]
+    gp = [alloc16(np.zeros(n, np.uint16)) for n in sizes]
+    opt = HL.make_optimizer(H, "MixedAdam", [lr, b1, b2, eps, wd, 65536.0, 2.0, 0.5, 2000], shapes, mm, dev)
+    assert opt, HL.err(H)
+    try:
+        assert H.gmh_optimizer_set_weight_buffers(opt, HL.uarr(wp), 3) == 0
+        for t, w in enumerate(master):
+            assert H.gmh_mixed_init_master(opt, t, w.ctypes.data, w.size) == 0, HL.err(H)
+        assert H.gmh_mixed_set_clip(opt, 0.05) == 0, HL.err(H)
+        assert H.gmh_mixed_set_clip(opt, -1.0) != 0
+        rng = np.random.default_rng(6)
+        for step in range(1, 6):
+            g16 = [O.scale_to_f16((rng.standard_normal(n) * 1e-3).astype(np.float32), st.scale) for n in sizes]
+            for p, g in zip(gp, g16):
+                gm.check(L.copy_data_to_cuda_buffer(p, g.ctypes.data, g.size * 2), "upload")
+            assert H.gmh_optimizer_step(opt, HL.uarr(gp), 3, 0.0) == 0, HL.err(H)
+            skipped, ss, coef = O.mixed_adam_step_clipped(g16, master, m, v, p16, lr, b1, b2, eps, wd, 0.05, [0, 0, 0], 8192, st)
+            got_ss, got_coef = C.c_float(), C.c_float()
+            assert H.gmh_mixed_last_clip(opt, C.byref(got_ss), C.byref(got_coef)) == 0, HL.err(H)
+            assert not skipped and 0 < coef < 1
+            assert np.float32(got_ss.value).view(np.uint32) == ss.view(np.uint32), f"step {step}: {got_ss.value} vs {ss}"
+            assert np.float32(got_coef.value).view(np.uint32) == coef.view(np.uint32), f"step {step}"
+        for t, n in enumerate(sizes):
+            got = np.empty(n, np.float32)
+            assert H.gmh_mixed_read_master(opt, t, got.ctypes.data, n) == 0, HL.err(H)
+            assert np.array_equal(got.view(np.uint32), master[t].view(np.uint32)), f"master_{t}"
+    finally:
+        H.gmh_optimizer_destroy(opt)
+        for p in wp + gp:
+            L.deallocate_cuda_buffer(p)
+        H.gmh_mm_destroy(mm)
+        H.gmh_device_destroy(dev)
