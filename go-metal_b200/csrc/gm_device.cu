@@ -597,7 +597,7 @@ int gm_device_set_tuning(uintptr_t h, const char* name, long long value) {
     else if (n == "mixed_fastdiv") d->mixed_fastdiv = value ? 1 : 0;
     else if (n == "mixed_pf") d->mixed_pf = value ? 1 : 0;
     else if (n == "mixed_variant") d->mixed_variant = value ? 1 : 0;
-    else if (n == "lbfgs_coop") d->lbfgs_coop = value ? 1 : 0;
+    else if (n == "lbfgs_coop") { if (value < 0 || value > 2) { set_error("lbfgs_coop is 0, 1 or 2"); return GM_ERR_BAD_ARG; } d->lbfgs_coop = (int)value; }
     else if (n == "barrier_budget_cycles") { if (value <= 0) { set_error("the budget must be positive"); return GM_ERR_BAD_ARG; } d->barrier_budget_cycles = value; }
     else { set_error("unknown tuning name '%s'", name); return GM_ERR_BAD_ARG; }
     return GM_OK;

@@ -90,7 +90,8 @@ struct Device {
     int lbfgs_waves = 1;                // resident-CTA waves of the pipelined L-BFGS pass (GOMETAL_LBFGS_WAVES)
     int grid_waves = 0;                 // 0: one CTA per chunk; >0: waves of resident CTAs (GOMETAL_GRID_WAVES)
     int chunk_elems = 0;                // 0: default tile; else elements per chunk (GOMETAL_CHUNK_ELEMS)
-    int lbfgs_coop = 0;                 // L-BFGS step as one cooperative launch with the direction kept on chip (GOMETAL_LBFGS_COOP)
+    int lbfgs_coop = 0;                 // L-BFGS step as one cooperative launch: 2 = direction left in L2, 1 = direction kept on
+                                        // chip, 0 = one launch per pass (GOMETAL_LBFGS_COOP)
     unsigned lbfgs_epoch = 0;           // barrier epochs handed to the single-launch L-BFGS step so far
     int lbfgs_mode = 3;                 // bit 0: corrected curvature pair, bit 1: descent direction
     // scratch for reductions (dot partials, tickets); grown on demand

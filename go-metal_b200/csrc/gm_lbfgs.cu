@@ -254,12 +254,108 @@ struct AxpyRef {
     bool fast;               // a whole chunk, 16-byte aligned in every column
 };
 
+// The chunk walk shared by the multi-launch pass kernel and the single-launch step: kinds 0, 1
+// and 2 over chunks first, first + stride, ...; the loads of the next chunk are issued before the
+// current chunk's sum is reduced; chunk sums land in partials[chunk].
+__device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int kind, const int descent, const bool has_vec,
+                                              const bool want_dot, const bool writes, const int col_axpy, const int col_dot,
+                                              const float coef, const unsigned long long pol, float* __restrict__ partials,
+                                              float* warp_sum, const int first, const int stride) {
+    constexpr int PASSES = kDotChunk / (kDotThreads * 4);
+    const int tid = threadIdx.x;
+    const int T = tb.T;
+    auto lookup = [&](int c) -> AxpyRef {
+        AxpyRef r;
+        const int t = find_tensor(tb.chunk_prefix, T, c);
+        r.n = __ldg(tb.numel + t);
+        r.base = (long long)(c - __ldg(tb.chunk_prefix + t)) * kDotChunk;
+        r.fast = __ldg(tb.aligned + t) != 0 && r.base + kDotChunk <= r.n;
+        auto col = [&](int cidx) -> float* { return reinterpret_cast<float*>(__ldg(tb.ptrs + (size_t)cidx * T + t)); };
+        r.dir = col(COL_DIR);
+        r.src = kind == 0 ? col(COL_G) : r.dir;
+        r.vec = has_vec ? col(col_axpy) : nullptr;
+        r.dv = want_dot ? col(col_dot) : nullptr;
+        return r;
+    };
+    auto new_dir = [&](float d_old, float v) -> float {
+        return kind == 1 ? sub(d_old, mul(coef, v)) : add(d_old, mul(coef, v));
+    };
+
+    if (writes || want_dot) {
+        float4 d4[PASSES], v4[PASSES], o4[PASSES];
+        auto issue = [&](const AxpyRef& r) {
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+                const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
+                // g and the history columns are read once per pass: streamed, so that dir stays in L2
+                if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
+                else d4[i] = ld_l2(r.src + e0, pol);
+                if (has_vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
+                if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
+            }
+        };
+
+        int c = first;
+        AxpyRef cur{};
+        if (c < tb.num_chunks) {
+            cur = lookup(c);
+            if (cur.fast) issue(cur);
+        }
+        while (c < tb.num_chunks) {
+            const int cn = c + stride;
+            AxpyRef nxt{};
+            if (cn < tb.num_chunks) nxt = lookup(cn);          // resolves while this chunk's loads arrive
+            float acc = 0.0f;
+            if (cur.fast) {
+#pragma unroll
+                for (int i = 0; i < PASSES; ++i) {
+                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                    if (kind == 0) {
+                        if (!descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
+                    } else if (has_vec) {
+                        d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
+                                            new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
+                    }
+                    if (writes) st_l2(cur.dir + e0, d4[i], pol);
+                    if (want_dot) {
+                        acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
+                        acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
+                    }
+                }
+            } else {
+                // ragged end of a tensor, or columns off a 16-byte boundary: element by
+                // element, lane t still owning elements (i*256+t)*4+k in that order
+                for (int i = 0; i < PASSES; ++i) {
+                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                    for (int k = 0; k < 4; ++k) {
+                        const long long e = e0 + k;
+                        if (e < cur.n) {
+                            float dn;
+                            if (kind == 0) dn = descent ? cur.src[e] : -cur.src[e];
+                            else dn = has_vec ? new_dir(cur.dir[e], cur.vec[e]) : cur.dir[e];
+                            if (writes) cur.dir[e] = dn;
+                            if (want_dot) acc = add(acc, mul(cur.dv[e], dn));
+                        }
+                    }
+                }
+            }
+            if (cn < tb.num_chunks && nxt.fast) issue(nxt);     // in flight during the reduction below
+            if (want_dot) {
+                const float total = cta_reduce_256(acc, warp_sum);
+                if (tid == 0) partials[c] = total;
+            }
+            c = cn;
+            cur = nxt;
+        }
+    }
+}
+
+
 __global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
 lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
                       unsigned int* __restrict__ ticket) {
     __shared__ float warp_sum[kDotThreads / 32];
     __shared__ int is_last;
-    constexpr int PASSES = kDotChunk / (kDotThreads * 4);
     const int tid = threadIdx.x;
     const int T = tb.T;
     const int kind = op.kind;
@@ -288,90 +384,8 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
     const bool writes = kind == 0 || !skip_axpy;
     const unsigned long long pol = l2_policy(op.keep_dir != 0);
 
-    auto lookup = [&](int c) -> AxpyRef {
-        AxpyRef r;
-        const int t = find_tensor(tb.chunk_prefix, T, c);
-        r.n = __ldg(tb.numel + t);
-        r.base = (long long)(c - __ldg(tb.chunk_prefix + t)) * kDotChunk;
-        r.fast = __ldg(tb.aligned + t) != 0 && r.base + kDotChunk <= r.n;
-        auto col = [&](int cidx) -> float* { return reinterpret_cast<float*>(__ldg(tb.ptrs + (size_t)cidx * T + t)); };
-        r.dir = col(COL_DIR);
-        r.src = kind == 0 ? col(COL_G) : r.dir;
-        r.vec = has_vec ? col(op.col_axpy) : nullptr;
-        r.dv = want_dot ? col(op.col_dot) : nullptr;
-        return r;
-    };
-    auto new_dir = [&](float d_old, float v) -> float {
-        return kind == 1 ? sub(d_old, mul(coef, v)) : add(d_old, mul(coef, v));
-    };
-
-    if (writes || want_dot) {
-        float4 d4[PASSES], v4[PASSES], o4[PASSES];
-        auto issue = [&](const AxpyRef& r) {
-#pragma unroll
-            for (int i = 0; i < PASSES; ++i) {
-                const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
-                // g and the history columns are read once per pass: streamed, so that dir stays in L2
-                if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
-                else d4[i] = ld_l2(r.src + e0, pol);
-                if (has_vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
-                if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
-            }
-        };
-
-        int c = blockIdx.x;
-        AxpyRef cur{};
-        if (c < tb.num_chunks) {
-            cur = lookup(c);
-            if (cur.fast) issue(cur);
-        }
-        while (c < tb.num_chunks) {
-            const int cn = c + gridDim.x;
-            AxpyRef nxt{};
-            if (cn < tb.num_chunks) nxt = lookup(cn);          // resolves while this chunk's loads arrive
-            float acc = 0.0f;
-            if (cur.fast) {
-#pragma unroll
-                for (int i = 0; i < PASSES; ++i) {
-                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
-                    if (kind == 0) {
-                        if (!op.descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
-                    } else if (has_vec) {
-                        d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
-                                            new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
-                    }
-                    if (writes) st_l2(cur.dir + e0, d4[i], pol);
-                    if (want_dot) {
-                        acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
-                        acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
-                    }
-                }
-            } else {
-                // ragged end of a tensor, or columns off a 16-byte boundary: element by
-                // element, lane t still owning elements (i*256+t)*4+k in that order
-                for (int i = 0; i < PASSES; ++i) {
-                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
-                    for (int k = 0; k < 4; ++k) {
-                        const long long e = e0 + k;
-                        if (e < cur.n) {
-                            float dn;
-                            if (kind == 0) dn = op.descent ? cur.src[e] : -cur.src[e];
-                            else dn = has_vec ? new_dir(cur.dir[e], cur.vec[e]) : cur.dir[e];
-                            if (writes) cur.dir[e] = dn;
-                            if (want_dot) acc = add(acc, mul(cur.dv[e], dn));
-                        }
-                    }
-                }
-            }
-            if (cn < tb.num_chunks && nxt.fast) issue(nxt);     // in flight during the reduction below
-            if (want_dot) {
-                const float total = cta_reduce_256(acc, warp_sum);
-                if (tid == 0) partials[c] = total;
-            }
-            c = cn;
-            cur = nxt;
-        }
-    }
+    axpy_dot_walk(tb, kind, op.descent, has_vec, want_dot, writes, op.col_axpy, op.col_dot, coef, pol, partials, warp_sum,
+                  blockIdx.x, gridDim.x);
     if (!op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
     finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
 }
@@ -514,6 +528,25 @@ static int coop_grid(Device* d, int num_chunks, int m) {
     return grid;
 }
 
+// Grid of the single-launch step that leaves the direction in L2: the resident CTAs, trimmed so
+// that every CTA walks the same number of chunks; 0 when it cannot serve this problem.
+static int fused_grid(Device* d, int num_chunks, int m) {
+    if (m > kCoopMaxHistory) return 0;
+    static thread_local int per_sm = 0;          // -1 unavailable
+    if (per_sm == 0) {
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, d->ordinal);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)lbfgs_fused_kernel, kDotThreads, 0);
+        if (e != cudaSuccess) cudaGetLastError();
+        if (!coop || e != cudaSuccess || per_sm < 1) per_sm = -1;
+    }
+    if (per_sm < 0) return 0;
+    const long long resident = (long long)per_sm * d->sm_count;
+    if (num_chunks <= resident) return num_chunks;
+    const long long rounds = (num_chunks + resident - 1) / resident;
+    return (int)((num_chunks + rounds - 1) / rounds);
+}
+
 static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in, const bool overlap = true) {
     LbfgsOp op = op_in;
     // Every pass after the first of a step is launched so that it may start while its
@@ -585,7 +618,8 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
     auto col_y = [&](int idx) { return COL_HIST + m + idx; };
 
     if (d->lbfgs_coop) {
-        const int grid = coop_grid(d, c->tb.num_chunks, m);
+        const bool on_chip = d->lbfgs_coop == 1;
+        const int grid = on_chip ? coop_grid(d, c->tb.num_chunks, m) : fused_grid(d, c->tb.num_chunks, m);
         if (grid > 0) {
             CoopPlan plan{};
             int np = 0;
@@ -627,9 +661,15 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
             LbfgsTable tbv = c->tb;
             float* partials = d->partials;
             unsigned int* ctl = d->ticket;
-            void* args[] = {&tbv, &plan, &partials, &ctl};
-            GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_coop_kernel, dim3(grid), dim3(kCoopThreads), args,
-                                                      kCoopSmemBytes, d->stream));
+            int keep_dir = d->lbfgs_keep_dir;
+            void* args[] = {&tbv, &plan, &partials, &ctl, &keep_dir};
+            if (on_chip) {
+                GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_coop_kernel, dim3(grid), dim3(kCoopThreads), args,
+                                                          kCoopSmemBytes, d->stream));
+            } else {
+                GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_fused_kernel, dim3(grid), dim3(kDotThreads), args, 0,
+                                                          d->stream));
+            }
             d->launches++;
             if (step_size) *step_size = initial_step;
             GM_CUDA_CHECK(cudaStreamSynchronize(d->stream));

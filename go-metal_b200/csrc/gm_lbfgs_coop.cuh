@@ -407,4 +407,121 @@ lbfgs_coop_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__ 
     }
 }
 
+// ---- the step as one launch with the direction left in L2 ("lbfgs_coop" = 2) ----
+// The same passes as the multi-launch step, by the same chunk walk (axpy_dot_walk) with the
+// direction read and written through L2 under the evict_last policy, but inside ONE
+// cooperative launch: between two passes stands a bounded grid-wide barrier instead of a
+// kernel boundary, and every CTA adds the chunk sums up itself.  A CTA walks the same
+// chunks in every pass, so it only ever reads direction values it wrote itself.  The idea:
+// trade the fixed cost of a pass (launch, table warm-up, last-CTA finisher, drain -- about
+// 7 us of the 23 us a pass takes at n = 10^7) for a barrier.  MEASURED: 0.561 ms per step
+// against 0.507-0.519 ms for the multi-launch step on the same box -- the barrier, the
+// 2,442 chunk sums every CTA re-reads and the 128 registers the walk needs inside the pass
+// loop (two CTAs per SM instead of three; at 80 registers it spills in its inner loop and
+// takes 0.775 ms) cost more than the launches they replace, which programmatic stream
+// serialization already overlaps.  Not the default.
+#ifndef GM_LBFGS_FUSED_MINB
+#define GM_LBFGS_FUSED_MINB 2      // 128 registers: at 3 CTAs per SM (80 registers) the walk spills inside its loop
+#endif
+__global__ void __launch_bounds__(kDotThreads, GM_LBFGS_FUSED_MINB)
+lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__ partials, unsigned int* __restrict__ ctl,
+                   const int keep_dir) {
+    __shared__ float warp_sum[kDotThreads / 32];
+    __shared__ float s_alpha[kCoopMaxHistory];
+    __shared__ float s_coef;
+    __shared__ float s_dot;
+    __shared__ int s_ok;
+    const int tid = threadIdx.x;
+    const int G = gridDim.x;
+    const unsigned long long pol = l2_policy(keep_dir != 0);
+    if (tid < kCoopMaxHistory) s_alpha[tid] = 0.0f;
+    if (tid == 0) s_coef = 0.0f;
+    __syncthreads();
+
+    unsigned barrier_no = 0;
+    for (int pi = 0; pi < plan.num_passes; ++pi) {
+        const CoopPass& ps = plan.pass[pi];
+        const bool final_pass = ps.kind == 3;
+        bool skip_axpy = false, want_dot = false, has_vec = false;
+        float coef = 0.0f, rho_dot = 0.0f;
+        if (!final_pass) {
+            skip_axpy = ps.kind != 0 && rho_skips(plan.rho[ps.rho_axpy]);
+            want_dot = ps.col_dot >= 0 && !(ps.rho_dot >= 0 && rho_skips(plan.rho[ps.rho_dot]));
+            has_vec = ps.kind != 0 && !skip_axpy;
+            if (ps.kind != 0) coef = ps.coef_alpha >= 0 ? s_alpha[ps.coef_alpha] : s_coef;
+            if (ps.rho_dot >= 0) rho_dot = *plan.rho[ps.rho_dot];
+        } else {
+            want_dot = plan.have_pair != 0;
+        }
+        float* psum = partials + ((barrier_no + 1) & 1u) * (size_t)tb.num_chunks;
+        if (!final_pass) {
+            const bool writes = ps.kind == 0 || !skip_axpy;
+            axpy_dot_walk(tb, ps.kind, plan.descent, has_vec, want_dot, writes, ps.col_axpy, ps.col_dot, coef, pol, psum, warp_sum,
+                          blockIdx.x, G);
+        } else {
+            for (int c = blockIdx.x; c < tb.num_chunks; c += G) {
+                const CoopChunk ck = coop_locate(tb, c);
+                const float* dirg = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)COL_DIR * tb.T + ck.t));
+                float4 d[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const long long e0 = ck.base + ((long long)i * kDotThreads + tid) * 4;
+                    if (ck.fast) {
+                        d[i] = ld_l2(dirg + e0, pol);
+                    } else {
+                        d[i] = make_float4(e0 < ck.n ? dirg[e0] : 0.f, e0 + 1 < ck.n ? dirg[e0 + 1] : 0.f,
+                                           e0 + 2 < ck.n ? dirg[e0 + 2] : 0.f, e0 + 3 < ck.n ? dirg[e0 + 3] : 0.f);
+                    }
+                }
+                const float acc = coop_final_chunk(tb, ck, plan, tid, d);
+                if (want_dot) {
+                    const float total = cta_reduce_256(acc, warp_sum);
+                    if (tid == 0) psum[c] = total;
+                }
+            }
+        }
+        if (ps.epilogue == 0) continue;
+
+        float dot = 0.0f;
+        if (want_dot) {
+            barrier_no += 1;
+            __syncthreads();
+            if (tid == 0) {
+                int ok = 1;
+                __threadfence();
+                const unsigned arrived = atomicAdd(ctl + kLbArrive, 1u);
+                if (arrived == (unsigned)G - 1u) {
+                    ctl[kLbArrive] = 0u;
+                    __threadfence();
+                    st_release(ctl + kLbGo, plan.epoch_base + barrier_no);
+                } else if (!bounded_wait_for(ctl + kLbGo, plan.epoch_base + barrier_no, plan.barrier_budget)) {
+                    atomicExch(ctl + kLbError, 1u);
+                    ok = 0;
+                }
+                s_ok = ok;
+            }
+            __syncthreads();
+            if (!s_ok) return;
+            float acc = 0.0f;
+            for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, __ldcg(psum + c));
+            const float total = cta_reduce_256(acc, warp_sum);
+            if (tid == 0) s_dot = total;
+            __syncthreads();
+            dot = s_dot;
+        }
+        if (tid == 0) {
+            float r = 0.0f;
+            switch (ps.epilogue) {
+                case 1: r = want_dot ? mul(dot, rho_dot) : 0.0f; break;
+                case 2: r = want_dot ? sub(s_alpha[ps.alpha_in], mul(dot, rho_dot)) : 0.0f; break;
+                default: r = (plan.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
+            }
+            if (ps.epilogue == 1) { s_alpha[ps.out_alpha] = r; if (blockIdx.x == 0) plan.alpha[ps.out_alpha] = r; }
+            else if (ps.epilogue == 2) s_coef = r;
+            else if (blockIdx.x == 0) *plan.rho_prev = r;
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace gm

@@ -1,5 +1,6 @@
-"""The L-BFGS step as one cooperative launch with the direction vector kept on chip
-("lbfgs_coop"): the parity cases of test_lbfgs_gpu.py run again through it.  It must give
+"""The L-BFGS step as one cooperative launch ("lbfgs_coop": 1 keeps the direction vector on
+chip, 2 leaves it in L2 and only replaces the kernel boundaries between passes by grid
+barriers): the parity cases of test_lbfgs_gpu.py run again through both.  It must give
 the bits of the oracle, like the multi-launch step, in every mode, for ragged and
 unaligned tensors, and at the 10^7-variable size it was built for; a problem too large
 for the on-chip storage silently takes the multi-launch step.
@@ -12,11 +13,11 @@ import test_lbfgs_gpu as TL
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture()
-def coop(gm, dev):
+@pytest.fixture(params=[1, 2], ids=["direction_on_chip", "direction_in_l2"])
+def coop(request, gm, dev):
     L = gm.lib
     before = L.gm_device_get_tuning(dev.h, b"lbfgs_coop")
-    gm.check(L.gm_device_set_tuning(dev.h, b"lbfgs_coop", 1), "single-launch step on")
+    gm.check(L.gm_device_set_tuning(dev.h, b"lbfgs_coop", request.param), "single-launch step on")
     launches = L.gm_device_launch_count(dev.h)
     yield lambda: L.gm_device_launch_count(dev.h) - launches
     gm.check(L.gm_device_set_tuning(dev.h, b"lbfgs_coop", before), "restore")
@@ -65,7 +66,9 @@ def test_10m_variables_history_10(gm, dev, oracle, coop):
         oracle.set_threads(1)
 
 
-def test_too_large_for_the_chip_takes_the_multi_launch_step(gm, dev, oracle, coop):
+def test_too_large_for_the_chip_takes_the_multi_launch_step(gm, dev, oracle, coop, request):
+    if "direction_in_l2" in request.node.name:
+        pytest.skip("the L2 form has no size limit")
     n = 17 * gm.lib.gm_device_sm_count(dev.h) * 4096 + 4096
     oracle.set_threads(oracle.all_cores())
     try:
