@@ -70,6 +70,7 @@ struct LbfgsOp {
     int descent;              // kind 0: dir = +g instead of -g
     int keep_dir;             // kinds 0..2: the direction's lines get the evict_last L2 policy
     int early_trigger;        // kinds 0..2: dependents may launch from the start of this grid (else from its end)
+    int prewait;              // kinds 1,2: history loads issued before the wait for the previous pass (0 none, 1 first chunk, 2 + L2 prefetch of the second)
     float step;
 };
 
@@ -254,16 +255,32 @@ struct AxpyRef {
     bool fast;               // a whole chunk, 16-byte aligned in every column
 };
 
+// What a pass knows only once its predecessor has finished: the coefficient, which of its two
+// halves the curvature test leaves standing, and the L2 policy of the direction's lines.
+struct WalkArgs {
+    float coef;
+    bool has_vec, want_dot, writes;
+    unsigned long long pol;
+};
+
 // The chunk walk shared by the multi-launch pass kernel and the single-launch step: kinds 0, 1
 // and 2 over chunks first, first + stride, ...; the loads of the next chunk are issued before the
 // current chunk's sum is reduced; chunk sums land in partials[chunk].
-__device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int kind, const int descent, const bool has_vec,
-                                              const bool want_dot, const bool writes, const int col_axpy, const int col_dot,
-                                              const float coef, const unsigned long long pol, float* __restrict__ partials,
-                                              float* warp_sum, const int first, const int stride) {
+//
+// The history columns are read-only for the whole step, so the walk loads its first chunk of
+// them (prewait >= 1) and asks L2 for its second (prewait >= 2) BEFORE it calls gate(), which
+// in the multi-launch step is where the grid waits for its predecessor: while that grid's last
+// CTA adds up the chunk sums, DRAM already works for this one.  Only the direction, the
+// coefficient and the curvature test wait for the gate.
+template <class Gate>
+__device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int kind, const int descent, const int col_axpy,
+                                              const int col_dot, const int prewait, float* __restrict__ partials,
+                                              float* warp_sum, const int first, const int stride, Gate gate) {
     constexpr int PASSES = kDotChunk / (kDotThreads * 4);
     const int tid = threadIdx.x;
     const int T = tb.T;
+    const bool may_vec = kind != 0 && col_axpy >= 0;
+    const bool may_dot = col_dot >= 0;
     auto lookup = [&](int c) -> AxpyRef {
         AxpyRef r;
         const int t = find_tensor(tb.chunk_prefix, T, c);
@@ -273,80 +290,103 @@ __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int ki
         auto col = [&](int cidx) -> float* { return reinterpret_cast<float*>(__ldg(tb.ptrs + (size_t)cidx * T + t)); };
         r.dir = col(COL_DIR);
         r.src = kind == 0 ? col(COL_G) : r.dir;
-        r.vec = has_vec ? col(col_axpy) : nullptr;
-        r.dv = want_dot ? col(col_dot) : nullptr;
+        r.vec = may_vec ? col(col_axpy) : nullptr;
+        r.dv = may_dot ? col(col_dot) : nullptr;
         return r;
     };
-    auto new_dir = [&](float d_old, float v) -> float {
-        return kind == 1 ? sub(d_old, mul(coef, v)) : add(d_old, mul(coef, v));
+
+    float4 d4[PASSES], v4[PASSES], o4[PASSES];
+    // g and the history columns are read once per pass: streamed, so that dir stays in L2
+    auto issue_hist = [&](const AxpyRef& r, const bool vec, const bool dot) {
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
+            if (vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
+            if (dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
+        }
+    };
+    auto issue_dir = [&](const AxpyRef& r, const unsigned long long pol) {
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
+            if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
+            else d4[i] = ld_l2(r.src + e0, pol);
+        }
     };
 
-    if (writes || want_dot) {
-        float4 d4[PASSES], v4[PASSES], o4[PASSES];
-        auto issue = [&](const AxpyRef& r) {
+    int c = first;
+    AxpyRef cur{}, nxt{};
+    const bool any = c < tb.num_chunks;
+    const bool early = prewait >= 1 && any;
+    if (any) {
+        cur = lookup(c);
+        if (early && cur.fast) issue_hist(cur, may_vec, may_dot);
+        if (c + stride < tb.num_chunks) {
+            nxt = lookup(c + stride);
+            if (prewait >= 2 && nxt.fast) {
+                // one 64-byte piece of the chunk per thread and column
+                if (may_vec) asm volatile("prefetch.global.L2 [%0];" :: "l"(nxt.vec + nxt.base + tid * 16LL));
+                if (may_dot) asm volatile("prefetch.global.L2 [%0];" :: "l"(nxt.dv + nxt.base + tid * 16LL));
+            }
+        }
+    }
+
+    const WalkArgs a = gate();
+    if (!(a.writes || a.want_dot) || !any) return;
+    auto new_dir = [&](float d_old, float v) -> float {
+        return kind == 1 ? sub(d_old, mul(a.coef, v)) : add(d_old, mul(a.coef, v));
+    };
+    if (cur.fast) {
+        if (!early) issue_hist(cur, a.has_vec, a.want_dot);
+        issue_dir(cur, a.pol);
+    }
+    while (c < tb.num_chunks) {
+        const int cn = c + stride;
+        float acc = 0.0f;
+        if (cur.fast) {
 #pragma unroll
             for (int i = 0; i < PASSES; ++i) {
-                const long long e0 = r.base + ((long long)i * kDotThreads + tid) * 4;
-                // g and the history columns are read once per pass: streamed, so that dir stays in L2
-                if (kind == 0) d4[i] = __ldcs(reinterpret_cast<const float4*>(r.src + e0));
-                else d4[i] = ld_l2(r.src + e0, pol);
-                if (has_vec) v4[i] = __ldcs(reinterpret_cast<const float4*>(r.vec + e0));
-                if (want_dot) o4[i] = __ldcs(reinterpret_cast<const float4*>(r.dv + e0));
-            }
-        };
-
-        int c = first;
-        AxpyRef cur{};
-        if (c < tb.num_chunks) {
-            cur = lookup(c);
-            if (cur.fast) issue(cur);
-        }
-        while (c < tb.num_chunks) {
-            const int cn = c + stride;
-            AxpyRef nxt{};
-            if (cn < tb.num_chunks) nxt = lookup(cn);          // resolves while this chunk's loads arrive
-            float acc = 0.0f;
-            if (cur.fast) {
-#pragma unroll
-                for (int i = 0; i < PASSES; ++i) {
-                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
-                    if (kind == 0) {
-                        if (!descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
-                    } else if (has_vec) {
-                        d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
-                                            new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
-                    }
-                    if (writes) st_l2(cur.dir + e0, d4[i], pol);
-                    if (want_dot) {
-                        acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
-                        acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
-                    }
+                const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                if (kind == 0) {
+                    if (!descent) d4[i] = make_float4(-d4[i].x, -d4[i].y, -d4[i].z, -d4[i].w);
+                } else if (a.has_vec) {
+                    d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
+                                        new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
                 }
-            } else {
-                // ragged end of a tensor, or columns off a 16-byte boundary: element by
-                // element, lane t still owning elements (i*256+t)*4+k in that order
-                for (int i = 0; i < PASSES; ++i) {
-                    const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
-                    for (int k = 0; k < 4; ++k) {
-                        const long long e = e0 + k;
-                        if (e < cur.n) {
-                            float dn;
-                            if (kind == 0) dn = descent ? cur.src[e] : -cur.src[e];
-                            else dn = has_vec ? new_dir(cur.dir[e], cur.vec[e]) : cur.dir[e];
-                            if (writes) cur.dir[e] = dn;
-                            if (want_dot) acc = add(acc, mul(cur.dv[e], dn));
-                        }
+                if (a.writes) st_l2(cur.dir + e0, d4[i], a.pol);
+                if (a.want_dot) {
+                    acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
+                    acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
+                }
+            }
+        } else {
+            // ragged end of a tensor, or columns off a 16-byte boundary: element by
+            // element, lane t still owning elements (i*256+t)*4+k in that order
+            for (int i = 0; i < PASSES; ++i) {
+                const long long e0 = cur.base + ((long long)i * kDotThreads + tid) * 4;
+                for (int k = 0; k < 4; ++k) {
+                    const long long e = e0 + k;
+                    if (e < cur.n) {
+                        float dn;
+                        if (kind == 0) dn = descent ? cur.src[e] : -cur.src[e];
+                        else dn = a.has_vec ? new_dir(cur.dir[e], cur.vec[e]) : cur.dir[e];
+                        if (a.writes) cur.dir[e] = dn;
+                        if (a.want_dot) acc = add(acc, mul(cur.dv[e], dn));
                     }
                 }
             }
-            if (cn < tb.num_chunks && nxt.fast) issue(nxt);     // in flight during the reduction below
-            if (want_dot) {
-                const float total = cta_reduce_256(acc, warp_sum);
-                if (tid == 0) partials[c] = total;
-            }
-            c = cn;
-            cur = nxt;
         }
+        if (cn < tb.num_chunks && nxt.fast) {                   // in flight during the reduction below
+            issue_hist(nxt, a.has_vec, a.want_dot);
+            issue_dir(nxt, a.pol);
+        }
+        if (a.want_dot) {
+            const float total = cta_reduce_256(acc, warp_sum);
+            if (tid == 0) partials[c] = total;
+        }
+        c = cn;
+        cur = nxt;
+        if (c + stride < tb.num_chunks) nxt = lookup(c + stride);   // resolves while this chunk's loads arrive
     }
 }
 
@@ -356,36 +396,28 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
                       unsigned int* __restrict__ ticket) {
     __shared__ float warp_sum[kDotThreads / 32];
     __shared__ int is_last;
-    const int tid = threadIdx.x;
-    const int T = tb.T;
     const int kind = op.kind;
 
     // Launched with programmatic stream serialization (every pass of a step but the
     // first), this grid may become resident while the previous pass drains.  Only the
-    // pointer table, which no pass writes, is touched before the wait; the scalars,
-    // the direction and the chunk sums are the previous pass's to finish first.
+    // pointer table and the history columns, which no pass writes, are touched before
+    // the wait; the scalars, the direction and the chunk sums are the previous pass's
+    // to finish first.
     if (op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
-    if (blockIdx.x < tb.num_chunks) {
-        const int t0 = find_tensor(tb.chunk_prefix, T, blockIdx.x);
-        const float* warm = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)COL_DIR * T + t0));
-        if (op.col_dot >= 0) warm = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)op.col_dot * T + t0));
-        // the history column this pass dots with is read-only during the step: start pulling
-        // this CTA's first chunk of it towards L2
-        const long long e0 = (long long)(blockIdx.x - __ldg(tb.chunk_prefix + t0)) * kDotChunk + tid * 16LL;
-        if (op.col_dot >= 0 && __ldg(tb.aligned + t0) != 0 && e0 + 16 <= __ldg(tb.numel + t0))
-            asm volatile("prefetch.global.L2 [%0];" :: "l"(warm + e0));
-    }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    const bool skip_axpy = kind != 0 && rho_skips(op.rho_axpy);
-    const bool want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot);
-    const float coef = kind != 0 ? *op.coef : 0.0f;
-    const bool has_vec = kind != 0 && !skip_axpy;
-    const bool writes = kind == 0 || !skip_axpy;
-    const unsigned long long pol = l2_policy(op.keep_dir != 0);
-
-    axpy_dot_walk(tb, kind, op.descent, has_vec, want_dot, writes, op.col_axpy, op.col_dot, coef, pol, partials, warp_sum,
-                  blockIdx.x, gridDim.x);
+    bool want_dot = false;
+    auto gate = [&]() -> WalkArgs {
+        asm volatile("griddepcontrol.wait;" ::: "memory");          // no effect after an ordinary launch
+        const bool skip_axpy = kind != 0 && rho_skips(op.rho_axpy);
+        WalkArgs a;
+        a.want_dot = want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot);
+        a.coef = kind != 0 ? *op.coef : 0.0f;
+        a.has_vec = kind != 0 && !skip_axpy;
+        a.writes = kind == 0 || !skip_axpy;
+        a.pol = l2_policy(op.keep_dir != 0);
+        return a;
+    };
+    axpy_dot_walk(tb, kind, op.descent, op.col_axpy, op.col_dot, kind == 0 ? 0 : op.prewait, partials, warp_sum,
+                  blockIdx.x, gridDim.x, gate);
     if (!op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
     finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
 }
@@ -560,6 +592,7 @@ static void launch_pass(Device* d, const LbfgsCtx* c, const LbfgsOp& op_in, cons
     if (op.kind <= 2) {
         op.keep_dir = d->lbfgs_keep_dir;
         op.early_trigger = d->lbfgs_overlap == 1;
+        op.prewait = d->lbfgs_prewait;
         cfg.gridDim = dim3(axpy_grid(d, c->tb.num_chunks));
         cudaLaunchKernelEx(&cfg, lbfgs_axpy_dot_kernel, c->tb, op, d->partials, d->ticket);
     } else {

@@ -428,6 +428,8 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
             // offset (the fp16 streams then force a multiple of 8 elements), which is the usual
             // packing.  A tensor whose streams sit at different offsets can miss it and takes the
             // 4-element path below.
+            int rot = 0;                                   // PUSH: the peer this thread's next pass addresses first
+            if (PUSH && peers.count > 1) rot = ((tid >> 5) + c) % peers.count;
             const bool wide_ok = WIDE && (((reinterpret_cast<uintptr_t>(w + b) | reinterpret_cast<uintptr_t>(m + b) |
                                             reinterpret_cast<uintptr_t>(v + b)) & 31) == 0);
             if (wide_ok) {
@@ -469,8 +471,14 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                     st256(w + b + 8LL * i, W); st256(m + b + 8LL * i, M); st256(v + b + 8LL * i, V);
                     const uint4 packed = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     if (PUSH) {
-                        for (int r = 0; r < peers.count; ++r)
-                            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(oq8 + i) + peers.delta[r]) = packed;
+                        // the first peer rotates with the warp and the pass, so that the warps of an SM do
+                        // not all address the same peer at the same moment
+                        int idx = rot;
+                        for (int r = 0; r < peers.count; ++r) {
+                            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(oq8 + i) + peers.delta[idx]) = packed;
+                            idx = idx + 1 == peers.count ? 0 : idx + 1;
+                        }
+                        rot = rot + 1 == peers.count ? 0 : rot + 1;
                     }
                     __stcs(oq8 + i, packed);
                 }
@@ -502,8 +510,12 @@ mixed_update_kernel(const DevList L, gm_loss_scale_t* __restrict__ state, unsign
                 __stcs(wq + i, wc); __stcs(mq + i, mc); __stcs(vq + i, vc);
                 const uint2 packed = make_uint2((unsigned)h0 | ((unsigned)h1 << 16), (unsigned)h2 | ((unsigned)h3 << 16));
                 if (PUSH) {
-                    for (int r = 0; r < peers.count; ++r)
-                        *reinterpret_cast<uint2*>(reinterpret_cast<char*>(oq + i) + peers.delta[r]) = packed;
+                    int idx = rot;
+                    for (int r = 0; r < peers.count; ++r) {
+                        *reinterpret_cast<uint2*>(reinterpret_cast<char*>(oq + i) + peers.delta[idx]) = packed;
+                        idx = idx + 1 == peers.count ? 0 : idx + 1;
+                    }
+                    rot = rot + 1 == peers.count ? 0 : rot + 1;
                 }
                 __stcs(oq + i, packed);
                 gc = gn; wc = wn; mc = mn; vc = vn;

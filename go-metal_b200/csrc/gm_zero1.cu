@@ -96,6 +96,7 @@ struct Zero1 {
     PeerMap map[kArenaSlots];          // peer-mapped arenas for the push paths
     int* barrier_word = nullptr;       // device int used by the closing all-reduce
     bool push_prefetch = true;         // GOMETAL_PUSH_PREFETCH=0 selects the push kernel without the software prefetch
+    int push_variant = 2;              // GOMETAL_PUSH_VARIANT (2 measured best on 8 GPUs): how the remote stores of a pass leave (see zero1_adam_push_kernel)
     // copy-engine path: one stream per peer, one event per slice, one "done" event per peer
     cudaStream_t copy_stream[kMaxPeers] = {nullptr};
     cudaEvent_t copy_done[kMaxPeers] = {nullptr};
@@ -121,7 +122,16 @@ static Zero1* as_zero1(uintptr_t h) {
 // and the peer offsets stay in registers.  Like mta_apply_kernel, a thread issues
 // the loads of its next pass before the arithmetic and the stores of the current
 // one, so the remote stores leave while loads are in flight.
-template <int NP>
+//
+// VAR picks how the NP remote stores of a pass leave: 0 = plain stores, peers in the order
+// rank+1, rank+2, ...; 1 = the same with the evict-first (.cs) qualifier; 2 = plain stores
+// whose first peer rotates with the warp and the pass, so that the warps of an SM do not all
+// address the same peer at the same moment.
+__device__ __forceinline__ void st_remote_cs(float4* a, const float4 v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" :: "l"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+template <int NP, int VAR>
 __global__ void __launch_bounds__(kApplyThreads, 4)
 zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst peers) {
     constexpr int NS = 4;
@@ -182,9 +192,20 @@ zero1_adam_push_kernel(const DevList L, const AdamRule::P prm, const PeerDst pee
             for (int s = 0; s < NS; ++s) { x0[s] = cur[s].x; x1[s] = cur[s].y; x2[s] = cur[s].z; x3[s] = cur[s].w; }
             AdamRule::elem(x0, prm); AdamRule::elem(x1, prm); AdamRule::elem(x2, prm); AdamRule::elem(x3, prm);
             const float4 wn = make_float4(x0[0], x1[0], x2[0], x3[0]);
+            if (VAR == 2) {
+                int idx = ((i >> 5) + (i / NT)) % NP;
 #pragma unroll
-            for (int r = 0; r < NP; ++r)
-                *reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[r]) = wn;
+                for (int r = 0; r < NP; ++r) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[idx]) = wn;
+                    idx = idx + 1 == NP ? 0 : idx + 1;
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < NP; ++r) {
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<char*>(q[0] + i) + peers.delta[r]);
+                    if (VAR == 1) st_remote_cs(dst, wn); else *dst = wn;
+                }
+            }
             *(q[0] + i) = wn;                                            // local copy stays cacheable
             st_stream(q[2] + i, make_float4(x0[2], x1[2], x2[2], x3[2]));
             st_stream(q[3] + i, make_float4(x0[3], x1[3], x2[3], x3[3]));
@@ -260,15 +281,25 @@ zero1_adam_push_plain_kernel(const DevList L, const AdamRule::P prm, const PeerD
 
 using PushFn = void (*)(const DevList, const AdamRule::P, const PeerDst);
 
-static PushFn push_kernel_for(int peers, bool prefetch) {
+template <int NP>
+static PushFn push_kernel_np(bool prefetch, int variant) {
+    if (!prefetch) return zero1_adam_push_plain_kernel<NP>;
+    switch (variant) {
+        case 1: return zero1_adam_push_kernel<NP, 1>;
+        case 2: return zero1_adam_push_kernel<NP, 2>;
+        default: return zero1_adam_push_kernel<NP, 0>;
+    }
+}
+
+static PushFn push_kernel_for(int peers, bool prefetch, int variant) {
     switch (peers) {
-        case 0: case 1: return prefetch ? zero1_adam_push_kernel<1> : zero1_adam_push_plain_kernel<1>;
-        case 2: return prefetch ? zero1_adam_push_kernel<2> : zero1_adam_push_plain_kernel<2>;
-        case 3: return prefetch ? zero1_adam_push_kernel<3> : zero1_adam_push_plain_kernel<3>;
-        case 4: return prefetch ? zero1_adam_push_kernel<4> : zero1_adam_push_plain_kernel<4>;
-        case 5: return prefetch ? zero1_adam_push_kernel<5> : zero1_adam_push_plain_kernel<5>;
-        case 6: return prefetch ? zero1_adam_push_kernel<6> : zero1_adam_push_plain_kernel<6>;
-        default: return prefetch ? zero1_adam_push_kernel<7> : zero1_adam_push_plain_kernel<7>;
+        case 0: case 1: return push_kernel_np<1>(prefetch, variant);
+        case 2: return push_kernel_np<2>(prefetch, variant);
+        case 3: return push_kernel_np<3>(prefetch, variant);
+        case 4: return push_kernel_np<4>(prefetch, variant);
+        case 5: return push_kernel_np<5>(prefetch, variant);
+        case 6: return push_kernel_np<6>(prefetch, variant);
+        default: return push_kernel_np<7>(prefetch, variant);
     }
 }
 
@@ -295,6 +326,7 @@ uintptr_t gm_zero1_create(uintptr_t device_ptr, const void* unique_id, int rank,
     Zero1* z = new Zero1();
     z->dev = d; z->rank = rank; z->world = world;
     if (const char* e = getenv("GOMETAL_PUSH_PREFETCH")) z->push_prefetch = atoi(e) != 0;
+    if (const char* e = getenv("GOMETAL_PUSH_VARIANT")) z->push_variant = atoi(e);
     DeviceGuard g(d);
     if (cudaMalloc((void**)&z->barrier_word, 256) != cudaSuccess) { cuda_fail(cudaGetLastError(), "cudaMalloc"); delete z; return 0; }
     cudaMemset(z->barrier_word, 0, 256);
@@ -496,7 +528,7 @@ static int push_launch(Zero1* z, const TensorList* l, const gm_hyper_t& hyper, W
     if (rc != GM_OK) return rc;
     if (dl.num_chunks == 0) return GM_OK;
     DeviceGuard g(d);
-    const PushFn kernel = push_kernel_for(peers.count, z->push_prefetch);
+    const PushFn kernel = push_kernel_for(peers.count, z->push_prefetch, z->push_variant);
     const int grid = launch_grid(d, (const void*)kernel, kApplyThreads, dl.num_chunks);
     kernel<<<grid, kApplyThreads, 0, d->stream>>>(dl, p, peers);
     d->launches++;
