@@ -158,6 +158,7 @@ static Device* make_device(int ordinal) {
     if (const char* e4 = getenv("GOMETAL_LBFGS_KEEP_DIR")) d->lbfgs_keep_dir = atoi(e4);
     if (const char* e9 = getenv("GOMETAL_LBFGS_OVERLAP")) d->lbfgs_overlap = atoi(e9);
     if (const char* e = getenv("GOMETAL_LBFGS_PREWAIT")) d->lbfgs_prewait = atoi(e);
+    if (const char* e = getenv("GOMETAL_LBFGS_DEFER")) d->lbfgs_defer = atoi(e) != 0;
     if (const char* e5 = getenv("GOMETAL_MIXED_KEEP_G")) d->mixed_keep_g = atoi(e5);
     if (const char* e6 = getenv("GOMETAL_MIXED_OVERLAP")) d->mixed_overlap = atoi(e6);
     if (const char* e8 = getenv("GOMETAL_MIXED_VARIANT")) d->mixed_variant = atoi(e8);
@@ -598,6 +599,7 @@ int gm_device_set_tuning(uintptr_t h, const char* name, long long value) {
     else if (n == "mixed_fastdiv") d->mixed_fastdiv = value ? 1 : 0;
     else if (n == "mixed_pf") d->mixed_pf = value ? 1 : 0;
     else if (n == "mixed_variant") d->mixed_variant = value ? 1 : 0;
+    else if (n == "lbfgs_defer") d->lbfgs_defer = value != 0;
     else if (n == "lbfgs_prewait") { if (value < 0 || value > 2) { set_error("lbfgs_prewait is 0, 1 or 2"); return GM_ERR_BAD_ARG; } d->lbfgs_prewait = (int)value; }
     else if (n == "lbfgs_coop") { if (value < 0 || value > 2) { set_error("lbfgs_coop is 0, 1 or 2"); return GM_ERR_BAD_ARG; } d->lbfgs_coop = (int)value; }
     else if (n == "barrier_budget_cycles") { if (value <= 0) { set_error("the budget must be positive"); return GM_ERR_BAD_ARG; } d->barrier_budget_cycles = value; }
@@ -615,6 +617,7 @@ long long gm_device_get_tuning(uintptr_t h, const char* name) {
     if (n == "mixed_variant") return d->mixed_variant;
     if (n == "lbfgs_coop") return d->lbfgs_coop;
     if (n == "lbfgs_prewait") return d->lbfgs_prewait;
+    if (n == "lbfgs_defer") return d->lbfgs_defer;
     if (n == "barrier_budget_cycles") return d->barrier_budget_cycles;
     set_error("unknown tuning name '%s'", name);
     return -1;

@@ -89,6 +89,8 @@ struct Device {
     int lbfgs_keep_dir = 1;             // L-BFGS direction lines marked evict_last in L2 (GOMETAL_LBFGS_KEEP_DIR=0 turns it off)
     int lbfgs_prewait = 1;              // history loads an L-BFGS pass issues before it waits for the previous pass: 0 none, 1 its first
                                         // chunk, 2 also an L2 prefetch of its second (GOMETAL_LBFGS_PREWAIT)
+    int lbfgs_defer = 1;                // an L-BFGS pass whose scalar only the next pass reads leaves the final sum to that pass
+                                        // instead of a ticket and a finishing CTA (GOMETAL_LBFGS_DEFER=0 turns it off)
     int lbfgs_waves = 1;                // resident-CTA waves of the pipelined L-BFGS pass (GOMETAL_LBFGS_WAVES)
     int grid_waves = 0;                 // 0: one CTA per chunk; >0: waves of resident CTAs (GOMETAL_GRID_WAVES)
     int chunk_elems = 0;                // 0: default tile; else elements per chunk (GOMETAL_CHUNK_ELEMS)

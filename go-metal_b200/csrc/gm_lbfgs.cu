@@ -70,6 +70,16 @@ struct LbfgsOp {
     int descent;              // kind 0: dir = +g instead of -g
     int keep_dir;             // kinds 0..2: the direction's lines get the evict_last L2 policy
     int early_trigger;        // kinds 0..2: dependents may launch from the start of this grid (else from its end)
+    // The scalar a pass with epilogue 1 or 2 produces is only ever read by the pass launched right
+    // after it.  With `defer` set the producer stops after writing its chunk sums (no ticket, no
+    // finishing CTA) and the consumer, told by pro_epilogue, starts by adding them up itself, every
+    // CTA for itself in the fixed order, while its first direction loads are already in flight.
+    int defer;                // kinds 0..2: the epilogue is left to the next pass
+    int pro_epilogue;         // kinds 1,2: epilogue of the previous pass to perform first (0: read *coef instead)
+    const float* pro_rho_dot; // the previous pass's rho_dot
+    const float* pro_alpha_in;
+    float* pro_out;           // where CTA 0 stores the scalar for later passes and for the caller
+    int part_in, part_out;    // which half of the chunk-sum buffer is read by the prologue / written by this pass
     int prewait;              // kinds 1,2: history loads issued before the wait for the previous pass (0 none, 1 first chunk, 2 + L2 prefetch of the second)
     float step;
 };
@@ -255,12 +265,11 @@ struct AxpyRef {
     bool fast;               // a whole chunk, 16-byte aligned in every column
 };
 
-// What a pass knows only once its predecessor has finished: the coefficient, which of its two
-// halves the curvature test leaves standing, and the L2 policy of the direction's lines.
+// What a pass knows only once its predecessor has finished: the coefficient and which of its
+// two halves the curvature test leaves standing.
 struct WalkArgs {
     float coef;
     bool has_vec, want_dot, writes;
-    unsigned long long pol;
 };
 
 // The chunk walk shared by the multi-launch pass kernel and the single-launch step: kinds 0, 1
@@ -272,10 +281,11 @@ struct WalkArgs {
 // in the multi-launch step is where the grid waits for its predecessor: while that grid's last
 // CTA adds up the chunk sums, DRAM already works for this one.  Only the direction, the
 // coefficient and the curvature test wait for the gate.
-template <class Gate>
+template <class Sync, class Gate>
 __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int kind, const int descent, const int col_axpy,
-                                              const int col_dot, const int prewait, float* __restrict__ partials,
-                                              float* warp_sum, const int first, const int stride, Gate gate) {
+                                              const int col_dot, const int prewait, const unsigned long long pol,
+                                              float* __restrict__ partials, float* warp_sum, const int first,
+                                              const int stride, Sync sync, Gate gate) {
     constexpr int PASSES = kDotChunk / (kDotThreads * 4);
     const int tid = threadIdx.x;
     const int T = tb.T;
@@ -331,15 +341,16 @@ __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int ki
         }
     }
 
+    // sync(): the predecessor has finished.  The direction is loaded next, and gate() -- which may
+    // have to add up the predecessor's chunk sums to know the coefficient -- runs under those loads.
+    sync();
+    if (any && cur.fast) issue_dir(cur, pol);
     const WalkArgs a = gate();
     if (!(a.writes || a.want_dot) || !any) return;
     auto new_dir = [&](float d_old, float v) -> float {
         return kind == 1 ? sub(d_old, mul(a.coef, v)) : add(d_old, mul(a.coef, v));
     };
-    if (cur.fast) {
-        if (!early) issue_hist(cur, a.has_vec, a.want_dot);
-        issue_dir(cur, a.pol);
-    }
+    if (cur.fast && !early) issue_hist(cur, a.has_vec, a.want_dot);
     while (c < tb.num_chunks) {
         const int cn = c + stride;
         float acc = 0.0f;
@@ -353,7 +364,7 @@ __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int ki
                     d4[i] = make_float4(new_dir(d4[i].x, v4[i].x), new_dir(d4[i].y, v4[i].y),
                                         new_dir(d4[i].z, v4[i].z), new_dir(d4[i].w, v4[i].w));
                 }
-                if (a.writes) st_l2(cur.dir + e0, d4[i], a.pol);
+                if (a.writes) st_l2(cur.dir + e0, d4[i], pol);
                 if (a.want_dot) {
                     acc = add(acc, mul(o4[i].x, d4[i].x)); acc = add(acc, mul(o4[i].y, d4[i].y));
                     acc = add(acc, mul(o4[i].z, d4[i].z)); acc = add(acc, mul(o4[i].w, d4[i].w));
@@ -378,7 +389,7 @@ __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int ki
         }
         if (cn < tb.num_chunks && nxt.fast) {                   // in flight during the reduction below
             issue_hist(nxt, a.has_vec, a.want_dot);
-            issue_dir(nxt, a.pol);
+            issue_dir(nxt, pol);
         }
         if (a.want_dot) {
             const float total = cta_reduce_256(acc, warp_sum);
@@ -395,8 +406,12 @@ __global__ void __launch_bounds__(kDotThreads, GM_LBFGS_MINB)
 lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__ partials,
                       unsigned int* __restrict__ ticket) {
     __shared__ float warp_sum[kDotThreads / 32];
+    __shared__ float s_dot;
     __shared__ int is_last;
     const int kind = op.kind;
+    const int tid = threadIdx.x;
+    float* part_out = partials + (size_t)op.part_out * tb.num_chunks;
+    const float* part_in = partials + (size_t)op.part_in * tb.num_chunks;
 
     // Launched with programmatic stream serialization (every pass of a step but the
     // first), this grid may become resident while the previous pass drains.  Only the
@@ -405,21 +420,38 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
     // to finish first.
     if (op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
     bool want_dot = false;
+    auto sync = [&]() { asm volatile("griddepcontrol.wait;" ::: "memory"); };   // no effect after an ordinary launch
     auto gate = [&]() -> WalkArgs {
-        asm volatile("griddepcontrol.wait;" ::: "memory");          // no effect after an ordinary launch
         const bool skip_axpy = kind != 0 && rho_skips(op.rho_axpy);
         WalkArgs a;
         a.want_dot = want_dot = op.col_dot >= 0 && !rho_skips(op.rho_dot);
-        a.coef = kind != 0 ? *op.coef : 0.0f;
         a.has_vec = kind != 0 && !skip_axpy;
         a.writes = kind == 0 || !skip_axpy;
-        a.pol = l2_policy(op.keep_dir != 0);
+        if (op.pro_epilogue != 0) {
+            // the previous pass left its epilogue to this one: same order as finish_pass
+            const bool have = !rho_skips(op.pro_rho_dot);
+            float dot = 0.0f;
+            if (have) {
+                float acc = 0.0f;
+                for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, __ldcg(part_in + c));
+                const float total = cta_reduce_256(acc, warp_sum);
+                if (tid == 0) s_dot = total;
+                __syncthreads();
+                dot = s_dot;
+            }
+            float r = 0.0f;
+            if (have) r = op.pro_epilogue == 1 ? mul(dot, *op.pro_rho_dot) : sub(*op.pro_alpha_in, mul(dot, *op.pro_rho_dot));
+            if (blockIdx.x == 0 && tid == 0) *op.pro_out = r;
+            a.coef = r;
+        } else {
+            a.coef = kind != 0 ? *op.coef : 0.0f;
+        }
         return a;
     };
-    axpy_dot_walk(tb, kind, op.descent, op.col_axpy, op.col_dot, kind == 0 ? 0 : op.prewait, partials, warp_sum,
-                  blockIdx.x, gridDim.x, gate);
+    axpy_dot_walk(tb, kind, op.descent, op.col_axpy, op.col_dot, kind == 0 ? 0 : op.prewait, l2_policy(op.keep_dir != 0),
+                  part_out, warp_sum, blockIdx.x, gridDim.x, sync, gate);
     if (!op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
-    finish_pass(tb, op, want_dot, partials, ticket, warp_sum, &is_last);
+    if (!op.defer) finish_pass(tb, op, want_dot, part_out, ticket, warp_sum, &is_last);
 }
 
 }  // namespace gm
@@ -493,7 +525,7 @@ static int get_ctx(Device* d, int T, int m, uintptr_t* const* cols4, uintptr_t* 
     c->tb.T = T; c->tb.num_chunks = prefix[T]; c->tb.ncols = ncols;
     c->key = std::move(key);
     c->history = m;
-    int rc = ensure_partials(d, c->tb.num_chunks);
+    int rc = ensure_partials(d, 2LL * c->tb.num_chunks);          // two halves: consecutive passes alternate
     if (rc != GM_OK) { cudaFree(c->blob); delete c; return rc; }
     std::lock_guard<std::mutex> lk(g_lb_mu);
     auto& v = g_lb[d];
@@ -717,6 +749,25 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
         }
     }
 
+    rc = ensure_partials(d, 2LL * c->tb.num_chunks);
+    if (rc != GM_OK) return rc;
+    // Consecutive loop passes write their chunk sums to alternating halves of the buffer.  A pass whose
+    // scalar only the next pass reads leaves its epilogue to that pass ("lbfgs_defer").
+    LbfgsOp prev_op{};
+    int half = 0;
+    auto emit = [&](LbfgsOp o, const bool overlap) {
+        o.part_out = half;
+        o.part_in = prev_op.part_out;
+        if (prev_op.defer) {
+            o.pro_epilogue = prev_op.epilogue; o.pro_rho_dot = prev_op.rho_dot;
+            o.pro_alpha_in = prev_op.alpha_in; o.pro_out = prev_op.out;
+        }
+        o.defer = d->lbfgs_defer && o.kind <= 2 && (o.epilogue == 1 || o.epilogue == 2) ? 1 : 0;
+        launch_pass(d, c, o, overlap);
+        prev_op = o;
+        half ^= 1;
+    };
+
     LbfgsOp op{};
     // q = -g, fused with the dot the newest pair needs
     op.kind = 0; op.col_dot = -1; op.epilogue = 0; op.descent = (d->lbfgs_mode & 2) ? 1 : 0;
@@ -724,7 +775,7 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
         const int idx = slot(hc - 1);
         op.col_dot = col_s(idx); op.rho_dot = rho_of(idx); op.epilogue = 1; op.out = alpha + (hc - 1);
     }
-    launch_pass(d, c, op, false);
+    emit(op, false);
 
     // first loop, newest to oldest: q -= alpha_j * y_j, fused with the next dot
     for (int j = hc - 1; j >= 0; --j) {
@@ -738,7 +789,7 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
             const int nx = slot(0);                                  // second loop starts with beta_0 = rho_0 * y_0.r
             o.col_dot = col_y(nx); o.rho_dot = rho_of(nx); o.epilogue = 2; o.out = coeff; o.alpha_in = alpha + 0;
         }
-        launch_pass(d, c, o);
+        emit(o, true);
     }
 
     // second loop, oldest to newest: r += (alpha_j - beta_j) * s_j, fused with the next dot
@@ -751,7 +802,7 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
             const int nx = slot(j + 1);
             o.col_dot = col_y(nx); o.rho_dot = rho_of(nx); o.epilogue = 2; o.out = coeff; o.alpha_in = alpha + (j + 1);
         }
-        launch_pass(d, c, o);
+        emit(o, true);
     }
 
     // p = -r ; x += step*p ; old_g <- g ; s[hi] = step*p ; y[prev], rho[prev]
@@ -763,6 +814,7 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
         o.col_y_prev = col_y(prev); o.col_s_prev = col_s(prev);
         o.col_dot = hc > 0 ? col_s(prev) : -1;
         o.epilogue = hc > 0 ? 3 : 0; o.out = (float*)rho_bufs[prev];
+        o.part_in = 0; o.part_out = 0;
         launch_pass(d, c, o);
     }
     GM_CUDA_CHECK(cudaGetLastError());

@@ -456,9 +456,9 @@ lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__
         float* psum = partials + ((barrier_no + 1) & 1u) * (size_t)tb.num_chunks;
         if (!final_pass) {
             const bool writes = ps.kind == 0 || !skip_axpy;
-            const WalkArgs wa{coef, has_vec, want_dot, writes, pol};
-            axpy_dot_walk(tb, ps.kind, plan.descent, ps.col_axpy, ps.col_dot, 0, psum, warp_sum, blockIdx.x, G,
-                          [&]() -> WalkArgs { return wa; });
+            const WalkArgs wa{coef, has_vec, want_dot, writes};
+            axpy_dot_walk(tb, ps.kind, plan.descent, ps.col_axpy, ps.col_dot, 0, pol, psum, warp_sum, blockIdx.x, G,
+                          []() {}, [&]() -> WalkArgs { return wa; });
         } else {
             for (int c = blockIdx.x; c < tb.num_chunks; c += G) {
                 const CoopChunk ck = coop_locate(tb, c);
