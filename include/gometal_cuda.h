@@ -168,7 +168,7 @@ int gm_device_synchronize_timeout(uintptr_t device_ptr, int timeout_ms);
 /* Launch-strategy switches of a handle; every setting computes the same bits.  Names:
  * "mixed_ring" (2: the mixed-precision step as one cooperative launch, 1: overflow check
  * followed by the shared-memory-ring update, 0: check followed by the one-CTA-per-chunk
- * update), "mixed_fastdiv", "mixed_pf", "mixed_variant", "lbfgs_coop", "lbfgs_prewait",
+ * update), "mixed_fastdiv", "mixed_pf", "mixed_variant", "lbfgs_coop", "lbfgs_prewait", "lbfgs_defer",
  * "barrier_budget_cycles" (bound of every device-side barrier wait). */
 int gm_device_set_tuning(uintptr_t device_ptr, const char* name, long long value);
 long long gm_device_get_tuning(uintptr_t device_ptr, const char* name);   /* -1: unknown name */
