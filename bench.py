@@ -131,11 +131,11 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU arm: the oracle timed on the host cores
 # ---------------------------------------------------------------------------
-def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | None):
-    """Returns (Gparams/s, cores, steps_run, seconds_per_step)."""
+def cpu_adam_rate(steps: int, warmup: int, sample_elems: int, budget_s: float | None, threads: int | None = None):
+    """Returns (Gparams/s, threads used, steps_run, seconds_per_step)."""
     import numpy as np
     from oracle import oracle as O
-    cores = os.cpu_count() or 1
+    cores = threads or os.cpu_count() or 1
     n = sample_elems
     lim = float(np.sqrt(6.0 / 4096.0))
     O.set_threads(cores)
@@ -869,7 +869,10 @@ def run_gpu(args):
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             rate, cores, done, per = cpu_adam_rate(50, 1, CPU_SAMPLE, 12.0)
-            cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(done)}
+            one, _, done1, _ = cpu_adam_rate(4, 1, CPU_SAMPLE // 4, 3.0, threads=1)
+            cpu = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(done),
+                   "single_thread": {"value": one, "unit": UNIT,
+                                     "sample": f"{done1} steps over {CPU_SAMPLE // 4} parameters, one thread"}}
         cfg = dict(CONFIG)
         if NUM_TENSORS != 256:
             cfg["workload"] = f"REDUCED for profiling: {NUM_TENSORS} tensors"

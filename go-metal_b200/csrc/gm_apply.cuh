@@ -96,6 +96,17 @@ __device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
+// One 64-bit word read or written as a unit at GPU scope: a value and its tag travel together,
+// so a reader that sees the tag has the value and no fence is needed on either side.
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+
 // Waits until *word == epoch, but no longer than `budget` clock cycles.  False: gave up.
 __device__ __forceinline__ bool bounded_wait_for(const unsigned* word, const unsigned epoch, const long long budget) {
     const long long t0 = clock64();

@@ -198,6 +198,17 @@ int ensure_partials(Device* d, int64_t count) {
     return GM_OK;
 }
 
+int ensure_tagged(Device* d, int64_t count) {
+    if (count <= d->tagged_cap) return GM_OK;
+    DeviceGuard g(d);
+    int64_t cap = round_up(count, 4096);
+    if (d->tagged) { cudaStreamSynchronize(d->stream); cudaFree(d->tagged); d->tagged = nullptr; d->tagged_cap = 0; }
+    GM_CUDA_CHECK(cudaMalloc((void**)&d->tagged, (size_t)cap * sizeof(unsigned long long)));
+    GM_CUDA_CHECK(cudaMemset(d->tagged, 0, (size_t)cap * sizeof(unsigned long long)));   // epoch 0 is never waited for
+    d->tagged_cap = cap;
+    return GM_OK;
+}
+
 int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items) {
     // grid_waves == 0: one CTA per chunk.  Measured on B200, a large grid of
     // short-lived CTAs streams about 15 % faster than resident CTAs looping
@@ -535,6 +546,7 @@ void destroy_cuda_device(uintptr_t h) {
     for (TensorList* l : lists) free_list(l);
     lbfgs_release_device(d);
     if (d->partials) cudaFree(d->partials);
+    if (d->tagged) cudaFree(d->tagged);
     if (d->ticket) cudaFree(d->ticket);
     if (d->scalars) cudaFree(d->scalars);
     cudaEventDestroy(d->ev_start);

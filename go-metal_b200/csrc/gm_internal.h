@@ -101,6 +101,9 @@ struct Device {
     // scratch for reductions (dot partials, tickets); grown on demand
     float* partials = nullptr;
     int64_t partials_cap = 0;
+    // chunk sums of the single-launch L-BFGS step, each a 64-bit word {barrier epoch, sum}; zeroed when allocated
+    unsigned long long* tagged = nullptr;
+    int64_t tagged_cap = 0;
     unsigned int* ticket = nullptr;     // one counter for last-CTA-done finishes
     float* scalars = nullptr;           // small device scratch for L-BFGS scalars
 };
@@ -149,6 +152,7 @@ void free_list(TensorList* l);
 int launch_grid(Device* d, const void* kernel, int threads, int64_t work_items);
 
 int ensure_partials(Device* d, int64_t count);
+int ensure_tagged(Device* d, int64_t count);
 constexpr int kDotChunkElems = 4096;    // elements per chunk of the fixed-order reductions
 
 // ---- rule launchers (gm_rules.cu) ----

@@ -274,17 +274,17 @@ struct WalkArgs {
 
 // The chunk walk shared by the multi-launch pass kernel and the single-launch step: kinds 0, 1
 // and 2 over chunks first, first + stride, ...; the loads of the next chunk are issued before the
-// current chunk's sum is reduced; chunk sums land in partials[chunk].
+// current chunk's sum is reduced; thread 0 hands every chunk sum to store(chunk, sum).
 //
 // The history columns are read-only for the whole step, so the walk loads its first chunk of
 // them (prewait >= 1) and asks L2 for its second (prewait >= 2) BEFORE it calls gate(), which
 // in the multi-launch step is where the grid waits for its predecessor: while that grid's last
 // CTA adds up the chunk sums, DRAM already works for this one.  Only the direction, the
 // coefficient and the curvature test wait for the gate.
-template <class Sync, class Gate>
+template <class Store, class Sync, class Gate>
 __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int kind, const int descent, const int col_axpy,
                                               const int col_dot, const int prewait, const unsigned long long pol,
-                                              float* __restrict__ partials, float* warp_sum, const int first,
+                                              Store store, float* warp_sum, const int first,
                                               const int stride, Sync sync, Gate gate) {
     constexpr int PASSES = kDotChunk / (kDotThreads * 4);
     const int tid = threadIdx.x;
@@ -393,7 +393,7 @@ __device__ __forceinline__ void axpy_dot_walk(const LbfgsTable& tb, const int ki
         }
         if (a.want_dot) {
             const float total = cta_reduce_256(acc, warp_sum);
-            if (tid == 0) partials[c] = total;
+            if (tid == 0) store(c, total);
         }
         c = cn;
         cur = nxt;
@@ -449,7 +449,7 @@ lbfgs_axpy_dot_kernel(const LbfgsTable tb, const LbfgsOp op, float* __restrict__
         return a;
     };
     axpy_dot_walk(tb, kind, op.descent, op.col_axpy, op.col_dot, kind == 0 ? 0 : op.prewait, l2_policy(op.keep_dir != 0),
-                  part_out, warp_sum, blockIdx.x, gridDim.x, sync, gate);
+                  [&](int c, float v) { part_out[c] = v; }, warp_sum, blockIdx.x, gridDim.x, sync, gate);
     if (!op.early_trigger) asm volatile("griddepcontrol.launch_dependents;");
     if (!op.defer) finish_pass(tb, op, want_dot, part_out, ticket, warp_sum, &is_last);
 }
@@ -732,7 +732,11 @@ static int lbfgs_step(uintptr_t device_ptr, uintptr_t* w, uintptr_t* g, uintptr_
                 GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_coop_kernel, dim3(grid), dim3(kCoopThreads), args,
                                                           kCoopSmemBytes, d->stream));
             } else {
-                GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_fused_kernel, dim3(grid), dim3(kDotThreads), args, 0,
+                rc = ensure_tagged(d, 2LL * c->tb.num_chunks);
+                if (rc != GM_OK) return rc;
+                unsigned long long* tagged = d->tagged;
+                void* fargs[] = {&tbv, &plan, &tagged, &ctl, &keep_dir};
+                GM_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)lbfgs_fused_kernel, dim3(grid), dim3(kDotThreads), fargs, 0,
                                                           d->stream));
             }
             d->launches++;

@@ -410,27 +410,28 @@ lbfgs_coop_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__ 
 // ---- the step as one launch with the direction left in L2 ("lbfgs_coop" = 2) ----
 // The same passes as the multi-launch step, by the same chunk walk (axpy_dot_walk) with the
 // direction read and written through L2 under the evict_last policy, but inside ONE
-// cooperative launch: between two passes stands a bounded grid-wide barrier instead of a
-// kernel boundary, and every CTA adds the chunk sums up itself.  A CTA walks the same
-// chunks in every pass, so it only ever reads direction values it wrote itself.  The idea:
-// trade the fixed cost of a pass (launch, table warm-up, last-CTA finisher, drain -- about
-// 7 us of the 23 us a pass takes at n = 10^7) for a barrier.  MEASURED: 0.561 ms per step
-// against 0.507-0.519 ms for the multi-launch step on the same box -- the barrier, the
-// 2,442 chunk sums every CTA re-reads and the 128 registers the walk needs inside the pass
-// loop (two CTAs per SM instead of three; at 80 registers it spills in its inner loop and
-// takes 0.775 ms) cost more than the launches they replace, which programmatic stream
-// serialization already overlaps.  Not the default.
+// cooperative launch.  A CTA walks the same chunks in every pass, so it only ever reads
+// direction values it wrote itself; the only thing that crosses CTAs is the dot product, and
+// that travels as tagged 64-bit words (see the pass loop), collected by every CTA under the
+// first loads of its next pass.  The idea: trade the fixed cost of a pass (launch, table
+// warm-up, finisher, drain) for that exchange.  MEASURED per step at n = 10^7, m = 10, same
+// box: 0.561 ms with a counter barrier (fence, atomic arrival, go word) waited for before the
+// next pass's loads; 0.537 ms with the wait moved under those loads; 0.510 ms with the tagged
+// words (floor of a pass 6.3 -> 5.9 -> 4.4 us); against 0.477 ms for the multi-launch step,
+// whose passes leave their final sum to the next launch in the same way.  What is left is the
+// 126 registers the walk needs inside the pass loop: two CTAs per SM instead of three (at 80
+// registers it spills in its inner loop: 0.775 ms), and the passes stream slower for it.  Not
+// the default.
 #ifndef GM_LBFGS_FUSED_MINB
 #define GM_LBFGS_FUSED_MINB 2      // 128 registers: at 3 CTAs per SM (80 registers) the walk spills inside its loop
 #endif
 __global__ void __launch_bounds__(kDotThreads, GM_LBFGS_FUSED_MINB)
-lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__ partials, unsigned int* __restrict__ ctl,
-                   const int keep_dir) {
+lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, unsigned long long* __restrict__ tagged,
+                   unsigned int* __restrict__ ctl, const int keep_dir) {
     __shared__ float warp_sum[kDotThreads / 32];
     __shared__ float s_alpha[kCoopMaxHistory];
     __shared__ float s_coef;
     __shared__ float s_dot;
-    __shared__ int s_ok;
     const int tid = threadIdx.x;
     const int G = gridDim.x;
     const unsigned long long pol = l2_policy(keep_dir != 0);
@@ -438,28 +439,92 @@ lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__
     if (tid == 0) s_coef = 0.0f;
     __syncthreads();
 
+    // A pass's dot product is finished inside the NEXT pass.  The producer writes every chunk sum
+    // as ONE 64-bit word {barrier epoch, sum} (a single relaxed store at GPU scope: the tag and
+    // the value arrive together, so there is no fence, no arrival counter and no go word).  The
+    // consumer first issues the loads of its first chunk -- the history columns are read-only
+    // and a CTA only reads direction values it wrote itself, so they depend on nobody -- and
+    // only then collects the sums: lane t spins, bounded, on the words of chunks t, t+256, ...
+    // which are exactly the ones it adds up, in that order.  Two halves alternate with the
+    // barriers, so a word is only overwritten after every CTA has read it.
     unsigned barrier_no = 0;
+    bool pending = false;                 // chunk sums have been written and not yet collected
+    int pend_epilogue = 0, pend_alpha_in = -1, pend_out_alpha = -1;
+    float pend_rho = 0.0f;
+    bool failed = false;
+    auto publish = [&](const int epilogue, const bool have, const float dot, const float rho_dot, const int alpha_in,
+                       const int out_alpha) {
+        if (tid == 0) {
+            float r = 0.0f;
+            switch (epilogue) {
+                case 1: r = have ? mul(dot, rho_dot) : 0.0f; break;
+                case 2: r = have ? sub(s_alpha[alpha_in], mul(dot, rho_dot)) : 0.0f; break;
+                default: r = (plan.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
+            }
+            if (epilogue == 1) { s_alpha[out_alpha] = r; if (blockIdx.x == 0) plan.alpha[out_alpha] = r; }
+            else if (epilogue == 2) s_coef = r;
+            else if (blockIdx.x == 0) *plan.rho_prev = r;
+        }
+        __syncthreads();
+    };
+    auto slots_of = [&](const unsigned barrier) { return tagged + (size_t)(barrier & 1u) * (size_t)tb.num_chunks; };
+    auto resolve = [&]() {
+        if (!pending) return;
+        pending = false;
+        const unsigned epoch = plan.epoch_base + barrier_no;
+        const unsigned long long* slots = slots_of(barrier_no);
+        const long long t0 = clock64();
+        float acc = 0.0f;
+        int ok = 1;
+        for (int c = tid; c < tb.num_chunks && ok; c += kDotThreads) {
+            unsigned long long w = ld_relaxed_u64(slots + c);
+            while ((unsigned)(w >> 32) != epoch) {
+                if (clock64() - t0 > plan.barrier_budget) { ok = 0; break; }
+                __nanosleep(32);
+                w = ld_relaxed_u64(slots + c);
+            }
+            if (ok) acc = add(acc, __uint_as_float((unsigned)w));
+        }
+        if (!__syncthreads_and(ok)) {
+            if (tid == 0) atomicExch(ctl + kLbError, 1u);
+            failed = true;
+            return;
+        }
+        const float total = cta_reduce_256(acc, warp_sum);
+        if (tid == 0) s_dot = total;
+        __syncthreads();
+        publish(pend_epilogue, true, s_dot, pend_rho, pend_alpha_in, pend_out_alpha);
+    };
+
     for (int pi = 0; pi < plan.num_passes; ++pi) {
         const CoopPass& ps = plan.pass[pi];
         const bool final_pass = ps.kind == 3;
-        bool skip_axpy = false, want_dot = false, has_vec = false;
-        float coef = 0.0f, rho_dot = 0.0f;
+        // the half no CTA can still be reading: it alternates with the barriers, not with the passes
+        unsigned long long* slots_out = slots_of(barrier_no + 1u);
+        const unsigned long long tag_out = (unsigned long long)(plan.epoch_base + barrier_no + 1u) << 32;
+        auto store = [&](int c, float v) { st_relaxed_u64(slots_out + c, tag_out | (unsigned long long)__float_as_uint(v)); };
+        bool want_dot = false;
+        float rho_dot = 0.0f;
         if (!final_pass) {
-            skip_axpy = ps.kind != 0 && rho_skips(plan.rho[ps.rho_axpy]);
+            const bool skip_axpy = ps.kind != 0 && rho_skips(plan.rho[ps.rho_axpy]);
             want_dot = ps.col_dot >= 0 && !(ps.rho_dot >= 0 && rho_skips(plan.rho[ps.rho_dot]));
-            has_vec = ps.kind != 0 && !skip_axpy;
-            if (ps.kind != 0) coef = ps.coef_alpha >= 0 ? s_alpha[ps.coef_alpha] : s_coef;
-            if (ps.rho_dot >= 0) rho_dot = *plan.rho[ps.rho_dot];
-        } else {
-            want_dot = plan.have_pair != 0;
-        }
-        float* psum = partials + ((barrier_no + 1) & 1u) * (size_t)tb.num_chunks;
-        if (!final_pass) {
+            const bool has_vec = ps.kind != 0 && !skip_axpy;
             const bool writes = ps.kind == 0 || !skip_axpy;
-            const WalkArgs wa{coef, has_vec, want_dot, writes};
-            axpy_dot_walk(tb, ps.kind, plan.descent, ps.col_axpy, ps.col_dot, 0, pol, psum, warp_sum, blockIdx.x, G,
-                          []() {}, [&]() -> WalkArgs { return wa; });
+            if (ps.rho_dot >= 0) rho_dot = *plan.rho[ps.rho_dot];
+            axpy_dot_walk(tb, ps.kind, plan.descent, ps.col_axpy, ps.col_dot, 1, pol, store, warp_sum, blockIdx.x, G,
+                          []() {},
+                          [&]() -> WalkArgs {
+                              resolve();
+                              float coef = 0.0f;
+                              if (ps.kind != 0) coef = ps.coef_alpha >= 0 ? s_alpha[ps.coef_alpha] : s_coef;
+                              // after a wait that ran out the pass is skipped and the kernel returns below
+                              return WalkArgs{coef, has_vec && !failed, want_dot && !failed, writes && !failed};
+                          });
+            if (failed) return;
         } else {
+            resolve();
+            if (failed) return;
+            want_dot = plan.have_pair != 0;
             for (int c = blockIdx.x; c < tb.num_chunks; c += G) {
                 const CoopChunk ck = coop_locate(tb, c);
                 const float* dirg = reinterpret_cast<const float*>(__ldg(tb.ptrs + (size_t)COL_DIR * tb.T + ck.t));
@@ -477,52 +542,21 @@ lbfgs_fused_kernel(const LbfgsTable tb, const CoopPlan plan, float* __restrict__
                 const float acc = coop_final_chunk(tb, ck, plan, tid, d);
                 if (want_dot) {
                     const float total = cta_reduce_256(acc, warp_sum);
-                    if (tid == 0) psum[c] = total;
+                    if (tid == 0) store(c, total);
                 }
             }
         }
         if (ps.epilogue == 0) continue;
-
-        float dot = 0.0f;
-        if (want_dot) {
-            barrier_no += 1;
-            __syncthreads();
-            if (tid == 0) {
-                int ok = 1;
-                __threadfence();
-                const unsigned arrived = atomicAdd(ctl + kLbArrive, 1u);
-                if (arrived == (unsigned)G - 1u) {
-                    ctl[kLbArrive] = 0u;
-                    __threadfence();
-                    st_release(ctl + kLbGo, plan.epoch_base + barrier_no);
-                } else if (!bounded_wait_for(ctl + kLbGo, plan.epoch_base + barrier_no, plan.barrier_budget)) {
-                    atomicExch(ctl + kLbError, 1u);
-                    ok = 0;
-                }
-                s_ok = ok;
-            }
-            __syncthreads();
-            if (!s_ok) return;
-            float acc = 0.0f;
-            for (int c = tid; c < tb.num_chunks; c += kDotThreads) acc = add(acc, __ldcg(psum + c));
-            const float total = cta_reduce_256(acc, warp_sum);
-            if (tid == 0) s_dot = total;
-            __syncthreads();
-            dot = s_dot;
+        if (!want_dot) {
+            publish(ps.epilogue, false, 0.0f, rho_dot, ps.alpha_in, ps.out_alpha);     // the scalar is zero
+            continue;
         }
-        if (tid == 0) {
-            float r = 0.0f;
-            switch (ps.epilogue) {
-                case 1: r = want_dot ? mul(dot, rho_dot) : 0.0f; break;
-                case 2: r = want_dot ? sub(s_alpha[ps.alpha_in], mul(dot, rho_dot)) : 0.0f; break;
-                default: r = (plan.have_pair && fabs((double)dot) > 1e-10) ? dvd(1.0f, dot) : 0.0f; break;
-            }
-            if (ps.epilogue == 1) { s_alpha[ps.out_alpha] = r; if (blockIdx.x == 0) plan.alpha[ps.out_alpha] = r; }
-            else if (ps.epilogue == 2) s_coef = r;
-            else if (blockIdx.x == 0) *plan.rho_prev = r;
-        }
-        __syncthreads();
+        barrier_no += 1;
+        pending = true;
+        pend_epilogue = ps.epilogue; pend_alpha_in = ps.alpha_in; pend_out_alpha = ps.out_alpha;
+        pend_rho = rho_dot;
     }
+    resolve();                                            // the final pass's s.y -> rho
 }
 
 }  // namespace gm
