@@ -310,7 +310,7 @@ def workload_lbfgs(gm, dev, torch, peak, reps):
     return _entry("L-BFGS iteration, n = 10,000,000, history 10 full (config 5; working mode)", n, med, 44 + 32 * m, must,
                   f"{must} B/element: what has to cross DRAM if the direction vector never left the chip "
                   "(history vectors do not fit L2, so each is read once per loop); the kernels' own ncu "
-                  "DRAM traffic is 215 B/element", peak,
+                  "DRAM traffic is 198 B/element", peak,
                   kernels=f"{2 * m + 1} x lbfgs_axpy_dot_kernel + lbfgs_pass_kernel", iterations_timed=len(times),
                   pairs_accepted=accepted, timing="CUDA events around the synchronous drop-in entry, median")
 
