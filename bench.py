@@ -371,6 +371,60 @@ def workload_rules(gm, dev, torch, peak, reps):
     return out
 
 
+def workload_small(gm, dev, torch, reps):
+    """The two small configurations: everything is L2-resident, so the figure is microseconds per
+    step, not bandwidth.  Config 1: Adam on the 101,770-parameter MLP (4 tensors); config 2: the
+    five other rules on the 545,098-parameter CNN (8 tensors)."""
+    L = gm.lib
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 40)
+    out = []
+
+    def make(sizes, streams):
+        n = sum(sizes)
+        bufs = [torch.zeros(n, dtype=torch.float32, device="cuda") for _ in range(streams)]
+        bufs[0].uniform_(-0.05, 0.05, generator=gen)
+        bufs[1].normal_(0.0, 0.01, generator=gen)
+        offs = [sum(sizes[:k]) for k in range(len(sizes))]
+        return bufs, [[b.data_ptr() + 4 * o for o in offs] for b in bufs]
+
+    mlp = [784 * 128, 128, 128 * 10, 10]
+    cnn = [864, 32, 18432, 64, 524288, 128, 1280, 10]
+    cases = [("config 1: Adam, MLP, 101,770 params in 4 tensors", gm.RULE_ADAM, mlp, 4,
+              dict(lr=LR, beta1=B1, beta2=B2, eps=EPS)),
+             ("config 2: SGD with momentum, CNN, 545,098 params in 8 tensors", gm.RULE_SGD, cnn, 3, dict(lr=0.01, beta1=0.9)),
+             ("config 2: RMSProp", gm.RULE_RMSPROP, cnn, 3, dict(lr=0.01, beta1=0.99, eps=1e-8)),
+             ("config 2: AdaGrad", gm.RULE_ADAGRAD, cnn, 3, dict(lr=0.01, eps=1e-10)),
+             ("config 2: AdaDelta", gm.RULE_ADADELTA, cnn, 4, dict(beta1=0.9, eps=1e-6)),
+             ("config 2: NAdam", gm.RULE_NADAM, cnn, 4, dict(lr=2e-3, beta1=0.9, beta2=0.999, eps=1e-8))]
+    for name, rule, sizes, streams, hp in cases:
+        bufs, ptrs = make(sizes, streams)
+        lst = dev.tensor_list(ptrs, sizes)
+        hy = gm.Hyper(step=1, **hp)
+        state = {"t": 0}
+
+        def one():
+            state["t"] += 1
+            hy.step = state["t"]
+            gm.check(L.gm_step_async(dev.h, rule, lst, C.byref(hy)), name)
+
+        n_async = max(reps, 20) * 10
+        us_async = _event_timed(gm, dev, one, n_async) * 1e3
+        # the same step, synchronous: returns with the results in the buffers, as the reference's entry does
+        for _ in range(3):
+            one(); dev.sync()
+        t0 = time.perf_counter()
+        for _ in range(n_async):
+            one(); dev.sync()
+        us_sync = (time.perf_counter() - t0) / n_async * 1e6
+        out.append({"name": name, "params": sum(sizes), "us_per_step_back_to_back": us_async,
+                    "us_per_step_synchronous": us_sync, "steps_timed": n_async,
+                    "note": "L2-resident: latency-bound, one launch per step"})
+        L.gm_tensor_list_destroy(lst)
+        del bufs
+    return out
+
+
 def run_only(args):
     """Profiler captures: one of the other configurations alone, a few repetitions, one JSON line."""
     import torch
@@ -381,7 +435,7 @@ def run_only(args):
     dev = gm.Device(0)
     peak, _ = measured_peak_gbs()
     fn = {"mixed": workload_mixed, "mixed_clip": lambda *a: workload_mixed(*a, clip=True), "lbfgs": workload_lbfgs,
-          "rules": workload_rules}[args.only]
+          "rules": workload_rules, "small": lambda gm_, dev_, torch_, peak_, reps_: workload_small(gm_, dev_, torch_, reps_)}[args.only]
     out = fn(gm, dev, torch, peak, max(args.steps, 1))
     dev.close()
     print(json.dumps({"only": args.only, "result": out}))
@@ -536,8 +590,9 @@ def run_workloads(gm, dev, torch, reps):
     torch.cuda.empty_cache()
     entries.extend(workload_rules(gm, dev, torch, peak, max(reps // 2, 10)))
     torch.cuda.empty_cache()
+    small = workload_small(gm, dev, torch, reps)
     return {"peak_gbs": peak, "peak_source": f"of {peak_kind}", "timing": "CUDA events on the launching stream, after warm-up; "
-            "every list is larger than the 126 MB L2", "entries": entries}
+            "every list is larger than the 126 MB L2", "entries": entries, "small_configs": small}
 
 
 # ---------------------------------------------------------------------------
@@ -922,7 +977,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--tensors", type=int, default=256,
                     help="profiling runs only: fewer 4 Mi tensors than the 256 of the workload")
-    ap.add_argument("--only", choices=["mixed", "mixed_clip", "lbfgs", "rules"],
+    ap.add_argument("--only", choices=["mixed", "mixed_clip", "lbfgs", "rules", "small"],
                     help="profiling runs only: time one of the other configurations alone for --steps repetitions")
     args = ap.parse_args()
     if args.impl == "reference":
