@@ -82,3 +82,30 @@ def test_too_large_for_the_chip_takes_the_multi_launch_step(gm, dev, oracle, coo
         assert coop() > 3
     finally:
         oracle.set_threads(1)
+
+
+# ---- launch-strategy switches of the multi-launch step: every setting gives the oracle's bits ----
+@pytest.fixture(params=[("lbfgs_defer", 0), ("lbfgs_prewait", 0), ("lbfgs_prewait", 2)],
+                ids=["own_final_sum", "no_early_loads", "early_loads_and_l2_prefetch"])
+def multi_launch_switch(request, gm, dev):
+    L = gm.lib
+    name, value = request.param
+    before = L.gm_device_get_tuning(dev.h, name.encode())
+    assert before >= 0, f"unknown switch {name}"
+    gm.check(L.gm_device_set_tuning(dev.h, name.encode(), value), "switch")
+    yield
+    gm.check(L.gm_device_set_tuning(dev.h, name.encode(), before), "restore")
+
+
+@pytest.mark.parametrize("mode", [0, 3])
+def test_switches_well_conditioned(gm, dev, oracle, multi_launch_switch, mode):
+    TL.test_lbfgs_well_conditioned_50_iterations(gm, dev, oracle, mode)
+
+
+def test_switches_ill_conditioned_pairs_rejected(gm, dev, oracle, multi_launch_switch):
+    TL.test_lbfgs_ill_conditioned_as_configured(gm, dev, oracle, 0)
+
+
+def test_switches_ragged_and_unaligned(gm, dev, oracle, multi_launch_switch):
+    TL.test_lbfgs_multi_tensor_short_history(gm, dev, oracle)
+    TL.test_lbfgs_unaligned_buffers(gm, dev, oracle, [0, 0, 0, 2, 0, 1, 0])

@@ -45,7 +45,11 @@ def main():
     assert z, gm.last_error()
     assert L.gm_zero1_rank(z) == rank and L.gm_zero1_world(z) == world
 
-    for exchange in ("nccl", "push", "dma", "push_host"):
+    # GM_TEST_EXCHANGES narrows the run to some exchange paths (and leaves out the mixed-precision
+    # and reduce-scatter parts): used to repeat the push path under its other store orders.
+    only = os.environ.get("GM_TEST_EXCHANGES")
+    exchanges = tuple(only.split(",")) if only else ("nccl", "push", "dma", "push_host")
+    for exchange in exchanges:
         w0 = O.fill_uniform(T * E, -0.1, 0.1, 91, 1)
         full, fm, fv = w0.copy(), np.zeros(T * E, np.float32), np.zeros(T * E, np.float32)
         arena = dev.to_device(w0)
@@ -117,9 +121,10 @@ def main():
         if exchange == "nccl":
             dev.free(arena)
         # the pushed arena stays mapped by the peers until the group is destroyed
-    mixed_zero1(L, dev, z, plan, rank, "nccl")
-    mixed_zero1(L, dev, z, plan, rank, "push")
-    reduce_scatter(L, dev, z, plan, rank, world)
+    if not only:
+        mixed_zero1(L, dev, z, plan, rank, "nccl")
+        mixed_zero1(L, dev, z, plan, rank, "push")
+        reduce_scatter(L, dev, z, plan, rank, world)
     dist.barrier()
     L.gm_zero1_destroy(z)
     dist.barrier()
