@@ -383,15 +383,20 @@ int gm_zero1_allgather_async(uintptr_t h, uintptr_t arena_base, int64_t count, i
     return GM_OK;
 }
 
-int gm_zero1_adam_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper, uintptr_t arena_base,
-                             int64_t count) {
+int gm_zero1_step_async(uintptr_t h, int rule, uintptr_t shard_list, const gm_hyper_t* hyper, uintptr_t arena_base,
+                        int64_t count) {
     Zero1* z = as_zero1(h);
     if (!z) return GM_ERR_BAD_ARG;
     TensorList* l = as_list(shard_list);
     if (!l || !hyper) { if (l) set_error("hyper-parameters are nil"); return GM_ERR_BAD_ARG; }
-    int rc = launch_rule(z->dev, GM_RULE_ADAM, l, *hyper);
+    int rc = launch_rule(z->dev, rule, l, *hyper);
     if (rc != GM_OK) return rc;
     return gm_zero1_allgather_async(h, arena_base, count, 4);
+}
+
+int gm_zero1_adam_step_async(uintptr_t h, uintptr_t shard_list, const gm_hyper_t* hyper, uintptr_t arena_base,
+                             int64_t count) {
+    return gm_zero1_step_async(h, GM_RULE_ADAM, shard_list, hyper, arena_base, count);
 }
 
 // cudaIpcGetMemHandle describes a whole device allocation, and the peer that opens it

@@ -254,6 +254,12 @@ func (z *Zero1) AdamStepAsync(shard *TensorList, hyper Hyper, arenaBase unsafe.P
 	return stepError("ZeRO-1 Adam", C.gm_zero1_adam_step_async(z.h, shard.h, &ch, handle(arenaBase), C.int64_t(countPerRank)))
 }
 
+// StepAsync is AdamStepAsync for any fp32 rule: the shard's update, then the in-place all-gather.
+func (z *Zero1) StepAsync(rule Rule, shard *TensorList, hyper Hyper, arenaBase unsafe.Pointer, countPerRank int64) error {
+	ch := hyper.c()
+	return stepError("ZeRO-1 step", C.gm_zero1_step_async(z.h, C.int(rule), shard.h, &ch, handle(arenaBase), C.int64_t(countPerRank)))
+}
+
 // IPCHandle exports this rank's arena; OpenPeers maps every rank's handle (rank order, 64 bytes each).
 func (z *Zero1) IPCHandle(arenaBase unsafe.Pointer) ([64]byte, error) {
 	var hnd [64]byte

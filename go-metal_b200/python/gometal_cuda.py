@@ -126,6 +126,7 @@ _SIGS = {
     "gm_zero1_destroy": (None, [u]),
     "gm_zero1_allgather_async": (i, [u, u, i64, i]),
     "gm_zero1_adam_step_async": (i, [u, u, C.POINTER(Hyper), u, i64]),
+    "gm_zero1_step_async": (i, [u, i, u, C.POINTER(Hyper), u, i64]),
     "gm_zero1_rank": (i, [u]),
     "gm_zero1_world": (i, [u]),
     "gm_zero1_ipc_handle": (i, [u, u, vp]),

@@ -336,7 +336,10 @@ void gm_zero1_destroy(uintptr_t zero1);
  * updated elements [r*count, (r+1)*count). */
 int gm_zero1_allgather_async(uintptr_t zero1, uintptr_t arena_base, int64_t count_per_rank,
                              int elem_bytes);
-/* Update of this rank's shard, then the all-gather, on one stream. */
+/* Update of this rank's shard, then the all-gather, on one stream: any fp32 rule
+ * (GM_RULE_*; stream 0 of the list is the parameters), or Adam by name. */
+int gm_zero1_step_async(uintptr_t zero1, int rule, uintptr_t shard_list, const gm_hyper_t* hyper,
+                        uintptr_t arena_base, int64_t count_per_rank);
 int gm_zero1_adam_step_async(uintptr_t zero1, uintptr_t shard_list, const gm_hyper_t* hyper,
                              uintptr_t arena_base, int64_t count_per_rank);
 int gm_zero1_rank(uintptr_t zero1);

@@ -122,6 +122,7 @@ def main():
             dev.free(arena)
         # the pushed arena stays mapped by the peers until the group is destroyed
     if not only:
+        other_rule_zero1(L, dev, z, plan, rank)
         mixed_zero1(L, dev, z, plan, rank, "nccl")
         mixed_zero1(L, dev, z, plan, rank, "push")
         reduce_scatter(L, dev, z, plan, rank, world)
@@ -131,6 +132,38 @@ def main():
     dev.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
+
+
+def other_rule_zero1(L, dev, z, plan, rank):
+    """The sharded step is not Adam's alone: NAdam through the rule-generic entry (update of the
+    shard, then the all-gather), every rank's whole arena against the oracle."""
+    w0 = O.fill_uniform(T * E, -0.1, 0.1, 93, 1)
+    full, fm, fv = w0.copy(), np.zeros(T * E, np.float32), np.zeros(T * E, np.float32)
+    arena = dev.to_device(w0)
+    dg = dev.alloc(4 * plan.shard_elems)
+    dm = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+    dv = dev.to_device(np.zeros(plan.shard_elems, np.float32))
+    w_ptrs = [arena + 4 * plan.tensor_offset(k) for k in plan.owned]
+    loc = lambda base: [base + 4 * plan.local_offset(k) for k in plan.owned]
+    lst = dev.tensor_list([w_ptrs, loc(dg), loc(dm), loc(dv)], [E] * plan.tensors_per_rank)
+    for step in range(1, 4):
+        grads = [O.fill_normal(E, 0.0, 0.01, 93, 1000 * step + k) for k in range(T)]
+        dev.upload(dg, np.concatenate([grads[k] for k in plan.owned]))
+        hy = gm.Hyper(lr=2e-3, beta1=B1, beta2=B2, eps=EPS, weight_decay=WD, step=step)
+        gm.check(L.gm_zero1_step_async(z, gm.RULE_NADAM, lst, C.byref(hy), arena, plan.shard_elems), "zero1 NAdam step")
+        dev.sync()
+        for k in range(T):
+            a = k * E
+            ws, ms, vs = (np.ascontiguousarray(x[a:a + E]) for x in (full, fm, fv))
+            O.nadam_step(ws, grads[k], ms, vs, 2e-3, B1, B2, EPS, WD, step)
+            full[a:a + E], fm[a:a + E], fv[a:a + E] = ws, ms, vs
+        got = dev.to_host(arena, T * E)
+        bad = np.flatnonzero(got.view(np.uint32) != full.view(np.uint32))
+        assert bad.size == 0, f"rank {rank} NAdam step {step}: {bad.size} parameters differ, first at {bad[0]}"
+        dist.barrier()
+    L.gm_tensor_list_destroy(lst)
+    for p in (dg, dm, dv, arena):
+        dev.free(p)
 
 
 def reduce_scatter(L, dev, z, plan, rank, world):
